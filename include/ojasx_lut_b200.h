@@ -1,0 +1,133 @@
+/*
+ * ojasx_lut_b200.h -- C ABI of libojasx_lut_b200.so, the sm_100a (B200) implementation of the
+ * split-manifold LUT execution path.
+ *
+ * Two groups of entry points:
+ *
+ *  1. The reference's handle API, same names, argument lists and return codes as
+ *     split_manifold_lut_experiment/native/include/ojasx_lut_c_api.h:35-150.  All data
+ *     pointers are HOST pointers; create_* deep-copies the arrays into device memory (the
+ *     reference deep-copies into std::vector, ojasx_lut_c_api.cpp:44-58, 230-251); *_forward
+ *     copies x to the device, runs the CUDA kernels on the handle's stream, copies y back and
+ *     returns after the result is in host memory.  A program or binding written against the
+ *     reference's libojasx_lut.so can load this library instead without changes.
+ *
+ *  2. ojasx_b200_* entry points that take DEVICE pointers and a CUDA stream (passed as void*,
+ *     like ojasx_cuda_rvq_fused_gemm in ojasx_24x96/native/vq_kernels_cuda.cu:230-245).  They
+ *     enqueue work and return without synchronising.
+ *
+ * Return codes: 0 ok, -1 null or invalid argument, -2 index out of range (both as the
+ * reference), -3 CUDA runtime error (text via ojasx_b200_last_error), -4 unsupported
+ * configuration, -5 size beyond a stated limit.
+ *
+ * There is no CPU fallback: every forward needs a CUDA device.
+ */
+#ifndef OJASX_LUT_B200_H
+#define OJASX_LUT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OJASX_API __attribute__((visibility("default")))
+
+typedef void* OjasxLinearHandle;
+typedef void* OjasxKVHandle;
+typedef void* OjasxMoEHandle;
+
+#define OJASX_B200_F32 0
+#define OJASX_B200_BF16 1
+
+/* ------------------------------------------------------------------ 1. reference handle API */
+
+/* ojasx_lut_c_api.h:40-41 */
+OJASX_API const char* ojasx_get_version(void);
+OJASX_API const char* ojasx_get_backend_name(void);
+
+/* ojasx_lut_c_api.h:46-55.  codebook [codebook_size, block_dim] f32, codes [out, in/block_dim]
+ * u8, scales [out] f32 (NULL = ones), bias [out] f32 (NULL = none). */
+OJASX_API OjasxLinearHandle ojasx_create_linear(int in_features, int out_features, int block_dim,
+                                                int codebook_size, const float* codebook_data,
+                                                const uint8_t* codes_data, const float* scales_data,
+                                                const float* bias_data);
+/* ojasx_lut_c_api.h:60-66.  row_ptrs has out_features+1 entries. */
+OJASX_API int ojasx_set_linear_outliers(OjasxLinearHandle handle, int nnz, const int* row_ptrs,
+                                        const int* col_indices, const float* values);
+/* ojasx_lut_c_api.h:72-78.  x [batch, in] f32 host, y [batch, out] f32 host.  num_threads is
+ * accepted and ignored (the work runs on the GPU). */
+OJASX_API int ojasx_linear_forward(OjasxLinearHandle handle, const float* x, float* y, int batch_size,
+                                   int num_threads);
+/* ojasx_lut_c_api.h:83-86 */
+OJASX_API size_t ojasx_get_compressed_size(OjasxLinearHandle handle);
+OJASX_API size_t ojasx_get_dense_size(OjasxLinearHandle handle);
+OJASX_API size_t ojasx_get_lut_sram_size(OjasxLinearHandle handle);
+OJASX_API float ojasx_get_compression_ratio(OjasxLinearHandle handle);
+/* ojasx_lut_c_api.h:91 */
+OJASX_API void ojasx_destroy_linear(OjasxLinearHandle handle);
+
+/* ojasx_lut_c_api.h:96-121.  The reference's cache as shipped: per token and per block_dim-wide
+ * block, the block's first coordinate as int8 with a per-token abs-max scale
+ * (ojasx_lut_kv_cache.cpp:16-65).  Grows by doubling like the reference. */
+OJASX_API OjasxKVHandle ojasx_create_kv_cache(int num_heads, int head_dim, int max_seq_len, int block_dim);
+OJASX_API int ojasx_kv_cache_append(OjasxKVHandle handle, int head_idx, const float* k, const float* v);
+OJASX_API int ojasx_kv_cache_attention(OjasxKVHandle handle, int head_idx, const float* q,
+                                       float* out_context, float scale_factor);
+OJASX_API size_t ojasx_kv_cache_get_memory_size(OjasxKVHandle handle);
+OJASX_API float ojasx_kv_cache_get_compression_ratio(OjasxKVHandle handle);
+OJASX_API void ojasx_destroy_kv_cache(OjasxKVHandle handle);
+
+/* ojasx_lut_c_api.h:126-150 */
+OJASX_API OjasxMoEHandle ojasx_create_moe(int num_experts, int hidden_dim, int intermediate_dim, int top_k,
+                                          int block_dim, const float* codebook_in, const float* codebook_down,
+                                          const uint8_t* gate_up_codes, const float* gate_up_scales,
+                                          const uint8_t* down_codes, const float* down_scales);
+OJASX_API int ojasx_moe_forward(OjasxMoEHandle handle, const float* x, const int* top_k_indices,
+                                const float* top_k_weights, float* y_out, int k_active);
+OJASX_API size_t ojasx_moe_get_compressed_size(OjasxMoEHandle handle);
+OJASX_API float ojasx_moe_get_compression_ratio(OjasxMoEHandle handle);
+OJASX_API void ojasx_destroy_moe(OjasxMoEHandle handle);
+
+/* ------------------------------------------------------------------ 2. device-pointer API */
+
+/* Text of the last error raised on the calling thread ("" if none). */
+OJASX_API const char* ojasx_b200_last_error(void);
+/* Number of kernels this library has launched since it was loaded (all threads). */
+OJASX_API unsigned long long ojasx_b200_launch_count(void);
+
+/* Forward of a linear handle on device buffers; replaces ojasx_linear_forward
+ * (ojasx_lut_c_api.h:72-78) for callers whose activations already live on the GPU.
+ * d_x [batch, in] and d_y [batch, row_stop-row_start] are of io_dtype (OJASX_B200_F32 / _BF16;
+ * bf16 follows ojasx_24x96/math_engine.py:161,208: widen x to fp32, compute in fp32, round y).
+ * Rows [row_start,row_stop) follow the row-slice contract of rvq_fused_gemm
+ * (ojasx_24x96/native/ojasx_backend_abi.h:97-111); pass 0, out_features for the whole layer. */
+OJASX_API int ojasx_b200_linear_forward(OjasxLinearHandle handle, const void* d_x, void* d_y, int batch_size,
+                                        int io_dtype, int row_start, int row_stop, void* stream);
+
+/* Same computation on borrowed device arrays, no handle: the device twin of
+ * ojasx_cuda_rvq_fused_gemm (ojasx_24x96/native/vq_kernels_cuda.cu:230-258) for the
+ * 8-bit single-stage layout, plus the CSR outliers of ojasx_set_linear_outliers. */
+OJASX_API int ojasx_b200_linear_forward_raw(const uint8_t* d_codes, const float* d_codebook,
+                                            const float* d_scales, const float* d_bias, int nnz,
+                                            const int* d_row_ptrs, const int* d_col_indices,
+                                            const float* d_values, const void* d_x, void* d_y,
+                                            int batch_size, int io_dtype, int block_dim, int codebook_size,
+                                            int rows, int columns, int row_start, int row_stop, void* stream);
+
+/* One launch over many independent linear handles (no counterpart in the reference, which
+ * runs one layer per call): problem p reads d_x + p*x_stride_bytes and writes
+ * d_y + p*y_stride_bytes.  x_stride_bytes == 0 feeds every layer the same activations
+ * (q/k/v, gate/up).  All handles must share block_dim. */
+typedef void* OjasxLinearGroupHandle;
+OJASX_API OjasxLinearGroupHandle ojasx_b200_create_linear_group(const OjasxLinearHandle* handles, int count);
+OJASX_API int ojasx_b200_linear_group_forward(OjasxLinearGroupHandle group, const void* d_x,
+                                              size_t x_stride_bytes, void* d_y, size_t y_stride_bytes,
+                                              int io_dtype, void* stream);
+OJASX_API void ojasx_b200_destroy_linear_group(OjasxLinearGroupHandle group);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OJASX_LUT_B200_H */

@@ -1,0 +1,65 @@
+"""Loader for libojasx_lut_b200.so.  There is no fallback: a missing library is an error."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG_DIR, "libojasx_lut_b200.so")
+
+_vp, _i, _sz, _f = C.c_void_p, C.c_int, C.c_size_t, C.c_float
+
+# name -> (restype, argtypes); mirrors include/ojasx_lut_b200.h
+SIGNATURES = {
+    "ojasx_get_version": (C.c_char_p, []),
+    "ojasx_get_backend_name": (C.c_char_p, []),
+    "ojasx_create_linear": (_vp, [_i, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "ojasx_set_linear_outliers": (_i, [_vp, _i, _vp, _vp, _vp]),
+    "ojasx_linear_forward": (_i, [_vp, _vp, _vp, _i, _i]),
+    "ojasx_get_compressed_size": (_sz, [_vp]),
+    "ojasx_get_dense_size": (_sz, [_vp]),
+    "ojasx_get_lut_sram_size": (_sz, [_vp]),
+    "ojasx_get_compression_ratio": (_f, [_vp]),
+    "ojasx_destroy_linear": (None, [_vp]),
+    "ojasx_b200_last_error": (C.c_char_p, []),
+    "ojasx_b200_launch_count": (C.c_ulonglong, []),
+    "ojasx_b200_linear_forward": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "ojasx_b200_linear_forward_raw": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp,
+                                           _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "ojasx_b200_create_linear_group": (_vp, [_vp, _i]),
+    "ojasx_b200_linear_group_forward": (_i, [_vp, _vp, _sz, _vp, _sz, _i, _vp]),
+    "ojasx_b200_destroy_linear_group": (None, [_vp]),
+}
+
+_lib = None
+
+
+class OjasxB200Error(RuntimeError):
+    pass
+
+
+def lib() -> C.CDLL:
+    """The loaded library.  Raises if it has not been built (run build.py / __graft_entry__.build())."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise OjasxB200Error(
+                f"{LIB_PATH} is missing: build it with `python {os.path.join(PKG_DIR, 'build.py')}`; "
+                "this package has no CPU or PyTorch fallback")
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)  # AttributeError here = header and library disagree
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = lib().ojasx_b200_last_error().decode(errors="replace")
+        raise OjasxB200Error(f"{what} failed with status {rc}" + (f": {msg}" if msg else ""))
+
+
+def launch_count() -> int:
+    return int(lib().ojasx_b200_launch_count())

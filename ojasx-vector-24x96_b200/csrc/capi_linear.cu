@@ -1,0 +1,263 @@
+// C ABI, linear-layer part: the reference's ojasx_*linear* handle API on host pointers
+// (split_manifold_lut_experiment/native/src/ojasx_lut_c_api.cpp:31-129) and the ojasx_b200_*
+// device-pointer entry points.  Handles own device copies of every array.
+#include "../../include/ojasx_lut_b200.h"
+#include "handles.h"
+#include "launch.h"
+
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <vector>
+
+namespace ojx {
+
+static thread_local char g_err[512] = "";
+static std::atomic<unsigned long long> g_launches{0};
+
+void set_last_error(const char* what, cudaError_t e) {
+    std::snprintf(g_err, sizeof(g_err), "%s: %s", what, cudaGetErrorString(e));
+}
+void set_last_error_msg(const char* what) { std::snprintf(g_err, sizeof(g_err), "%s", what); }
+void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
+
+int num_sms() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return kNumSMsDefault;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = kNumSMsDefault;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+int upload(void** dptr, const void* host, size_t bytes) {
+    *dptr = nullptr;
+    if (bytes == 0) return OJX_OK;
+    OJX_CUDA_TRY(cudaMalloc(dptr, bytes));
+    if (host) OJX_CUDA_TRY(cudaMemcpy(*dptr, host, bytes, cudaMemcpyHostToDevice));
+    else OJX_CUDA_TRY(cudaMemset(*dptr, 0, bytes));
+    return OJX_OK;
+}
+
+int ensure_capacity(void** dptr, size_t* cap, size_t bytes) {
+    if (*cap >= bytes && *dptr) return OJX_OK;
+    if (*dptr) OJX_CUDA_TRY(cudaFree(*dptr));
+    *dptr = nullptr;
+    *cap = 0;
+    size_t want = bytes < 4096 ? 4096 : bytes;
+    OJX_CUDA_TRY(cudaMalloc(dptr, want));
+    *cap = want;
+    return OJX_OK;
+}
+
+DeviceGuard::DeviceGuard(int dev) : prev_(-1) {
+    if (cudaGetDevice(&prev_) != cudaSuccess) prev_ = -1;
+    if (prev_ != dev) cudaSetDevice(dev); else prev_ = -1;
+}
+DeviceGuard::~DeviceGuard() { if (prev_ >= 0) cudaSetDevice(prev_); }
+
+LinearHandle::~LinearHandle() {
+    DeviceGuard g(dev);
+    cudaFree(codes); cudaFree(codebook); cudaFree(scales); cudaFree(bias);
+    cudaFree(row_ptrs); cudaFree(cols); cudaFree(vals); cudaFree(d_x); cudaFree(d_y);
+    if (stream) cudaStreamDestroy(stream);
+}
+
+LinearProblem LinearHandle::problem(const void* x, void* y, int batch, int io_dtype, int row_start, int row_stop) const {
+    LinearProblem P{};
+    P.codes = codes; P.codebook = codebook; P.scales = scales; P.bias = bias;
+    P.csr = CsrView{row_ptrs, cols, vals, nnz};
+    P.x = x; P.y = y; P.K = in; P.G = G; P.D = D; P.Kcb = Kcb;
+    P.row_start = row_start; P.row_stop = row_stop; P.batch = batch; P.io_dtype = io_dtype;
+    return P;
+}
+
+}  // namespace ojx
+
+using namespace ojx;
+
+extern "C" {
+
+const char* ojasx_get_version(void) { return "OjasX-LUT-Engine-v1.0.0-B200"; }
+const char* ojasx_get_backend_name(void) { return "NVIDIA_CUDA_sm_100a"; }
+const char* ojasx_b200_last_error(void) { return g_err; }
+unsigned long long ojasx_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+OjasxLinearHandle ojasx_create_linear(int in_features, int out_features, int block_dim, int codebook_size,
+                                      const float* codebook_data, const uint8_t* codes_data,
+                                      const float* scales_data, const float* bias_data) {
+    if (in_features <= 0 || out_features <= 0 || block_dim <= 0 || codebook_size <= 0 || codebook_size > 256) {
+        set_last_error_msg("ojasx_create_linear: invalid dimensions");
+        return nullptr;
+    }
+    auto* h = new (std::nothrow) LinearHandle();
+    if (!h) return nullptr;
+    h->in = in_features; h->out = out_features; h->D = block_dim; h->Kcb = codebook_size;
+    h->G = in_features / block_dim;  // ojasx_lut.h:92
+    if (cudaGetDevice(&h->dev) != cudaSuccess) { set_last_error_msg("no CUDA device"); delete h; return nullptr; }
+    int rc = OJX_OK;
+    // Null data pointers leave the array zero-filled (codes, codebook) or at its default
+    // (scales = 1, no bias), as the reference constructor does (ojasx_lut.h:95-98).
+    if ((rc = upload((void**)&h->codebook, codebook_data, sizeof(float) * (size_t)codebook_size * block_dim)) == OJX_OK &&
+        (rc = upload((void**)&h->codes, codes_data, (size_t)out_features * h->G)) == OJX_OK) {
+        if (scales_data) rc = upload((void**)&h->scales, scales_data, sizeof(float) * (size_t)out_features);
+        if (rc == OJX_OK && bias_data) rc = upload((void**)&h->bias, bias_data, sizeof(float) * (size_t)out_features);
+    }
+    if (rc == OJX_OK && cudaStreamCreateWithFlags(&h->stream, cudaStreamNonBlocking) != cudaSuccess) rc = OJX_ERR_CUDA;
+    if (rc != OJX_OK) { delete h; return nullptr; }
+    return h;
+}
+
+int ojasx_set_linear_outliers(OjasxLinearHandle handle, int nnz, const int* row_ptrs, const int* col_indices,
+                              const float* values) {
+    if (!handle) return OJX_ERR_ARG;
+    auto* h = static_cast<LinearHandle*>(handle);
+    if (nnz < 0 || !row_ptrs || (nnz > 0 && (!col_indices || !values))) return OJX_ERR_ARG;
+    DeviceGuard g(h->dev);
+    cudaFree(h->row_ptrs); cudaFree(h->cols); cudaFree(h->vals);
+    h->row_ptrs = nullptr; h->cols = nullptr; h->vals = nullptr; h->nnz = 0;
+    int rc;
+    if ((rc = upload((void**)&h->row_ptrs, row_ptrs, sizeof(int) * (size_t)(h->out + 1))) != OJX_OK) return rc;
+    if ((rc = upload((void**)&h->cols, col_indices, sizeof(int) * (size_t)nnz)) != OJX_OK) return rc;
+    if ((rc = upload((void**)&h->vals, values, sizeof(float) * (size_t)nnz)) != OJX_OK) return rc;
+    h->nnz = nnz;
+    h->has_outlier_arrays = true;
+    return OJX_OK;
+}
+
+int ojasx_b200_linear_forward(OjasxLinearHandle handle, const void* d_x, void* d_y, int batch_size, int io_dtype,
+                              int row_start, int row_stop, void* stream) {
+    if (!handle || !d_x || !d_y) return OJX_ERR_ARG;
+    auto* h = static_cast<LinearHandle*>(handle);
+    if (batch_size <= 0 || row_start < 0 || row_stop > h->out || row_start >= row_stop) return OJX_ERR_ARG;
+    if (io_dtype != OJX_F32 && io_dtype != OJX_BF16) return OJX_ERR_ARG;
+    return launch_linear(h->problem(d_x, d_y, batch_size, io_dtype, row_start, row_stop),
+                         static_cast<cudaStream_t>(stream));
+}
+
+int ojasx_b200_linear_forward_raw(const uint8_t* d_codes, const float* d_codebook, const float* d_scales,
+                                  const float* d_bias, int nnz, const int* d_row_ptrs, const int* d_col_indices,
+                                  const float* d_values, const void* d_x, void* d_y, int batch_size, int io_dtype,
+                                  int block_dim, int codebook_size, int rows, int columns, int row_start,
+                                  int row_stop, void* stream) {
+    if (!d_codes || !d_codebook || !d_x || !d_y) return OJX_ERR_ARG;
+    if (batch_size <= 0 || rows <= 0 || columns <= 0 || block_dim <= 0 || row_start < 0 || row_stop > rows ||
+        row_start >= row_stop)
+        return OJX_ERR_ARG;
+    if (io_dtype != OJX_F32 && io_dtype != OJX_BF16) return OJX_ERR_ARG;
+    LinearProblem P{};
+    P.codes = d_codes; P.codebook = d_codebook; P.scales = d_scales; P.bias = d_bias;
+    P.csr = CsrView{d_row_ptrs, d_col_indices, d_values, nnz};
+    P.x = d_x; P.y = d_y; P.K = columns;
+    P.G = (columns + block_dim - 1) / block_dim;  // blocks_per_row of the packed layout (codec.py:108)
+    P.D = block_dim; P.Kcb = codebook_size;
+    P.row_start = row_start; P.row_stop = row_stop; P.batch = batch_size; P.io_dtype = io_dtype;
+    return launch_linear(P, static_cast<cudaStream_t>(stream));
+}
+
+int ojasx_linear_forward(OjasxLinearHandle handle, const float* x, float* y, int batch_size, int num_threads) {
+    (void)num_threads;
+    if (!handle || !x || !y) return OJX_ERR_ARG;  // ojasx_lut_c_api.cpp:100
+    auto* h = static_cast<LinearHandle*>(handle);
+    if (batch_size <= 0) return OJX_OK;           // the reference's batch loop simply does not run
+    DeviceGuard g(h->dev);
+    const size_t xb = sizeof(float) * (size_t)batch_size * h->in, yb = sizeof(float) * (size_t)batch_size * h->out;
+    int rc;
+    if ((rc = ensure_capacity(&h->d_x, &h->cap_x, xb)) != OJX_OK) return rc;
+    if ((rc = ensure_capacity(&h->d_y, &h->cap_y, yb)) != OJX_OK) return rc;
+    OJX_CUDA_TRY(cudaMemcpyAsync(h->d_x, x, xb, cudaMemcpyHostToDevice, h->stream));
+    rc = launch_linear(h->problem(h->d_x, h->d_y, batch_size, OJX_F32, 0, h->out), h->stream);
+    if (rc != OJX_OK) return rc;
+    OJX_CUDA_TRY(cudaMemcpyAsync(y, h->d_y, yb, cudaMemcpyDeviceToHost, h->stream));
+    OJX_CUDA_TRY(cudaStreamSynchronize(h->stream));
+    return OJX_OK;
+}
+
+/* Size queries: formulas of ojasx_lut.h:101-124 (the scales vector always exists in the
+ * reference object, so its bytes are always counted). */
+size_t ojasx_get_compressed_size(OjasxLinearHandle handle) {
+    if (!handle) return 0;
+    auto* h = static_cast<LinearHandle*>(handle);
+    size_t n = (size_t)h->out * h->G + sizeof(float) * (size_t)h->Kcb * h->D + sizeof(float) * (size_t)h->out;
+    if (h->bias) n += sizeof(float) * (size_t)h->out;
+    if (h->has_outlier_arrays) n += (size_t)h->nnz * 8 + sizeof(int) * (size_t)(h->out + 1);
+    return n;
+}
+size_t ojasx_get_dense_size(OjasxLinearHandle handle) {
+    if (!handle) return 0;
+    auto* h = static_cast<LinearHandle*>(handle);
+    return (size_t)h->out * h->in * sizeof(float);
+}
+size_t ojasx_get_lut_sram_size(OjasxLinearHandle handle) {
+    if (!handle) return 0;
+    auto* h = static_cast<LinearHandle*>(handle);
+    return (size_t)h->G * h->Kcb * sizeof(float);
+}
+float ojasx_get_compression_ratio(OjasxLinearHandle handle) {
+    if (!handle) return 0.0f;
+    size_t c = ojasx_get_compressed_size(handle);
+    return (float)ojasx_get_dense_size(handle) / (float)(c ? c : 1);
+}
+void ojasx_destroy_linear(OjasxLinearHandle handle) {
+    if (handle) delete static_cast<LinearHandle*>(handle);
+}
+
+/* ---- grouped launch */
+OjasxLinearGroupHandle ojasx_b200_create_linear_group(const OjasxLinearHandle* handles, int count) {
+    if (!handles || count <= 0) return nullptr;
+    auto* g = new (std::nothrow) LinearGroup();
+    if (!g) return nullptr;
+    g->host.resize(count);
+    int item = 0;
+    for (int i = 0; i < count; ++i) {
+        auto* h = static_cast<LinearHandle*>(handles[i]);
+        if (!h || (i > 0 && h->D != g->D)) { set_last_error_msg("linear group: null handle or mixed block_dim"); delete g; return nullptr; }
+        if (i == 0) { g->D = h->D; g->dev = h->dev; }
+        LinearProblem P = h->problem(nullptr, nullptr, 1, OJX_F32, 0, h->out);
+        P.tile_rows = plan_tile_rows(h->out, count);
+        P.tiles = (h->out + P.tile_rows - 1) / P.tile_rows;
+        P.item_begin = item;
+        item += P.tiles;
+        g->host[i] = P;
+    }
+    g->total_items = item;
+    if (cudaMalloc((void**)&g->dev_probs, sizeof(LinearProblem) * (size_t)count) != cudaSuccess) { delete g; return nullptr; }
+    return g;
+}
+
+int ojasx_b200_linear_group_forward(OjasxLinearGroupHandle group, const void* d_x, size_t x_stride_bytes, void* d_y,
+                                    size_t y_stride_bytes, int io_dtype, void* stream) {
+    if (!group || !d_x || !d_y) return OJX_ERR_ARG;
+    if (io_dtype != OJX_F32 && io_dtype != OJX_BF16) return OJX_ERR_ARG;
+    auto* g = static_cast<LinearGroup*>(group);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // The problem table is rewritten only when the I/O binding changes, so steady-state calls
+    // enqueue exactly one kernel.
+    if (g->bound_x != d_x || g->bound_y != d_y || g->bound_xs != x_stride_bytes || g->bound_ys != y_stride_bytes ||
+        g->bound_dtype != io_dtype) {
+        for (size_t i = 0; i < g->host.size(); ++i) {
+            g->host[i].x = static_cast<const char*>(d_x) + i * x_stride_bytes;
+            g->host[i].y = static_cast<char*>(d_y) + i * y_stride_bytes;
+            g->host[i].io_dtype = io_dtype;
+        }
+        OJX_CUDA_TRY(cudaMemcpyAsync(g->dev_probs, g->host.data(), sizeof(LinearProblem) * g->host.size(),
+                                     cudaMemcpyHostToDevice, s));
+        OJX_CUDA_TRY(cudaStreamSynchronize(s));
+        g->bound_x = d_x; g->bound_y = d_y; g->bound_xs = x_stride_bytes; g->bound_ys = y_stride_bytes;
+        g->bound_dtype = io_dtype;
+    }
+    return launch_linear_group(g->dev_probs, (int)g->host.size(), g->total_items, g->D, s);
+}
+
+void ojasx_b200_destroy_linear_group(OjasxLinearGroupHandle group) {
+    if (!group) return;
+    auto* g = static_cast<LinearGroup*>(group);
+    cudaFree(g->dev_probs);
+    delete g;
+}
+
+}  // extern "C"

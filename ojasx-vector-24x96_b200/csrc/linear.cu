@@ -1,0 +1,147 @@
+// VQ linear layer:  y[b,m] = (sum_g LUT_b[g, codes[m,g]]) * scales[m] (+ bias[m]) + CSR row m . x_b
+// Replaces SplitManifoldLinear::forward_cpu + forward_outliers_cpu
+// (split_manifold_lut_experiment/native/src/ojasx_lut_cpu.cpp:104-206) and the three kernels of
+// split_manifold_lut_experiment/native/src/ojasx_lut_cuda.cu:28-162 with one persistent kernel:
+// table build, code gather and CSR outlier add all happen in the CTA that owns the rows, and y
+// is written once.
+#include "lut_core.cuh"
+#include "launch.h"
+#include "handles.h"
+
+namespace ojx {
+
+__device__ __forceinline__ const LinearProblem& find_problem(const LinearProblem* probs, int nprobs, int item) {
+    int lo = 0, hi = nprobs - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (probs[mid].item_begin <= item) lo = mid; else hi = mid - 1;
+    }
+    return probs[lo];
+}
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1)
+lut_linear_kernel(const LinearProblem* __restrict__ probs, int nprobs, int total_items,
+                  const __grid_constant__ LinearProblem single) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    CoreSmem& sm = *reinterpret_cast<CoreSmem*>(smem_raw);
+
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+        const LinearProblem P = probs ? find_problem(probs, nprobs, item) : single;
+        const int local = item - P.item_begin;
+        const int b = local / P.tiles, t = local - b * P.tiles;
+        const int r0 = P.row_start + t * P.tile_rows;
+        const int n = min(P.tile_rows, P.row_stop - r0);
+        const int rows_out = P.row_stop - P.row_start;
+        const size_t esz = P.io_dtype == OJX_BF16 ? 2 : 4;
+
+        RowSet rs;
+        rs.base0 = P.codes + (size_t)r0 * P.G;
+        rs.base1 = rs.base0;
+        rs.n0 = n;
+        rs.n = n;
+        rs.G = P.G;
+        rs.aligned = ((P.G & 15) == 0) && ((reinterpret_cast<uintptr_t>(P.codes) & 15) == 0);
+        const XLoad xl{static_cast<const char*>(P.x) + (size_t)b * P.K * esz, P.K, P.io_dtype};
+
+        RowWalker<D> walker(sm, rs);
+        if (walker.nslices == 0)
+            for (int lr = threadIdx.x; lr < n; lr += kThreads) sm.acc[lr] = 0.0f;
+        walker.run(xl, P.codebook, P.Kcb);
+        __syncthreads();
+
+        // Epilogue (ojasx_lut_cpu.cpp:178-182 then :117-127): scale, bias, outlier row, one store.
+        for (int lr = threadIdx.x; lr < n; lr += kThreads) {
+            const int m = r0 + lr;
+            float res = sm.acc[lr];
+            if (P.scales) res = __fmul_rn(res, P.scales[m]);
+            if (P.bias) res = __fadd_rn(res, P.bias[m]);
+            if (P.csr.nnz > 0) res = __fadd_rn(res, csr_row_sum(P.csr, m, xl));
+            const size_t o = (size_t)b * rows_out + (m - P.row_start);
+            if (P.io_dtype == OJX_BF16) reinterpret_cast<__nv_bfloat16*>(P.y)[o] = __float2bfloat16_rn(res);
+            else reinterpret_cast<float*>(P.y)[o] = res;
+        }
+        __syncthreads();
+    }
+}
+
+using LinearKernel = void (*)(const LinearProblem*, int, int, const LinearProblem);
+
+static LinearKernel pick_linear_kernel(int D) {
+    switch (D) {
+        case 4: return lut_linear_kernel<4>;
+        case 8: return lut_linear_kernel<8>;
+        case 16: return lut_linear_kernel<16>;
+        case 32: return lut_linear_kernel<32>;
+        default: return nullptr;
+    }
+}
+
+static int prepare_kernel(LinearKernel k) {
+    // Opt in to the large dynamic shared-memory carve-out once per kernel per device.
+    static thread_local LinearKernel done[8] = {};
+    static thread_local int done_dev[8] = {};
+    int dev = 0;
+    OJX_CUDA_TRY(cudaGetDevice(&dev));
+    for (int i = 0; i < 8; ++i)
+        if (done[i] == k && done_dev[i] == dev + 1) return OJX_OK;
+    OJX_CUDA_TRY(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(CoreSmem)));
+    for (int i = 0; i < 8; ++i)
+        if (done[i] == nullptr) { done[i] = k; done_dev[i] = dev + 1; break; }
+    return OJX_OK;
+}
+
+int plan_tile_rows(int rows, int parallel_items) {
+    // Spread one problem over the SMs when it is alone; otherwise keep tiles large so the table
+    // build (replicated per tile) is amortised over many rows.
+    const int sms = num_sms();
+    int tiles_wanted = sms / (parallel_items > 0 ? parallel_items : 1);
+    if (tiles_wanted < 1) tiles_wanted = 1;
+    int tr = round_up((rows + tiles_wanted - 1) / tiles_wanted, 32);
+    if (tr < 32) tr = 32;
+    if (tr > kAccRows) tr = kAccRows;
+    return tr;
+}
+
+int validate_linear(const LinearProblem& P) {
+    if (!P.codes || !P.codebook || !P.x || !P.y) return OJX_ERR_ARG;
+    if (P.batch <= 0 || P.K <= 0 || P.G < 0 || P.row_stop <= P.row_start || P.row_start < 0) return OJX_ERR_ARG;
+    if (P.Kcb <= 0 || P.Kcb > 256) return OJX_ERR_UNSUPPORTED;
+    if (!pick_linear_kernel(P.D)) return OJX_ERR_UNSUPPORTED;
+    if (P.csr.nnz > 0 && (!P.csr.row_ptrs || !P.csr.cols || !P.csr.vals)) return OJX_ERR_ARG;
+    return OJX_OK;
+}
+
+int launch_linear(LinearProblem P, cudaStream_t stream) {
+    int rc = validate_linear(P);
+    if (rc != OJX_OK) return rc;
+    const int rows = P.row_stop - P.row_start;
+    if (P.tile_rows <= 0) P.tile_rows = plan_tile_rows(rows, P.batch);
+    P.tiles = (rows + P.tile_rows - 1) / P.tile_rows;
+    P.item_begin = 0;
+    const int total = P.tiles * P.batch;
+    LinearKernel k = pick_linear_kernel(P.D);
+    rc = prepare_kernel(k);
+    if (rc != OJX_OK) return rc;
+    const int grid = total < num_sms() ? total : num_sms();
+    k<<<grid, kThreads, sizeof(CoreSmem), stream>>>(nullptr, 0, total, P);
+    count_launch(1);
+    OJX_CUDA_TRY(cudaGetLastError());
+    return OJX_OK;
+}
+
+int launch_linear_group(const LinearProblem* d_probs, int nprobs, int total_items, int D, cudaStream_t stream) {
+    if (!d_probs || nprobs <= 0 || total_items <= 0) return OJX_ERR_ARG;
+    LinearKernel k = pick_linear_kernel(D);
+    if (!k) return OJX_ERR_UNSUPPORTED;
+    int rc = prepare_kernel(k);
+    if (rc != OJX_OK) return rc;
+    const int grid = total_items < num_sms() ? total_items : num_sms();
+    LinearProblem dummy{};
+    k<<<grid, kThreads, sizeof(CoreSmem), stream>>>(d_probs, nprobs, total_items, dummy);
+    count_launch(1);
+    OJX_CUDA_TRY(cudaGetLastError());
+    return OJX_OK;
+}
+
+}  // namespace ojx

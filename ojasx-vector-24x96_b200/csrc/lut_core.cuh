@@ -1,0 +1,244 @@
+// Core of the split-manifold LUT path: build an fp32 lookup-table slice in shared memory and
+// accumulate, for a set of code rows, sum_g LUT[g, code[row, g]] in ascending g with one fp32
+// accumulator per row -- the evaluation order of the reference's CPU kernel
+// (split_manifold_lut_experiment/native/src/ojasx_lut_cpu.cpp:93-100 for the table,
+// :161-175 for the row sum), so results are bit-identical to it.
+//
+// Shape of the computation on one SM (one 512-thread CTA, ~214 KB of shared memory):
+//   * the table of one token is G*256 fp32 and does not fit, so the group axis is cut into
+//     slices of <= 128 groups (128 KB); slices are processed in ascending order and the
+//     per-row accumulators are parked in shared memory between slices, which keeps the
+//     summation order of a row strictly g = 0..G-1;
+//   * inside a slice each warp owns 32-row blocks; lane l walks row l of the block, so the
+//     row sum stays sequential; code bytes arrive through a per-warp 4-stage cp.async ring
+//     of 32 rows x 32 bytes, loaded as coalesced 16-byte pieces and read back as two
+//     conflict-free 128-bit shared loads per lane;
+//   * the only CTA-wide barriers are around the table build of each slice; the code stream
+//     of a warp runs ahead across slice boundaries.
+#pragma once
+#include "common.cuh"
+
+namespace ojx {
+
+constexpr int kThreads = 512;
+constexpr int kWarps = kThreads / 32;
+constexpr int kSliceGroups = 128;            // table slice: 128 groups x 256 entries x 4 B = 128 KB
+constexpr int kXsFloats = kSliceGroups * 16; // x slice staging (block_dim <= 16 at 128 groups)
+constexpr int kAccRows = 3584;               // rows per work item that can park an accumulator
+constexpr int kChunk = 32;                   // code bytes per row per ring stage
+constexpr int kStages = 4;
+constexpr int kStageBytes = 32 * kChunk;     // 32 rows x 32 bytes
+
+struct alignas(16) CoreSmem {
+    float lut[kSliceGroups * 256];
+    float acc[kAccRows];
+    float xs[kXsFloats];
+    uint8_t ring[kWarps * kStages * kStageBytes];
+};
+static_assert(sizeof(CoreSmem) <= 227 * 1024, "shared memory budget");
+
+// Rows of a work item: local row lr < n0 lives at base0 + lr*G, the rest at base1 + (lr-n0)*G
+// (two ranges so that an expert's gate rows and up rows can share one table pass).
+struct RowSet {
+    const uint8_t* base0;
+    const uint8_t* base1;
+    int n0;
+    int n;        // total local rows (<= kAccRows)
+    int G;        // code bytes per row
+    int aligned;  // 1: G % 16 == 0 and both bases 16-byte aligned -> cp.async path
+};
+
+// Reads element k of the activation vector as fp32; k >= K reads as zero (the reference's
+// LUT GEMM pads the feature axis with zeros, ojasx_24x96/math_engine.py:166-171).
+struct XLoad {
+    const void* p;
+    int K;
+    int dtype;
+    __device__ __forceinline__ float operator()(int k) const {
+        if (k >= K) return 0.0f;
+        if (dtype == OJX_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[k]);
+        return reinterpret_cast<const float*>(p)[k];
+    }
+};
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, int src_bytes) {
+    unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(gsrc), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+template <int D>
+constexpr int slice_groups() { return (kXsFloats / D) < kSliceGroups ? (kXsFloats / D) : kSliceGroups; }
+
+// Position of a warp's code stream: slice s, row block rb, 32-byte chunk cc inside the slice.
+struct StagePos {
+    int s, rb, cc;
+    bool valid;
+};
+
+template <int D>
+struct RowWalker {
+    static constexpr int SG = slice_groups<D>();
+
+    CoreSmem& sm;
+    const RowSet rs;
+    const int warp, lane, nrb, nslices;
+
+    __device__ RowWalker(CoreSmem& sm_, const RowSet& rs_)
+        : sm(sm_), rs(rs_), warp(threadIdx.x >> 5), lane(threadIdx.x & 31), nrb((rs_.n + 31) >> 5),
+          nslices((rs_.G + SG - 1) / SG) {}
+
+    __device__ __forceinline__ int slice_ng(int s) const { int r = rs.G - s * SG; return r < SG ? r : SG; }
+    __device__ __forceinline__ int slice_chunks(int s) const { return (slice_ng(s) + kChunk - 1) / kChunk; }
+
+    __device__ __forceinline__ StagePos first() const { return StagePos{0, warp, 0, warp < nrb && nslices > 0}; }
+    __device__ __forceinline__ void advance(StagePos& p) const {
+        if (!p.valid) return;
+        if (++p.cc == slice_chunks(p.s)) {
+            p.cc = 0;
+            p.rb += kWarps;
+            if (p.rb >= nrb) {
+                p.rb = warp;
+                if (++p.s == nslices) p.valid = false;
+            }
+        }
+    }
+    __device__ __forceinline__ const uint8_t* row_ptr(int lr) const {
+        return lr < rs.n0 ? rs.base0 + (size_t)lr * rs.G : rs.base1 + (size_t)(lr - rs.n0) * rs.G;
+    }
+
+    // Fill ring slot `slot` of this warp with stage p (no-op when p is past the end).
+    __device__ __forceinline__ void issue(const StagePos& p, int slot) const {
+        if (p.valid) {
+            uint8_t* st = sm.ring + (warp * kStages + slot) * kStageBytes;
+            const int col_end = p.s * SG + slice_ng(p.s);
+            const int col0 = p.s * SG + p.cc * kChunk;
+            if (rs.aligned) {
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    const int piece = lane + 32 * q;
+                    const int row = piece >> 1, half = piece & 1;
+                    const int lr = p.rb * 32 + row;
+                    const int col = col0 + half * 16;
+                    const bool ok = lr < rs.n && col < col_end;
+                    const uint8_t* src = ok ? row_ptr(lr) + col : rs.base0;
+                    cp_async16(st + row * kChunk + ((half ^ ((row >> 2) & 1)) << 4), src, ok ? 16 : 0);
+                }
+            } else {
+                const int lr = p.rb * 32 + lane;
+                const uint8_t* src = lr < rs.n ? row_ptr(lr) : nullptr;
+#pragma unroll 4
+                for (int j = 0; j < kChunk; ++j) {
+                    const int col = col0 + j;
+                    const uint8_t v = (src && col < col_end) ? src[col] : (uint8_t)0;
+                    st[lane * kChunk + ((((j >> 4) ^ ((lane >> 2) & 1)) << 4) | (j & 15))] = v;
+                }
+            }
+        }
+        cp_async_commit();
+    }
+
+    // Build table slice s: lut[gl*256 + k] = sum_d x[(g0+gl)*D + d] * cb[k*D + d], d ascending,
+    // separate multiply and add (no fused multiply-add), as ojasx_lut_cpu.cpp:93-100 compiles
+    // to on a baseline x86-64 build.  c[] holds this thread's centroid (tid & 255).
+    __device__ __forceinline__ void build_slice(int s, const XLoad& xl, const float (&c)[D], int Kcb) const {
+        const int g0 = s * SG, ng = slice_ng(s);
+        for (int i = threadIdx.x; i < ng * D; i += kThreads) sm.xs[i] = xl(g0 * D + i);
+        __syncthreads();
+        const int kc = threadIdx.x & 255;
+        for (int gl = threadIdx.x >> 8; gl < ng; gl += kThreads / 256) {
+            const float* xg = sm.xs + gl * D;
+            float dot = __fmul_rn(xg[0], c[0]);
+#pragma unroll
+            for (int d = 1; d < D; ++d) dot = __fadd_rn(dot, __fmul_rn(xg[d], c[d]));
+            sm.lut[gl * 256 + kc] = kc < Kcb ? dot : 0.0f;
+        }
+        __syncthreads();
+    }
+
+    // Consume one landed stage: add the (up to 32) table entries of this lane's row, in order.
+    __device__ __forceinline__ float consume(const StagePos& p, int slot, float acc) const {
+        const uint8_t* st = sm.ring + (warp * kStages + slot) * kStageBytes + lane * kChunk;
+        const int ng = slice_ng(p.s);
+        const int swz = (lane >> 2) & 1;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int gl0 = p.cc * kChunk + h * 16;
+            if (gl0 >= ng) break;
+            const uint4 w = *reinterpret_cast<const uint4*>(st + ((h ^ swz) << 4));
+            const float* lp = sm.lut + gl0 * 256;
+            const unsigned ws[4] = {w.x, w.y, w.z, w.w};
+            if (gl0 + 16 <= ng) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const unsigned code = (ws[j >> 2] >> ((j & 3) * 8)) & 0xffu;
+                    acc = __fadd_rn(acc, lp[j * 256 + code]);
+                }
+            } else {
+                const int nb = ng - gl0;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    if (j < nb) {
+                        const unsigned code = (ws[j >> 2] >> ((j & 3) * 8)) & 0xffu;
+                        acc = __fadd_rn(acc, lp[j * 256 + code]);
+                    }
+                }
+            }
+        }
+        return acc;
+    }
+
+    // Leaves sm.acc[lr] = sum_{g<G} LUT_x[g, code[lr, g]] for lr < rs.n.  All threads of the
+    // CTA must call it; on return a __syncthreads() has NOT yet been executed.
+    __device__ void run(const XLoad& xl, const float* __restrict__ codebook, int Kcb) const {
+        float c[D];
+        {
+            const int kc = threadIdx.x & 255;
+#pragma unroll
+            for (int d = 0; d < D; ++d) c[d] = kc < Kcb ? codebook[kc * D + d] : 0.0f;
+        }
+        StagePos prod = first();
+        StagePos cons = prod;
+        int issued = 0, consumed = 0;
+#pragma unroll
+        for (int i = 0; i < kStages - 1; ++i) {
+            issue(prod, issued % kStages);
+            advance(prod);
+            ++issued;
+        }
+        for (int s = 0; s < nslices; ++s) {
+            __syncthreads();  // every warp has left the previous slice's table (and sm.xs)
+            build_slice(s, xl, c, Kcb);
+            const int nch = slice_chunks(s);
+            for (int rb = warp; rb < nrb; rb += kWarps) {
+                const int lr = rb * 32 + lane;
+                float acc = s == 0 ? 0.0f : sm.acc[lr];
+                for (int cc = 0; cc < nch; ++cc) {
+                    cp_async_wait<kStages - 2>();
+                    __syncwarp();
+                    issue(prod, issued % kStages);
+                    advance(prod);
+                    ++issued;
+                    acc = consume(cons, consumed % kStages, acc);
+                    advance(cons);
+                    ++consumed;
+                }
+                sm.acc[lr] = acc;
+            }
+        }
+        cp_async_wait<0>();
+    }
+};
+
+// CSR outlier row sum, reference order (ojasx_lut_cpu.cpp:117-126): acc = 0; j ascending;
+// acc += val * x[col] with separate multiply and add.
+__device__ __forceinline__ float csr_row_sum(const CsrView& csr, int row, const XLoad& xl) {
+    float acc = 0.0f;
+    const int e = csr.row_ptrs[row + 1];
+    for (int j = csr.row_ptrs[row]; j < e; ++j) acc = __fadd_rn(acc, __fmul_rn(csr.vals[j], xl(csr.cols[j])));
+    return acc;
+}
+
+}  // namespace ojx
