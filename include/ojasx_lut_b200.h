@@ -127,6 +127,56 @@ OJASX_API int ojasx_b200_linear_group_forward(OjasxLinearGroupHandle group, cons
                                               int io_dtype, void* stream);
 OJASX_API void ojasx_b200_destroy_linear_group(OjasxLinearGroupHandle group);
 
+/* ---- MoE on device buffers; replaces ojasx_moe_forward (ojasx_lut_c_api.h:139-146) for any
+ * number of tokens.  d_x, d_y [n_tokens, hidden] of io_dtype; d_topk_idx i32 and d_topk_w f32
+ * are [n_tokens, k_active] with GLOBAL expert ids; ids outside this handle's experts and
+ * weights with |w| < 1e-8 are skipped (ojasx_lut_cpu.cpp:284-286).  The first call with a
+ * larger n_tokens*k_active grows the handle's scratch (cudaMalloc); ojasx_b200_moe_reserve
+ * does that ahead of time. */
+OJASX_API int ojasx_b200_moe_forward(OjasxMoEHandle handle, const void* d_x, const int* d_topk_idx,
+                                     const float* d_topk_w, void* d_y, int n_tokens, int k_active, int io_dtype,
+                                     void* stream);
+OJASX_API int ojasx_b200_moe_reserve(OjasxMoEHandle handle, int max_tokens, int k_active);
+/* CSR outliers on the expert matrices (host arrays; no counterpart in the reference MoE, which
+ * has none: composed like ojasx_set_linear_outliers, ojasx_lut_c_api.h:60-66).  which = 0: the
+ * flattened gate_up matrix [E*2I, hidden]; which = 1: the flattened down matrix [E*hidden, I]. */
+OJASX_API int ojasx_b200_moe_set_outliers(OjasxMoEHandle handle, int which, int nnz, const int* row_ptrs,
+                                          const int* col_indices, const float* values);
+/* Router weights f32 [num_experts_total, hidden] (host).  Formula of
+ * split_manifold_lut_experiment/tools/run_full_48_layers_and_generate.py:172-175:
+ * softmax(x W^T) -> top-k -> renormalise. */
+OJASX_API int ojasx_b200_moe_set_router(OjasxMoEHandle handle, const float* router_weight, int num_experts_total);
+/* Expert-parallel shard: this handle holds global experts [first, first + num_experts). */
+OJASX_API int ojasx_b200_moe_set_expert_offset(OjasxMoEHandle handle, int first_global_expert);
+OJASX_API int ojasx_b200_moe_route(OjasxMoEHandle handle, const void* d_x, int n_tokens, int top_k, int* d_idx_out,
+                                   float* d_w_out, int io_dtype, void* stream);
+/* Router followed by the experts, one stream, no host round trip. */
+OJASX_API int ojasx_b200_moe_forward_routed(OjasxMoEHandle handle, const void* d_x, void* d_y, int n_tokens, int top_k,
+                                            int io_dtype, void* stream);
+
+/* ---- Codebook-VQ KV cache of one layer (no counterpart in the reference, whose HeadKVCache
+ * allocates k_codebook / v_codebook but never reads them, ojasx_lut_kv_cache.h:33-35): every
+ * head vector is head_dim/block_dim uint8 codes into a per-KV-head codebook
+ * f32 [kv_heads, 256, block_dim] (host arrays at create).  Codes live on the device as
+ * [batch, kv_heads, max_seq_len, groups]. */
+typedef void* OjasxKvqHandle;
+OJASX_API OjasxKvqHandle ojasx_b200_kvq_create(int batch, int kv_heads, int q_heads, int head_dim, int block_dim,
+                                               int max_seq_len, const float* k_codebook, const float* v_codebook);
+/* Fill the cache from host codes [batch, kv_heads, seq_len, groups] and set every length to seq_len. */
+OJASX_API int ojasx_b200_kvq_load(OjasxKvqHandle handle, const uint8_t* k_codes, const uint8_t* v_codes, int seq_len);
+/* Copy tokens [t_begin, t_end) of every head back to host arrays [batch, kv_heads, t_end-t_begin, groups]. */
+OJASX_API int ojasx_b200_kvq_read(OjasxKvqHandle handle, uint8_t* k_codes, uint8_t* v_codes, int t_begin, int t_end);
+OJASX_API int ojasx_b200_kvq_seq_len(OjasxKvqHandle handle);
+OJASX_API int ojasx_b200_kvq_reset(OjasxKvqHandle handle);
+/* Append one token per sequence: d_k, d_v [batch, kv_heads, head_dim] of io_dtype; nearest
+ * centroid per sub-vector, rule of ojasx_24x96/codec.py:217-224.  -2 when the cache is full. */
+OJASX_API int ojasx_b200_kvq_append(OjasxKvqHandle handle, const void* d_k, const void* d_v, int io_dtype, void* stream);
+/* One decode query per sequence: d_q, d_out [batch, q_heads, head_dim] of io_dtype; softmax over
+ * every cached token; scale <= 0 means 1/sqrt(head_dim) (ojasx_lut_kv_cache.cpp:74-76). */
+OJASX_API int ojasx_b200_kvq_decode(OjasxKvqHandle handle, const void* d_q, void* d_out, float scale, int io_dtype,
+                                    void* stream);
+OJASX_API void ojasx_b200_kvq_destroy(OjasxKvqHandle handle);
+
 #ifdef __cplusplus
 }
 #endif

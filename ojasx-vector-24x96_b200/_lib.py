@@ -29,6 +29,32 @@ SIGNATURES = {
     "ojasx_b200_create_linear_group": (_vp, [_vp, _i]),
     "ojasx_b200_linear_group_forward": (_i, [_vp, _vp, _sz, _vp, _sz, _i, _vp]),
     "ojasx_b200_destroy_linear_group": (None, [_vp]),
+    "ojasx_create_kv_cache": (_vp, [_i, _i, _i, _i]),
+    "ojasx_kv_cache_append": (_i, [_vp, _i, _vp, _vp]),
+    "ojasx_kv_cache_attention": (_i, [_vp, _i, _vp, _vp, _f]),
+    "ojasx_kv_cache_get_memory_size": (_sz, [_vp]),
+    "ojasx_kv_cache_get_compression_ratio": (_f, [_vp]),
+    "ojasx_destroy_kv_cache": (None, [_vp]),
+    "ojasx_create_moe": (_vp, [_i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "ojasx_moe_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _i]),
+    "ojasx_moe_get_compressed_size": (_sz, [_vp]),
+    "ojasx_moe_get_compression_ratio": (_f, [_vp]),
+    "ojasx_destroy_moe": (None, [_vp]),
+    "ojasx_b200_moe_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "ojasx_b200_moe_reserve": (_i, [_vp, _i, _i]),
+    "ojasx_b200_moe_set_outliers": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
+    "ojasx_b200_moe_set_router": (_i, [_vp, _vp, _i]),
+    "ojasx_b200_moe_set_expert_offset": (_i, [_vp, _i]),
+    "ojasx_b200_moe_route": (_i, [_vp, _vp, _i, _i, _vp, _vp, _i, _vp]),
+    "ojasx_b200_moe_forward_routed": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
+    "ojasx_b200_kvq_create": (_vp, [_i, _i, _i, _i, _i, _i, _vp, _vp]),
+    "ojasx_b200_kvq_load": (_i, [_vp, _vp, _vp, _i]),
+    "ojasx_b200_kvq_read": (_i, [_vp, _vp, _vp, _i, _i]),
+    "ojasx_b200_kvq_seq_len": (_i, [_vp]),
+    "ojasx_b200_kvq_reset": (_i, [_vp]),
+    "ojasx_b200_kvq_append": (_i, [_vp, _vp, _vp, _i, _vp]),
+    "ojasx_b200_kvq_decode": (_i, [_vp, _vp, _vp, _f, _i, _vp]),
+    "ojasx_b200_kvq_destroy": (None, [_vp]),
 }
 
 _lib = None

@@ -51,6 +51,49 @@ struct LinearProblem {
     int item_begin;           // first global work item of this problem (grouped launches)
 };
 
+// Top-k MoE over VQ experts (layout of SplitManifoldMoE, ojasx_lut.h:156-242).  Device pointers.
+struct MoeProblem {
+    const void* x;            // [n_tokens, H] io dtype
+    void* y;                  // [n_tokens, H] io dtype
+    const int* topk_idx;      // [n_tokens, k_active] global expert ids
+    const float* topk_w;      // [n_tokens, k_active]
+    const float* cb_in;       // [Kcb, D] shared by every expert's gate/up
+    const float* cb_down;     // [Kcb, D]
+    const uint8_t* gu_codes;  // [E, 2I, G]  gate rows [0,I) then up rows [I,2I)
+    const float* gu_scales;   // [E, 2I] or null
+    const uint8_t* dn_codes;  // [E, H, Gi]
+    const float* dn_scales;   // [E, H] or null
+    CsrView gu_csr;           // rows of the flattened [E*2I, H] matrix
+    CsrView dn_csr;           // rows of the flattened [E*H, I] matrix
+    float* inter;             // scratch [pairs, I]
+    float* expert_out;        // scratch [pairs, H]
+    int n_tokens, k_active;
+    int E;                    // experts held by this handle
+    int expert_offset;        // global id of local expert 0 (expert-parallel shards)
+    int H, I, G, Gi, D, Kcb;
+    int io_dtype;
+    int gu_tile, gu_tiles, dn_tile, dn_tiles;
+};
+
+// Codebook-VQ KV cache of one layer.  Device pointers.
+struct KvqProblem {
+    const void* q;          // [B, Hq, head_dim] io dtype (decode)
+    void* out;              // [B, Hq, head_dim] io dtype (decode)
+    const void* new_k;      // [B, Hkv, head_dim] io dtype (append)
+    const void* new_v;
+    uint8_t* k_codes;       // [B, Hkv, max_seq, G]
+    uint8_t* v_codes;
+    const float* k_cb;      // [Hkv, Kcb, D]
+    const float* v_cb;
+    int* seq_lens;          // [B] tokens cached per sequence
+    int* error_flag;        // set to 1 when an append found the cache full
+    float* partials;        // scratch [B, Hkv, n_chunks, R, head_dim + 2]
+    int B, Hkv, Hq, head_dim, D, G, Kcb, max_seq;
+    int chunk, n_chunks;
+    int io_dtype;
+    float scale;
+};
+
 inline int round_up(int a, int b) { return (a + b - 1) / b * b; }
 
 #define OJX_CUDA_TRY(expr)                                   \

@@ -52,4 +52,68 @@ struct LinearGroup {
     int bound_dtype = -1;
 };
 
+struct MoeHandle {
+    int dev = 0;
+    int E = 0;            // experts held here
+    int E_total = 0;      // experts the router scores (== E unless sharded)
+    int expert_offset = 0;
+    int H = 0, I = 0, top_k = 0, D = 0;
+    float* cb_in = nullptr;
+    float* cb_down = nullptr;
+    uint8_t* gu_codes = nullptr;
+    float* gu_scales = nullptr;
+    uint8_t* dn_codes = nullptr;
+    float* dn_scales = nullptr;
+    int* csr_rp[2] = {nullptr, nullptr};     // 0 gate_up, 1 down
+    int* csr_cols[2] = {nullptr, nullptr};
+    float* csr_vals[2] = {nullptr, nullptr};
+    int csr_nnz[2] = {0, 0};
+    float* router = nullptr;                 // [E_total, H]
+    void* scratch = nullptr;                 // inter [pairs, I] + expert_out [pairs, H]
+    size_t scratch_cap = 0;
+    void* route_scratch = nullptr;           // logits, probs [tokens, E_total], idx, w [pairs]
+    size_t route_cap = 0;
+    void* stage = nullptr;                   // host-pointer forward staging
+    size_t stage_cap = 0;
+    cudaStream_t stream = nullptr;
+
+    ~MoeHandle();
+    int reserve(int n_tokens, int k);
+    MoeProblem problem(const void* x, void* y, const int* idx, const float* w, int n_tokens, int k, int io) const;
+};
+
+struct KvqHandle {
+    int dev = 0;
+    int B = 0, Hkv = 0, Hq = 0, head_dim = 0, D = 0, G = 0, max_seq = 0;
+    int host_len = 0;                        // host mirror of the (uniform) cached length
+    uint8_t* k_codes = nullptr;
+    uint8_t* v_codes = nullptr;
+    float* k_cb = nullptr;
+    float* v_cb = nullptr;
+    int* seq_lens = nullptr;
+    int* error_flag = nullptr;
+    void* partials = nullptr;
+    size_t partials_cap = 0;
+    ~KvqHandle();
+};
+
+struct LegacyKvHandle {
+    struct Head {
+        uint8_t* k_codes = nullptr;
+        uint8_t* v_codes = nullptr;
+        float* k_scales = nullptr;
+        float* v_scales = nullptr;
+        int len = 0, cap = 0;
+    };
+    int dev = 0;
+    int num_heads = 0, head_dim = 0, D = 0, G = 0, initial_cap = 0;
+    std::vector<Head> heads;
+    void* stage = nullptr;    // q | k,v | out
+    size_t stage_cap = 0;
+    void* logits = nullptr;
+    size_t logits_cap = 0;
+    cudaStream_t stream = nullptr;
+    ~LegacyKvHandle();
+};
+
 }  // namespace ojx

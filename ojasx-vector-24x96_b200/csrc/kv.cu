@@ -1,0 +1,398 @@
+// Quantized KV cache kernels.
+//
+// (1) Codebook-VQ cache ("kvq"): every head vector is stored as head_dim/block_dim uint8 codes
+//     into a per-KV-head codebook.  Append = nearest centroid per sub-vector (rule of
+//     ojasx_24x96/codec.py:217-224); decode = per-head query table LUT[g, code] = <q_g, C_k[code]>,
+//     logit[t] = scale * sum_g LUT[g, k_code[t,g]] (structure of
+//     split_manifold_lut_experiment/native/src/ojasx_lut_kv_cache.cpp:86-107), online softmax
+//     over context chunks (ojasx_24x96/long_context.py:92-176) and value gather
+//     out = sum_t p_t * C_v[v_code[t,g]].  The query heads that share a KV head (GQA) are
+//     scored from one read of the code stream.
+// (2) The reference's cache as shipped ("legacy"): int8 of each block's first coordinate with a
+//     per-token abs-max scale (ojasx_lut_kv_cache.cpp:16-132, softmax of
+//     ojasx_lut_c_api.cpp:178-191).
+#include "common.cuh"
+#include "launch.h"
+#include "handles.h"
+
+namespace ojx {
+
+constexpr int kKvThreads = 256;
+constexpr int kKvMaxRep = 8;      // query heads per KV head
+constexpr int kKvMaxGroups = 32;  // head_dim / block_dim
+constexpr int kKvMaxD = 16;
+
+__device__ __forceinline__ float load_io(const void* p, size_t i, int dtype) {
+    return dtype == OJX_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i])
+                             : reinterpret_cast<const float*>(p)[i];
+}
+
+// ------------------------------------------------------------------------------ kvq append
+// One CTA per sequence.  Task = (k|v, kv head, group); one warp per task scans the 256
+// centroids.  dist = (|v|^2 - 2 v.c) + |c|^2 with every dot product a sequential fp32 sum
+// (separate multiply and add); arg-min takes the first minimum.
+__global__ void __launch_bounds__(kKvThreads) kvq_append_kernel(const __grid_constant__ KvqProblem P) {
+    const int b = blockIdx.x;
+    const int T = P.seq_lens[b];
+    if (T >= P.max_seq) {
+        if (threadIdx.x == 0) atomicExch(P.error_flag, 1);
+        return;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int D = P.D, G = P.G, hd = P.head_dim;
+    const int tasks = 2 * P.Hkv * G;
+    for (int task = warp; task < tasks; task += nwarps) {
+        const int which = task / (P.Hkv * G);
+        const int rem = task - which * P.Hkv * G;
+        const int h = rem / G, g = rem - h * G;
+        const void* src = which ? P.new_v : P.new_k;
+        const float* cb = (which ? P.v_cb : P.k_cb) + (size_t)h * P.Kcb * D;
+        float v[kKvMaxD];
+        float vv = 0.0f;
+        for (int d = 0; d < D; ++d) {
+            v[d] = load_io(src, ((size_t)b * P.Hkv + h) * hd + g * D + d, P.io_dtype);
+            vv = __fadd_rn(vv, __fmul_rn(v[d], v[d]));
+        }
+        float bd = INFINITY;
+        int bi = 0x7fffffff;
+        for (int c = lane; c < P.Kcb; c += 32) {
+            const float* cv = cb + (size_t)c * D;
+            float vc = 0.0f, cc = 0.0f;
+            for (int d = 0; d < D; ++d) vc = __fadd_rn(vc, __fmul_rn(v[d], cv[d]));
+            for (int d = 0; d < D; ++d) cc = __fadd_rn(cc, __fmul_rn(cv[d], cv[d]));
+            const float dist = __fadd_rn(__fsub_rn(vv, __fmul_rn(2.0f, vc)), cc);
+            if (dist < bd) { bd = dist; bi = c; }
+        }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            const float od = __shfl_xor_sync(0xffffffffu, bd, off);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+            if (od < bd || (od == bd && oi < bi)) { bd = od; bi = oi; }
+        }
+        if (lane == 0) {
+            uint8_t* codes = which ? P.v_codes : P.k_codes;
+            codes[(((size_t)b * P.Hkv + h) * P.max_seq + T) * G + g] = (uint8_t)bi;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) P.seq_lens[b] = T + 1;
+}
+
+// ------------------------------------------------------------------------------ kvq decode
+// grid = (chunks, Hkv, B).  Shared memory: query table [G,256,R] fp32, value codebook [256,D],
+// the chunk's scores/probabilities [chunk, R] and its value codes [chunk, G].
+template <int R>
+__global__ void __launch_bounds__(kKvThreads) kvq_decode_kernel(const __grid_constant__ KvqProblem P) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int G = P.G, D = P.D, hd = P.head_dim, tid = threadIdx.x;
+    float* lut = reinterpret_cast<float*>(smem_raw);               // [G*256*R]
+    float* vcb = lut + (size_t)G * 256 * R;                        // [256*D]
+    float* sc = vcb + 256 * D;                                     // [chunk*R]
+    float* red = sc + (size_t)P.chunk * R;                         // [kKvThreads]
+    float* osum = red + kKvThreads;                                // [2][R*hd] partial outputs of the two token halves
+    uint8_t* vcs = reinterpret_cast<uint8_t*>(osum + 2 * R * hd);  // [chunk*G]
+
+    const int b = blockIdx.z, h = blockIdx.y, ch = blockIdx.x;
+    const int T = P.seq_lens[b];
+    const int t0 = ch * P.chunk;
+    const int n = min(P.chunk, T - t0);
+    float* part = P.partials + ((((size_t)b * P.Hkv + h) * P.n_chunks + ch) * R) * (hd + 2);
+    if (n <= 0) {  // chunk beyond this sequence: neutral partial
+        for (int i = tid; i < R * (hd + 2); i += blockDim.x) {
+            const int w = i % (hd + 2);
+            part[i] = w == 0 ? -INFINITY : 0.0f;
+        }
+        return;
+    }
+    const uint8_t* kc = P.k_codes + (((size_t)b * P.Hkv + h) * P.max_seq + t0) * G;
+    const uint8_t* vc = P.v_codes + (((size_t)b * P.Hkv + h) * P.max_seq + t0) * G;
+
+    // query table: thread c owns centroid c
+    {
+        const float* kcb = P.k_cb + ((size_t)h * P.Kcb + (tid < P.Kcb ? tid : 0)) * D;
+        float c[kKvMaxD];
+        for (int d = 0; d < D; ++d) c[d] = tid < P.Kcb ? kcb[d] : 0.0f;
+        for (int r = 0; r < R; ++r) {
+            const size_t qoff = ((size_t)b * P.Hq + (size_t)h * R + r) * hd;
+            for (int g = 0; g < G; ++g) {
+                float dot = 0.0f;
+                for (int d = 0; d < D; ++d) dot = fmaf(load_io(P.q, qoff + g * D + d, P.io_dtype), c[d], dot);
+                lut[((size_t)g * 256 + tid) * R + r] = dot;
+            }
+        }
+        for (int i = tid; i < 256 * D; i += blockDim.x) vcb[i] = i < P.Kcb * D ? P.v_cb[(size_t)h * P.Kcb * D + i] : 0.0f;
+        for (int i = tid; i < n * G; i += blockDim.x) vcs[i] = vc[i];
+    }
+    __syncthreads();
+
+    // scores: one thread per token, R heads at once
+    float mloc[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) mloc[r] = -INFINITY;
+    for (int t = tid; t < n; t += blockDim.x) {
+        float acc[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) acc[r] = 0.0f;
+        const uint8_t* row = kc + (size_t)t * G;
+        for (int g = 0; g < G; ++g) {
+            const float* e = lut + ((size_t)g * 256 + row[g]) * R;
+#pragma unroll
+            for (int r = 0; r < R; ++r) acc[r] += e[r];
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const float s = acc[r] * P.scale;
+            sc[(size_t)t * R + r] = s;
+            mloc[r] = fmaxf(mloc[r], s);
+        }
+    }
+    // chunk max and normaliser per head (fixed-shape tree: deterministic)
+    float mch[R], lch[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        red[tid] = mloc[r];
+        __syncthreads();
+        for (int s = blockDim.x / 2; s > 0; s >>= 1) {
+            if (tid < s) red[tid] = fmaxf(red[tid], red[tid + s]);
+            __syncthreads();
+        }
+        mch[r] = red[0];
+        __syncthreads();
+    }
+    float lloc[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) lloc[r] = 0.0f;
+    for (int t = tid; t < n; t += blockDim.x) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const float p = __expf(sc[(size_t)t * R + r] - mch[r]);
+            sc[(size_t)t * R + r] = p;
+            lloc[r] += p;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        red[tid] = lloc[r];
+        __syncthreads();
+        for (int s = blockDim.x / 2; s > 0; s >>= 1) {
+            if (tid < s) red[tid] += red[tid + s];
+            __syncthreads();
+        }
+        lch[r] = red[0];
+        __syncthreads();
+    }
+
+    // values: thread = (token half, output column); R accumulators
+    {
+        const int col = tid % hd, half = tid / hd, halves = blockDim.x / hd;  // blockDim.x is a multiple of hd
+        const int g = col / D, d = col - g * D;
+        float o[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) o[r] = 0.0f;
+        if (half < halves) {
+            for (int t = half; t < n; t += halves) {
+                const float v = vcb[(int)vcs[(size_t)t * G + g] * D + d];
+#pragma unroll
+                for (int r = 0; r < R; ++r) o[r] = fmaf(sc[(size_t)t * R + r], v, o[r]);
+            }
+        }
+        // combine the token halves in a fixed order
+        for (int hh = 0; hh < halves; ++hh) {
+            if (half == hh) {
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    float* dst = osum + (size_t)r * hd + col;
+                    *dst = hh == 0 ? o[r] : *dst + o[r];
+                }
+            }
+            __syncthreads();
+        }
+    }
+    for (int i = tid; i < R * hd; i += blockDim.x) {
+        const int r = i / hd, c = i - r * hd;
+        part[(size_t)r * (hd + 2) + 2 + c] = osum[i];
+    }
+    if (tid < R) {
+        part[(size_t)tid * (hd + 2) + 0] = mch[tid];
+        part[(size_t)tid * (hd + 2) + 1] = lch[tid];
+    }
+}
+
+// Merge the chunk partials of one (sequence, query head): M = max m_c, weights exp(m_c - M).
+__global__ void kvq_combine_kernel(const __grid_constant__ KvqProblem P, int R) {
+    const int b = blockIdx.y, qh = blockIdx.x, hd = P.head_dim;
+    const int h = qh / R, r = qh - h * R;
+    const float* base = P.partials + (((size_t)b * P.Hkv + h) * P.n_chunks) * R * (hd + 2);
+    float M = -INFINITY;
+    for (int c = 0; c < P.n_chunks; ++c) M = fmaxf(M, base[((size_t)c * R + r) * (hd + 2)]);
+    float L = 0.0f;
+    for (int c = 0; c < P.n_chunks; ++c) {
+        const float* p = base + ((size_t)c * R + r) * (hd + 2);
+        if (p[0] != -INFINITY) L += p[1] * __expf(p[0] - M);
+    }
+    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+    for (int col = threadIdx.x; col < hd; col += blockDim.x) {
+        float o = 0.0f;
+        for (int c = 0; c < P.n_chunks; ++c) {
+            const float* p = base + ((size_t)c * R + r) * (hd + 2);
+            if (p[0] != -INFINITY) o = fmaf(p[2 + col], __expf(p[0] - M), o);
+        }
+        o *= inv;
+        const size_t oi = ((size_t)b * P.Hq + qh) * hd + col;
+        if (P.io_dtype == OJX_BF16) reinterpret_cast<__nv_bfloat16*>(P.out)[oi] = __float2bfloat16_rn(o);
+        else reinterpret_cast<float*>(P.out)[oi] = o;
+    }
+}
+
+size_t kvq_decode_smem(const KvqProblem& P, int R) {
+    return sizeof(float) * ((size_t)P.G * 256 * R + 256 * (size_t)P.D + (size_t)P.chunk * R + kKvThreads +
+                            2 * (size_t)R * P.head_dim) + (size_t)P.chunk * P.G;
+}
+
+int launch_kvq_append(const KvqProblem& P, cudaStream_t s) {
+    if (!P.new_k || !P.new_v || !P.k_codes || !P.v_codes || !P.seq_lens) return OJX_ERR_ARG;
+    if (P.D > kKvMaxD || P.G > kKvMaxGroups) return OJX_ERR_UNSUPPORTED;
+    kvq_append_kernel<<<P.B, kKvThreads, 0, s>>>(P);
+    OJX_CUDA_TRY(cudaGetLastError());
+    count_launch(1);
+    return OJX_OK;
+}
+
+template <int R>
+static int launch_decode_t(const KvqProblem& P, cudaStream_t s) {
+    const size_t smem = kvq_decode_smem(P, R);
+    if (smem > 227 * 1024) return OJX_ERR_TOO_LARGE;
+    OJX_CUDA_TRY(cudaFuncSetAttribute(kvq_decode_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kvq_decode_kernel<R><<<dim3(P.n_chunks, P.Hkv, P.B), kKvThreads, smem, s>>>(P);
+    OJX_CUDA_TRY(cudaGetLastError());
+    kvq_combine_kernel<<<dim3(P.Hq, P.B), 128, 0, s>>>(P, R);
+    OJX_CUDA_TRY(cudaGetLastError());
+    count_launch(2);
+    return OJX_OK;
+}
+
+int launch_kvq_decode(const KvqProblem& P, cudaStream_t s) {
+    if (!P.q || !P.out || !P.partials || !P.seq_lens) return OJX_ERR_ARG;
+    if (P.D > kKvMaxD || P.G > kKvMaxGroups || P.Hq % P.Hkv != 0) return OJX_ERR_UNSUPPORTED;
+    if (P.head_dim > kKvThreads || kKvThreads % P.head_dim != 0) return OJX_ERR_UNSUPPORTED;
+    switch (P.Hq / P.Hkv) {
+        case 1: return launch_decode_t<1>(P, s);
+        case 2: return launch_decode_t<2>(P, s);
+        case 4: return launch_decode_t<4>(P, s);
+        case 8: return launch_decode_t<8>(P, s);
+        default: return OJX_ERR_UNSUPPORTED;
+    }
+}
+
+// ------------------------------------------------------------------------------ legacy cache
+// ojasx_lut_kv_cache.cpp:16-65 for one head: abs-max scale, then per block the first coordinate
+// as round(val/scale) clamped to [-128,127], stored +128.
+__global__ void legacy_append_kernel(const float* __restrict__ k, const float* __restrict__ v, int head_dim,
+                                     int block_dim, uint8_t* k_row, uint8_t* v_row, float* k_scale, float* v_scale) {
+    __shared__ float red[128];
+    const int G = head_dim / block_dim;
+    for (int which = 0; which < 2; ++which) {
+        const float* src = which ? v : k;
+        float m = 1e-8f;
+        for (int d = threadIdx.x; d < head_dim; d += blockDim.x) m = fmaxf(m, fabsf(src[d]));
+        red[threadIdx.x] = m;
+        __syncthreads();
+        for (int s = blockDim.x / 2; s > 0; s >>= 1) {
+            if (threadIdx.x < s) red[threadIdx.x] = fmaxf(red[threadIdx.x], red[threadIdx.x + s]);
+            __syncthreads();
+        }
+        const float scale = __fdiv_rn(red[0], 127.0f);
+        __syncthreads();
+        if (threadIdx.x == 0) *(which ? v_scale : k_scale) = scale;
+        for (int g = threadIdx.x; g < G; g += blockDim.x) {
+            int q = (int)roundf(__fdiv_rn(src[g * block_dim], scale));
+            q = max(-128, min(127, q));
+            (which ? v_row : k_row)[g] = (uint8_t)(q + 128);
+        }
+    }
+}
+
+// Attention of one head over T cached tokens (ojasx_lut_kv_cache.cpp:67-132 and the softmax of
+// ojasx_lut_c_api.cpp:178-191), one CTA.  logits live in global scratch [T].
+__global__ void __launch_bounds__(256) legacy_attention_kernel(const float* __restrict__ q, int head_dim, int block_dim, int T,
+                                                               const uint8_t* __restrict__ k_codes,
+                                                               const uint8_t* __restrict__ v_codes,
+                                                               const float* __restrict__ k_scales,
+                                                               const float* __restrict__ v_scales, float scale_factor,
+                                                               float* __restrict__ logits, float* __restrict__ out) {
+    extern __shared__ float lut[];  // [G*256]
+    __shared__ float red[256];
+    const int G = head_dim / block_dim, tid = threadIdx.x;
+    if (scale_factor <= 0.0f) scale_factor = __fdiv_rn(1.0f, sqrtf((float)head_dim));
+    for (int i = tid; i < G * 256; i += blockDim.x) lut[i] = __fmul_rn(q[(i >> 8) * block_dim], (float)((i & 255) - 128));
+    __syncthreads();
+    float m = -INFINITY;
+    for (int t = tid; t < T; t += blockDim.x) {
+        float s = 0.0f;
+        for (int g = 0; g < G; ++g) s = __fadd_rn(s, lut[g * 256 + k_codes[(size_t)t * G + g]]);
+        const float l = __fmul_rn(__fmul_rn(s, k_scales[t]), scale_factor);
+        logits[t] = l;
+        m = fmaxf(m, l);
+    }
+    red[tid] = m;
+    __syncthreads();
+    for (int s = blockDim.x / 2; s > 0; s >>= 1) {
+        if (tid < s) red[tid] = fmaxf(red[tid], red[tid + s]);
+        __syncthreads();
+    }
+    m = red[0];
+    __syncthreads();
+    float sum = 0.0f;
+    for (int t = tid; t < T; t += blockDim.x) {
+        const float e = (float)exp((double)__fsub_rn(logits[t], m));
+        logits[t] = e;
+        sum += e;
+    }
+    red[tid] = sum;
+    __syncthreads();
+    for (int s = blockDim.x / 2; s > 0; s >>= 1) {
+        if (tid < s) red[tid] += red[tid + s];
+        __syncthreads();
+    }
+    const float inv = __fdiv_rn(1.0f, red[0]);
+    __syncthreads();
+    for (int d = tid; d < head_dim; d += blockDim.x) out[d] = 0.0f;
+    __syncthreads();
+    // context: warp per group, lanes over tokens, fixed-shape shuffle reduction
+    const int warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
+    for (int g = warp; g < G; g += nw) {
+        float acc = 0.0f;
+        for (int t = lane; t < T; t += 32) {
+            const float w = __fmul_rn(__fmul_rn(logits[t], inv), v_scales[t]);
+            acc += (float)((int)v_codes[(size_t)t * G + g] - 128) * w;
+        }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+        if (lane == 0) out[g * block_dim] = acc;
+    }
+}
+
+int launch_legacy_append(const float* k, const float* v, int head_dim, int block_dim, uint8_t* k_row, uint8_t* v_row,
+                         float* k_scale, float* v_scale, cudaStream_t s) {
+    legacy_append_kernel<<<1, 128, 0, s>>>(k, v, head_dim, block_dim, k_row, v_row, k_scale, v_scale);
+    OJX_CUDA_TRY(cudaGetLastError());
+    count_launch(1);
+    return OJX_OK;
+}
+
+int launch_legacy_attention(const float* q, int head_dim, int block_dim, int T, const uint8_t* k_codes,
+                            const uint8_t* v_codes, const float* k_scales, const float* v_scales, float scale_factor,
+                            float* logits, float* out, cudaStream_t s) {
+    const int G = head_dim / block_dim;
+    if (G > 128) return OJX_ERR_UNSUPPORTED;
+    const size_t smem = sizeof(float) * (size_t)G * 256;
+    if (smem > 48 * 1024)
+        OJX_CUDA_TRY(cudaFuncSetAttribute(legacy_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    legacy_attention_kernel<<<1, 256, smem, s>>>(q, head_dim, block_dim, T, k_codes, v_codes, k_scales, v_scales,
+                                                 scale_factor, logits, out);
+    OJX_CUDA_TRY(cudaGetLastError());
+    count_launch(1);
+    return OJX_OK;
+}
+
+}  // namespace ojx

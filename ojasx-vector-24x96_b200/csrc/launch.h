@@ -10,4 +10,19 @@ int validate_linear(const LinearProblem& P);
 int launch_linear(LinearProblem P, cudaStream_t stream);
 int launch_linear_group(const LinearProblem* d_probs, int nprobs, int total_items, int D, cudaStream_t stream);
 
+// --- moe.cu
+int launch_moe_experts(MoeProblem P, cudaStream_t stream);
+int launch_moe_router(const float* Wr, const void* x, int io_dtype, int n_tokens, int H, int E, int k,
+                      float* logits, float* probs, int* idx_out, float* w_out, cudaStream_t stream);
+
+// --- kv.cu
+size_t kvq_decode_smem(const KvqProblem& P, int R);
+int launch_kvq_append(const KvqProblem& P, cudaStream_t stream);
+int launch_kvq_decode(const KvqProblem& P, cudaStream_t stream);
+int launch_legacy_append(const float* k, const float* v, int head_dim, int block_dim, uint8_t* k_row, uint8_t* v_row,
+                         float* k_scale, float* v_scale, cudaStream_t stream);
+int launch_legacy_attention(const float* q, int head_dim, int block_dim, int T, const uint8_t* k_codes,
+                            const uint8_t* v_codes, const float* k_scales, const float* v_scales, float scale_factor,
+                            float* logits, float* out, cudaStream_t stream);
+
 }  // namespace ojx

@@ -1,0 +1,278 @@
+// Top-k MoE over VQ-coded experts: only the routed experts' code rows are read.
+// Replaces SplitManifoldMoE::forward_cpu
+// (split_manifold_lut_experiment/native/src/ojasx_lut_cpu.cpp:213-365) and adds the router of
+// split_manifold_lut_experiment/tools/run_full_48_layers_and_generate.py:172-175.
+//
+// Stages (all on one stream, no host round trip):
+//   router   : logits -> softmax -> top-k -> renormalise           (moe_router_*)
+//   gate/up  : per (token, expert) pair and tile of intermediate indices, one table pass over
+//              the expert's gate rows and up rows, then inter = silu(gate) * up
+//   down     : per pair and tile of hidden rows, table of `inter` against the down codebook
+//   combine  : y[t] = sum over the token's pairs in caller order of expert_out * weight
+// The combine is a separate ordered pass so that the sum over experts has the reference's
+// order whatever SM finished first.
+#include "lut_core.cuh"
+#include "launch.h"
+#include "handles.h"
+
+namespace ojx {
+
+// silu(v) = v / (1 + exp(-v))  (ojasx_lut_cpu.cpp:209-211).  exp is evaluated in double and
+// rounded once, which reproduces a correctly rounded expf in all but ~1e-9 of arguments.
+__device__ __forceinline__ float silu_ref(float v) {
+    const float e = (float)exp((double)(-v));
+    return __fdiv_rn(v, __fadd_rn(1.0f, e));
+}
+
+struct MoePair {
+    int token, expert;  // expert is the LOCAL expert index, or -1 when the pair is skipped
+};
+
+__device__ __forceinline__ MoePair decode_pair(const MoeProblem& P, int pair) {
+    MoePair r;
+    r.token = pair / P.k_active;
+    const int e = P.topk_idx[pair] - P.expert_offset;
+    const float w = P.topk_w[pair];
+    // ojasx_lut_cpu.cpp:284-286: ids outside the expert table and |w| < 1e-8 are skipped.
+    r.expert = (e < 0 || e >= P.E || fabsf(w) < 1e-8f) ? -1 : e;
+    return r;
+}
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1) moe_gate_up_kernel(const __grid_constant__ MoeProblem P) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    CoreSmem& sm = *reinterpret_cast<CoreSmem*>(smem_raw);
+    const int total = P.n_tokens * P.k_active * P.gu_tiles;
+    const size_t esz = P.io_dtype == OJX_BF16 ? 2 : 4;
+    for (int item = blockIdx.x; item < total; item += gridDim.x) {
+        const int pair = item / P.gu_tiles, tile = item - pair * P.gu_tiles;
+        const MoePair pr = decode_pair(P, pair);
+        if (pr.expert < 0) continue;  // uniform across the CTA
+        const int i0 = tile * P.gu_tile, n = min(P.gu_tile, P.I - i0);
+        const size_t row0 = (size_t)pr.expert * 2 * P.I;
+        RowSet rs;
+        rs.base0 = P.gu_codes + (row0 + i0) * P.G;
+        rs.base1 = P.gu_codes + (row0 + P.I + i0) * P.G;
+        rs.n0 = n;
+        rs.n = 2 * n;
+        rs.G = P.G;
+        rs.aligned = ((P.G & 15) == 0) && ((reinterpret_cast<uintptr_t>(P.gu_codes) & 15) == 0);
+        const XLoad xl{static_cast<const char*>(P.x) + (size_t)pr.token * P.H * esz, P.H, P.io_dtype};
+        RowWalker<D> walker(sm, rs);
+        if (walker.nslices == 0)
+            for (int lr = threadIdx.x; lr < 2 * n; lr += kThreads) sm.acc[lr] = 0.0f;
+        walker.run(xl, P.cb_in, P.Kcb);
+        __syncthreads();
+        for (int lr = threadIdx.x; lr < n; lr += kThreads) {
+            const size_t rg = row0 + i0 + lr, ru = row0 + P.I + i0 + lr;
+            float gate = sm.acc[lr], up = sm.acc[n + lr];
+            if (P.gu_scales) { gate = __fmul_rn(gate, P.gu_scales[rg]); up = __fmul_rn(up, P.gu_scales[ru]); }
+            if (P.gu_csr.nnz > 0) {
+                gate = __fadd_rn(gate, csr_row_sum(P.gu_csr, (int)rg, xl));
+                up = __fadd_rn(up, csr_row_sum(P.gu_csr, (int)ru, xl));
+            }
+            P.inter[(size_t)pair * P.I + i0 + lr] = __fmul_rn(silu_ref(gate), up);
+        }
+        __syncthreads();
+    }
+}
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1) moe_down_kernel(const __grid_constant__ MoeProblem P) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    CoreSmem& sm = *reinterpret_cast<CoreSmem*>(smem_raw);
+    const int total = P.n_tokens * P.k_active * P.dn_tiles;
+    for (int item = blockIdx.x; item < total; item += gridDim.x) {
+        const int pair = item / P.dn_tiles, tile = item - pair * P.dn_tiles;
+        const MoePair pr = decode_pair(P, pair);
+        if (pr.expert < 0) continue;
+        const int h0 = tile * P.dn_tile, n = min(P.dn_tile, P.H - h0);
+        const size_t row0 = (size_t)pr.expert * P.H;
+        RowSet rs;
+        rs.base0 = P.dn_codes + (row0 + h0) * P.Gi;
+        rs.base1 = rs.base0;
+        rs.n0 = n;
+        rs.n = n;
+        rs.G = P.Gi;
+        rs.aligned = ((P.Gi & 15) == 0) && ((reinterpret_cast<uintptr_t>(P.dn_codes) & 15) == 0);
+        const XLoad xl{P.inter + (size_t)pair * P.I, P.I, OJX_F32};
+        RowWalker<D> walker(sm, rs);
+        if (walker.nslices == 0)
+            for (int lr = threadIdx.x; lr < n; lr += kThreads) sm.acc[lr] = 0.0f;
+        walker.run(xl, P.cb_down, P.Kcb);
+        __syncthreads();
+        for (int lr = threadIdx.x; lr < n; lr += kThreads) {
+            const size_t r = row0 + h0 + lr;
+            float v = sm.acc[lr];
+            if (P.dn_scales) v = __fmul_rn(v, P.dn_scales[r]);
+            if (P.dn_csr.nnz > 0) v = __fadd_rn(v, csr_row_sum(P.dn_csr, (int)r, xl));
+            P.expert_out[(size_t)pair * P.H + h0 + lr] = v;
+        }
+        __syncthreads();
+    }
+}
+
+// y[t,h] = sum_k expert_out[t*k+k', h] * w  in caller order (ojasx_lut_cpu.cpp:361-362).
+__global__ void moe_combine_kernel(const __grid_constant__ MoeProblem P) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= P.n_tokens * P.H) return;
+    const int t = idx / P.H, h = idx - t * P.H;
+    float y = 0.0f;
+    for (int k = 0; k < P.k_active; ++k) {
+        const int pair = t * P.k_active + k;
+        if (decode_pair(P, pair).expert < 0) continue;
+        y = __fadd_rn(y, __fmul_rn(P.expert_out[(size_t)pair * P.H + h], P.topk_w[pair]));
+    }
+    if (P.io_dtype == OJX_BF16) reinterpret_cast<__nv_bfloat16*>(P.y)[idx] = __float2bfloat16_rn(y);
+    else reinterpret_cast<float*>(P.y)[idx] = y;
+}
+
+// ------------------------------------------------------------------------------- router
+// logit[t,e] with 32 interleaved partial sums and a butterfly combine: lane j owns columns
+// j, j+32, ... in ascending order (separate multiply and add), then v += shfl_xor(v, off) for
+// off = 16..1.  One warp per expert (its row of W stays hot in L1 while the warp loops over the
+// tokens of its blockIdx.y stripe).
+
+__global__ void __launch_bounds__(256) moe_router_logits_kernel(const float* __restrict__ Wr, const void* __restrict__ x,
+                                                                int io_dtype, int n_tokens, int H, int E,
+                                                                float* __restrict__ logits) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= E) return;
+    const float* w = Wr + (size_t)warp * H;
+    const size_t esz = io_dtype == OJX_BF16 ? 2 : 4;
+    for (int t = blockIdx.y; t < n_tokens; t += gridDim.y) {
+        const XLoad xl{static_cast<const char*>(x) + (size_t)t * H * esz, H, io_dtype};
+        float part = 0.0f;
+        for (int c = lane; c < H; c += 32) part = __fadd_rn(part, __fmul_rn(w[c], xl(c)));
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, off));
+        if (lane == 0) logits[(size_t)t * E + warp] = part;
+    }
+}
+
+// One CTA per token: softmax over E logits, k rounds of arg-max (ties to the lower index),
+// renormalise.  The normaliser and the weight sum are accumulated sequentially in fp32 so the
+// result does not depend on the thread count.
+__global__ void __launch_bounds__(256) moe_router_topk_kernel(const float* __restrict__ logits, int E, int k,
+                                                              int* __restrict__ idx_out, float* __restrict__ w_out,
+                                                              float* __restrict__ probs /* [n_tokens, E] scratch */) {
+    __shared__ float red_v[256];
+    __shared__ int red_i[256];
+    __shared__ float s_bcast;
+    const int t = blockIdx.x, tid = threadIdx.x;
+    const float* l = logits + (size_t)t * E;
+    float* p = probs + (size_t)t * E;
+    float m = -INFINITY;
+    for (int e = tid; e < E; e += blockDim.x) m = fmaxf(m, l[e]);
+    red_v[tid] = m;
+    __syncthreads();
+    for (int s = blockDim.x / 2; s > 0; s >>= 1) {
+        if (tid < s) red_v[tid] = fmaxf(red_v[tid], red_v[tid + s]);
+        __syncthreads();
+    }
+    m = red_v[0];
+    __syncthreads();
+    for (int e = tid; e < E; e += blockDim.x) p[e] = (float)exp((double)__fsub_rn(l[e], m));
+    __syncthreads();
+    if (tid == 0) {
+        float s = 0.0f;
+        for (int e = 0; e < E; ++e) s = __fadd_rn(s, p[e]);
+        s_bcast = s;
+    }
+    __syncthreads();
+    const float s = s_bcast;
+    for (int e = tid; e < E; e += blockDim.x) p[e] = __fdiv_rn(p[e], s);
+    __syncthreads();
+    for (int r = 0; r < k; ++r) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = tid; e < E; e += blockDim.x) {
+            const float v = p[e];
+            if (v > bv) { bv = v; bi = e; }  // ascending e per thread keeps the lowest index on ties
+        }
+        red_v[tid] = bv;
+        red_i[tid] = bi;
+        __syncthreads();
+        for (int st = blockDim.x / 2; st > 0; st >>= 1) {
+            if (tid < st) {
+                const float ov = red_v[tid + st];
+                const int oi = red_i[tid + st];
+                if (ov > red_v[tid] || (ov == red_v[tid] && oi < red_i[tid])) { red_v[tid] = ov; red_i[tid] = oi; }
+            }
+            __syncthreads();
+        }
+        if (tid == 0) {
+            idx_out[(size_t)t * k + r] = red_i[0];
+            w_out[(size_t)t * k + r] = red_v[0];
+            p[red_i[0]] = -1.0f;  // taken (probabilities are >= 0)
+        }
+        __syncthreads();
+    }
+    if (tid == 0) {
+        float ws = 0.0f;
+        for (int r = 0; r < k; ++r) ws = __fadd_rn(ws, w_out[(size_t)t * k + r]);
+        for (int r = 0; r < k; ++r) w_out[(size_t)t * k + r] = __fdiv_rn(w_out[(size_t)t * k + r], ws);
+    }
+}
+
+// ------------------------------------------------------------------------------- host side
+template <typename K>
+static int set_smem(K kern) {
+    OJX_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(CoreSmem)));
+    return OJX_OK;
+}
+
+template <int D>
+static int launch_moe_experts_t(const MoeProblem& P, cudaStream_t s) {
+    int rc;
+    if ((rc = set_smem(moe_gate_up_kernel<D>)) != OJX_OK) return rc;
+    if ((rc = set_smem(moe_down_kernel<D>)) != OJX_OK) return rc;
+    const int pairs = P.n_tokens * P.k_active, sms = num_sms();
+    const int gu_items = pairs * P.gu_tiles, dn_items = pairs * P.dn_tiles;
+    moe_gate_up_kernel<D><<<gu_items < sms ? gu_items : sms, kThreads, sizeof(CoreSmem), s>>>(P);
+    OJX_CUDA_TRY(cudaGetLastError());
+    moe_down_kernel<D><<<dn_items < sms ? dn_items : sms, kThreads, sizeof(CoreSmem), s>>>(P);
+    OJX_CUDA_TRY(cudaGetLastError());
+    const int n = P.n_tokens * P.H;
+    moe_combine_kernel<<<(n + 255) / 256, 256, 0, s>>>(P);
+    OJX_CUDA_TRY(cudaGetLastError());
+    count_launch(3);
+    return OJX_OK;
+}
+
+int launch_moe_experts(MoeProblem P, cudaStream_t s) {
+    if (!P.x || !P.y || !P.topk_idx || !P.topk_w || !P.inter || !P.expert_out) return OJX_ERR_ARG;
+    if (P.n_tokens <= 0 || P.k_active <= 0) return OJX_ERR_ARG;
+    const int pairs = P.n_tokens * P.k_active, sms = num_sms();
+    // Tiles: spread few pairs over the SMs, keep tiles whole when there are many pairs.
+    int want = (sms + pairs - 1) / pairs;
+    P.gu_tile = round_up((P.I + want - 1) / want, 16);
+    if (P.gu_tile > kAccRows / 2) P.gu_tile = kAccRows / 2;
+    P.gu_tiles = (P.I + P.gu_tile - 1) / P.gu_tile;
+    P.dn_tile = round_up((P.H + want - 1) / want, 32);
+    if (P.dn_tile > kAccRows) P.dn_tile = kAccRows;
+    P.dn_tiles = (P.H + P.dn_tile - 1) / P.dn_tile;
+    switch (P.D) {
+        case 4: return launch_moe_experts_t<4>(P, s);
+        case 8: return launch_moe_experts_t<8>(P, s);
+        case 16: return launch_moe_experts_t<16>(P, s);
+        case 32: return launch_moe_experts_t<32>(P, s);
+        default: return OJX_ERR_UNSUPPORTED;
+    }
+}
+
+int launch_moe_router(const float* Wr, const void* x, int io_dtype, int n_tokens, int H, int E, int k,
+                      float* logits, float* probs, int* idx_out, float* w_out, cudaStream_t s) {
+    if (!Wr || !x || !logits || !probs || !idx_out || !w_out) return OJX_ERR_ARG;
+    if (n_tokens <= 0 || k <= 0 || k > E) return OJX_ERR_ARG;
+    const int warps_per_block = 8;
+    const dim3 lgrid((E + warps_per_block - 1) / warps_per_block, n_tokens < 32 ? n_tokens : 32);
+    moe_router_logits_kernel<<<lgrid, 256, 0, s>>>(Wr, x, io_dtype, n_tokens, H, E, logits);
+    OJX_CUDA_TRY(cudaGetLastError());
+    moe_router_topk_kernel<<<n_tokens, 256, 0, s>>>(logits, E, k, idx_out, w_out, probs);
+    OJX_CUDA_TRY(cudaGetLastError());
+    count_launch(2);
+    return OJX_OK;
+}
+
+}  // namespace ojx

@@ -135,3 +135,156 @@ class VQLinearGroup:
             self.close()
         except Exception:
             pass
+
+
+class VQMoE:
+    """512-expert style top-k MoE layer over VQ-coded experts, resident on the current device.
+
+    ``expert_range=(first, stop)`` keeps only those experts on this device (expert-parallel
+    shard); routed ids outside the range contribute nothing here.
+    """
+
+    def __init__(self, w, expert_range=None):
+        self.hidden, self.inter, self.block_dim = w.hidden, w.inter, w.block_dim
+        self.num_experts_total = w.num_experts
+        e0, e1 = (0, w.num_experts) if expert_range is None else expert_range
+        self.expert_range = (e0, e1)
+        n = e1 - e0
+        args = [np.ascontiguousarray(w.codebook, dtype=np.float32), np.ascontiguousarray(w.down_codebook, dtype=np.float32),
+                np.ascontiguousarray(w.gate_up_codes[e0:e1], dtype=np.uint8),
+                np.ascontiguousarray(w.gate_up_scales[e0:e1], dtype=np.float32),
+                np.ascontiguousarray(w.down_codes[e0:e1], dtype=np.uint8),
+                np.ascontiguousarray(w.down_scales[e0:e1], dtype=np.float32)]
+        self._h = lib().ojasx_create_moe(n, w.hidden, w.inter, 10, w.block_dim, *[_p(a) for a in args])
+        if not self._h:
+            check(-3, "ojasx_create_moe")
+        check(lib().ojasx_b200_moe_set_expert_offset(self._h, e0), "ojasx_b200_moe_set_expert_offset")
+        for which, csr, rows_per in ((0, w.gate_up_csr, 2 * w.inter), (1, w.down_csr, w.hidden)):
+            if csr is None:
+                continue
+            rp, ci, va = csr
+            r0, r1 = e0 * rows_per, e1 * rows_per
+            lo, hi = int(rp[r0]), int(rp[r1])
+            srp = np.ascontiguousarray(rp[r0:r1 + 1] - lo, dtype=np.int32)
+            sci = np.ascontiguousarray(ci[lo:hi], dtype=np.int32)
+            sva = np.ascontiguousarray(va[lo:hi], dtype=np.float32)
+            check(lib().ojasx_b200_moe_set_outliers(self._h, which, hi - lo, _p(srp), _p(sci), _p(sva)),
+                  "ojasx_b200_moe_set_outliers")
+        self.has_router = w.router is not None
+        if self.has_router:
+            r = np.ascontiguousarray(w.router, dtype=np.float32)
+            check(lib().ojasx_b200_moe_set_router(self._h, _p(r), w.num_experts), "ojasx_b200_moe_set_router")
+
+    @property
+    def handle(self):
+        return self._h
+
+    def reserve(self, max_tokens: int, k: int = 10):
+        check(lib().ojasx_b200_moe_reserve(self._h, max_tokens, k), "ojasx_b200_moe_reserve")
+
+    def forward(self, x: torch.Tensor, top_k_index: torch.Tensor, top_k_weights: torch.Tensor) -> torch.Tensor:
+        """Argument order of ``ResidualVQFusedExperts.forward`` (ojasx_24x96/module.py:653-658)."""
+        _require_cuda(x, "hidden_states")
+        x2 = x.reshape(-1, self.hidden).contiguous()
+        idx = top_k_index.reshape(x2.shape[0], -1).to(torch.int32).contiguous()
+        wts = top_k_weights.reshape(x2.shape[0], -1).to(torch.float32).contiguous()
+        y = torch.empty_like(x2)
+        check(lib().ojasx_b200_moe_forward(self._h, x2.data_ptr(), idx.data_ptr(), wts.data_ptr(), y.data_ptr(),
+                                           x2.shape[0], idx.shape[1], _dtype_code(x2), _stream_ptr(x.device)),
+              "ojasx_b200_moe_forward")
+        return y.reshape(x.shape)
+
+    def route(self, x: torch.Tensor, top_k: int = 10):
+        _require_cuda(x, "x")
+        x2 = x.reshape(-1, self.hidden).contiguous()
+        idx = torch.empty((x2.shape[0], top_k), device=x.device, dtype=torch.int32)
+        wts = torch.empty((x2.shape[0], top_k), device=x.device, dtype=torch.float32)
+        check(lib().ojasx_b200_moe_route(self._h, x2.data_ptr(), x2.shape[0], top_k, idx.data_ptr(), wts.data_ptr(),
+                                         _dtype_code(x2), _stream_ptr(x.device)), "ojasx_b200_moe_route")
+        return idx, wts
+
+    def forward_routed(self, x: torch.Tensor, top_k: int = 10, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        _require_cuda(x, "x")
+        x2 = x.reshape(-1, self.hidden).contiguous()
+        y = torch.empty_like(x2) if out is None else out
+        check(lib().ojasx_b200_moe_forward_routed(self._h, x2.data_ptr(), y.data_ptr(), x2.shape[0], top_k,
+                                                  _dtype_code(x2), _stream_ptr(x.device)),
+              "ojasx_b200_moe_forward_routed")
+        return y.reshape(x.shape)
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib().ojasx_destroy_moe(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class VQKVCache:
+    """Codebook-VQ KV cache of one layer: append one token per sequence, one decode query per sequence.
+
+    ``head_range=(first, stop)`` keeps only those KV heads (and their query heads) on this
+    device: the KV-head shard of a multi-GPU run.
+    """
+
+    def __init__(self, batch: int, kv_heads: int, q_heads: int, head_dim: int, block_dim: int, max_seq_len: int,
+                 k_codebook, v_codebook):
+        kcb = np.ascontiguousarray(k_codebook, dtype=np.float32)
+        vcb = np.ascontiguousarray(v_codebook, dtype=np.float32)
+        assert kcb.shape == (kv_heads, 256, block_dim) and vcb.shape == kcb.shape
+        self.batch, self.kv_heads, self.q_heads = batch, kv_heads, q_heads
+        self.head_dim, self.block_dim, self.max_seq_len = head_dim, block_dim, max_seq_len
+        self.groups = head_dim // block_dim
+        self._h = lib().ojasx_b200_kvq_create(batch, kv_heads, q_heads, head_dim, block_dim, max_seq_len, _p(kcb), _p(vcb))
+        if not self._h:
+            check(-3, "ojasx_b200_kvq_create")
+
+    def load(self, k_codes, v_codes):
+        kc = np.ascontiguousarray(k_codes, dtype=np.uint8)
+        vc = np.ascontiguousarray(v_codes, dtype=np.uint8)
+        assert kc.shape[:2] == (self.batch, self.kv_heads) and kc.shape[3] == self.groups and vc.shape == kc.shape
+        check(lib().ojasx_b200_kvq_load(self._h, _p(kc), _p(vc), kc.shape[2]), "ojasx_b200_kvq_load")
+
+    def read(self, t_begin: int, t_end: int):
+        kc = np.empty((self.batch, self.kv_heads, t_end - t_begin, self.groups), np.uint8)
+        vc = np.empty_like(kc)
+        check(lib().ojasx_b200_kvq_read(self._h, _p(kc), _p(vc), t_begin, t_end), "ojasx_b200_kvq_read")
+        return kc, vc
+
+    @property
+    def seq_len(self) -> int:
+        return lib().ojasx_b200_kvq_seq_len(self._h)
+
+    def reset(self):
+        check(lib().ojasx_b200_kvq_reset(self._h), "ojasx_b200_kvq_reset")
+
+    def append(self, k: torch.Tensor, v: torch.Tensor):
+        _require_cuda(k, "k")
+        k2, v2 = k.contiguous(), v.contiguous()
+        assert k2.shape == (self.batch, self.kv_heads, self.head_dim) and v2.shape == k2.shape and v2.dtype == k2.dtype
+        check(lib().ojasx_b200_kvq_append(self._h, k2.data_ptr(), v2.data_ptr(), _dtype_code(k2), _stream_ptr(k.device)),
+              "ojasx_b200_kvq_append")
+
+    def decode(self, q: torch.Tensor, scale: float = -1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        _require_cuda(q, "q")
+        q2 = q.contiguous()
+        assert q2.shape == (self.batch, self.q_heads, self.head_dim)
+        o = torch.empty_like(q2) if out is None else out
+        check(lib().ojasx_b200_kvq_decode(self._h, q2.data_ptr(), o.data_ptr(), scale, _dtype_code(q2),
+                                          _stream_ptr(q.device)), "ojasx_b200_kvq_decode")
+        return o
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib().ojasx_b200_kvq_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
