@@ -69,11 +69,11 @@ def test_legacy_kv_cache_matches_reference_semantics(cuda, oracle):
         kc, vc = np.zeros((T, G), np.uint8), np.zeros((T, G), np.uint8)
         ksc, vsc = np.zeros(T, np.float32), np.zeros(T, np.float32)
         for t in range(T):
-            cache.append(1, ks[t], vs[t])
+            cache.append(0, ks[t], vs[t])
             kc[t], vc[t], ksc[t], vsc[t] = oracle.kv_legacy_append(ks[t], vs[t], block_dim=D)
         want = oracle.kv_legacy_attention(q, kc, vc, ksc, vsc, block_dim=D)
-        got = cache.attention(1, q)
+        got = cache.attention(0, q)
         assert np.allclose(got, want, rtol=1e-4, atol=1e-6), np.abs(got - want).max()
         assert np.all(got.reshape(G, D)[:, 1:] == 0)          # only each block's first coordinate is written
-        assert np.all(cache.attention(0, q) == 0)             # empty head: output untouched (zeros)
+        assert np.all(cache.attention(1, q) == 0)             # empty head: output untouched (zeros)
         assert cache.compression_ratio >= 12.0
