@@ -154,6 +154,34 @@ OJASX_API int ojasx_b200_moe_route(OjasxMoEHandle handle, const void* d_x, int n
 OJASX_API int ojasx_b200_moe_forward_routed(OjasxMoEHandle handle, const void* d_x, void* d_y, int n_tokens, int top_k,
                                             int io_dtype, void* stream);
 
+/* MoE forward that obtains no memory.  It has no counterpart in the reference.
+ *
+ * Who it is for: code that runs where asking the CUDA runtime for memory is not possible or not
+ * allowed -- a serving loop whose device memory was handed out in full at start-up to a pool
+ * owned by someone else, a plugin called from inside another framework's step where an
+ * allocation would synchronise the device and stall that framework's streams, or a host thread
+ * with a hard latency budget.  ojasx_b200_moe_forward grows a per-handle scratch buffer with
+ * cudaMalloc whenever n_tokens*k_active rises; this variant instead keeps its scratch (the
+ * per-pair intermediate activations and per-pair expert outputs) in a fixed array inside the
+ * library's device image and calls no cudaMalloc, cudaFree or other allocating routine.
+ *
+ * Same arguments, same results, same skipping rules as ojasx_b200_moe_forward.  Limits and rules:
+ *  - n_tokens * k_active * (intermediate_dim + hidden_dim) must not exceed
+ *    OJASX_B200_NOALLOC_SCRATCH_FLOATS (1 MiB of fp32; 81 routed pairs at hidden 2560 /
+ *    intermediate 640, i.e. 8 tokens at top-10).  Larger requests return -5 and do nothing.
+ *  - Every GPU that loads the library holds that 1 MiB until the process exits.
+ *  - The handle's device must be the current device (-1 otherwise).
+ *  - The first call on each device looks up the array's device address; make that first call
+ *    outside of any stream capture.
+ *  - All calls, from every handle and stream, share the one array.  The array keeps whatever the
+ *    last call left in it (nothing needs clearing: each call writes every slot before reading it),
+ *    and two calls that overlap in time on the same GPU race on it.  Keep calls on one stream, or
+ *    order them with events. */
+#define OJASX_B200_NOALLOC_SCRATCH_FLOATS 262144
+OJASX_API int ojasx_b200_moe_forward_noalloc(OjasxMoEHandle handle, const void* d_x, const int* d_topk_idx,
+                                             const float* d_topk_w, void* d_y, int n_tokens, int k_active,
+                                             int io_dtype, void* stream);
+
 /* ---- Codebook-VQ KV cache of one layer (no counterpart in the reference, whose HeadKVCache
  * allocates k_codebook / v_codebook but never reads them, ojasx_lut_kv_cache.h:33-35): every
  * head vector is head_dim/block_dim uint8 codes into a per-KV-head codebook

@@ -41,6 +41,7 @@ SIGNATURES = {
     "ojasx_moe_get_compression_ratio": (_f, [_vp]),
     "ojasx_destroy_moe": (None, [_vp]),
     "ojasx_b200_moe_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "ojasx_b200_moe_forward_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "ojasx_b200_moe_reserve": (_i, [_vp, _i, _i]),
     "ojasx_b200_moe_set_outliers": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "ojasx_b200_moe_set_router": (_i, [_vp, _vp, _i]),

@@ -14,6 +14,9 @@
 #include "lut_core.cuh"
 #include "launch.h"
 #include "handles.h"
+#include "../../include/ojasx_lut_b200.h"
+
+#include <mutex>
 
 namespace ojx {
 
@@ -276,3 +279,55 @@ int launch_moe_router(const float* Wr, const void* x, int io_dtype, int n_tokens
 }
 
 }  // namespace ojx
+
+// ---------------------------------------------------------------- no-allocation MoE forward
+// Scratch for ojasx_b200_moe_forward_noalloc: a fixed array in this library's device image, so
+// the call never has to obtain memory.  Every GPU that loads the library holds these 1 MiB
+// until the process exits.
+namespace ojx {
+constexpr size_t kNoAllocScratchFloats = OJASX_B200_NOALLOC_SCRATCH_FLOATS;
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
+}  // namespace ojx
+
+extern "C" int ojasx_b200_moe_forward_noalloc(OjasxMoEHandle handle, const void* d_x, const int* d_topk_idx,
+                                              const float* d_topk_w, void* d_y, int n_tokens, int k_active,
+                                              int io_dtype, void* stream) {
+    using namespace ojx;
+    if (!handle || !d_x || !d_topk_idx || !d_topk_w || !d_y) return OJX_ERR_ARG;
+    if (n_tokens <= 0 || k_active <= 0 || (io_dtype != OJX_F32 && io_dtype != OJX_BF16)) return OJX_ERR_ARG;
+    auto* h = static_cast<MoeHandle*>(handle);
+    const size_t need = (size_t)n_tokens * k_active * ((size_t)h->I + h->H);
+    if (need > kNoAllocScratchFloats) {
+        set_last_error_msg("ojasx_b200_moe_forward_noalloc: n_tokens*k_active*(intermediate+hidden) exceeds "
+                           "OJASX_B200_NOALLOC_SCRATCH_FLOATS; use ojasx_b200_moe_forward for larger batches");
+        return OJX_ERR_TOO_LARGE;
+    }
+    int dev = -1;
+    OJX_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev != h->dev || dev < 0 || dev >= 64) {
+        set_last_error_msg("ojasx_b200_moe_forward_noalloc: the handle's device must be the current device");
+        return OJX_ERR_ARG;
+    }
+    // Set-up, once per device, with that device current: in host code `g_noalloc_scratch` is
+    // only a stand-in for the symbol, so its device address is looked up here and that pointer,
+    // not the symbol, is what the kernels receive.
+    static std::mutex mu;
+    static float* scratch_on[64] = {};
+    float* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!scratch_on[dev]) {
+            void* p = nullptr;
+            OJX_CUDA_TRY(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+            scratch_on[dev] = static_cast<float*>(p);
+        }
+        scratch = scratch_on[dev];
+    }
+    MoeProblem P = h->problem(d_x, d_y, d_topk_idx, d_topk_w, n_tokens, k_active, io_dtype);
+    // Nothing in the scratch has to start at zero: every (pair, index) slot that a later stage
+    // reads was written by the stage before it in this same call, and slots of skipped pairs are
+    // never read.  What an earlier call left there is therefore harmless.
+    P.inter = scratch;
+    P.expert_out = scratch + (size_t)n_tokens * k_active * h->I;
+    return launch_moe_experts(P, static_cast<cudaStream_t>(stream));
+}
