@@ -20,7 +20,7 @@ __device__ __forceinline__ const LinearProblem& find_problem(const LinearProblem
 }
 
 template <int D>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 lut_linear_kernel(const LinearProblem* __restrict__ probs, int nprobs, int total_items,
                   const __grid_constant__ LinearProblem single) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -47,16 +47,17 @@ lut_linear_kernel(const LinearProblem* __restrict__ probs, int nprobs, int total
         RowWalker<D> walker(sm, rs);
         if (walker.nslices == 0)
             for (int lr = threadIdx.x; lr < n; lr += kThreads) sm.acc[lr] = 0.0f;
-        walker.run(xl, P.codebook, P.Kcb);
+        walker.run(xl, P.codebook, P.Kcb, [&]() { if (P.csr.nnz > 0) csr_prefetch_l2(P.csr, r0, n); });
         __syncthreads();
 
         // Epilogue (ojasx_lut_cpu.cpp:178-182 then :117-127): scale, bias, outlier row, one store.
+        if (P.csr.nnz > 0) csr_rows_to_smem(sm, P.csr, r0, n, 0, xl);
         for (int lr = threadIdx.x; lr < n; lr += kThreads) {
             const int m = r0 + lr;
             float res = sm.acc[lr];
             if (P.scales) res = __fmul_rn(res, P.scales[m]);
             if (P.bias) res = __fadd_rn(res, P.bias[m]);
-            if (P.csr.nnz > 0) res = __fadd_rn(res, csr_row_sum(P.csr, m, xl));
+            if (P.csr.nnz > 0) res = __fadd_rn(res, sm.lut[lr]);
             const size_t o = (size_t)b * rows_out + (m - P.row_start);
             if (P.io_dtype == OJX_BF16) reinterpret_cast<__nv_bfloat16*>(P.y)[o] = __float2bfloat16_rn(res);
             else reinterpret_cast<float*>(P.y)[o] = res;
@@ -94,7 +95,7 @@ static int prepare_kernel(LinearKernel k) {
 int plan_tile_rows(int rows, int parallel_items) {
     // Spread one problem over the SMs when it is alone; otherwise keep tiles large so the table
     // build (replicated per tile) is amortised over many rows.
-    const int sms = num_sms();
+    const int sms = kCtasPerSm * num_sms();
     int tiles_wanted = sms / (parallel_items > 0 ? parallel_items : 1);
     if (tiles_wanted < 1) tiles_wanted = 1;
     int tr = round_up((rows + tiles_wanted - 1) / tiles_wanted, 32);
@@ -123,7 +124,8 @@ int launch_linear(LinearProblem P, cudaStream_t stream) {
     LinearKernel k = pick_linear_kernel(P.D);
     rc = prepare_kernel(k);
     if (rc != OJX_OK) return rc;
-    const int grid = total < num_sms() ? total : num_sms();
+    const int cap = kCtasPerSm * num_sms();
+    const int grid = total < cap ? total : cap;
     k<<<grid, kThreads, sizeof(CoreSmem), stream>>>(nullptr, 0, total, P);
     count_launch(1);
     OJX_CUDA_TRY(cudaGetLastError());
@@ -136,7 +138,8 @@ int launch_linear_group(const LinearProblem* d_probs, int nprobs, int total_item
     if (!k) return OJX_ERR_UNSUPPORTED;
     int rc = prepare_kernel(k);
     if (rc != OJX_OK) return rc;
-    const int grid = total_items < num_sms() ? total_items : num_sms();
+    const int cap = kCtasPerSm * num_sms();
+    const int grid = total_items < cap ? total_items : cap;
     LinearProblem dummy{};
     k<<<grid, kThreads, sizeof(CoreSmem), stream>>>(d_probs, nprobs, total_items, dummy);
     count_launch(1);

@@ -4,7 +4,8 @@
 // (split_manifold_lut_experiment/native/src/ojasx_lut_cpu.cpp:93-100 for the table,
 // :161-175 for the row sum), so results are bit-identical to it.
 //
-// Shape of the computation on one SM (one 512-thread CTA, ~214 KB of shared memory):
+// Shape of the computation on one SM (one 512-thread CTA, all 227 KB of shared memory; two
+// 256-thread CTAs with half-size tables were measured and were not faster):
 //   * the table of one token is G*256 fp32 and does not fit, so the group axis is cut into
 //     slices of <= 128 groups (128 KB); slices are processed in ascending order and the
 //     per-row accumulators are parked in shared memory between slices, which keeps the
@@ -21,10 +22,11 @@
 namespace ojx {
 
 constexpr int kThreads = 512;
+constexpr int kCtasPerSm = 1;
 constexpr int kWarps = kThreads / 32;
 constexpr int kSliceGroups = 128;            // table slice: 128 groups x 256 entries x 4 B = 128 KB
 constexpr int kXsFloats = kSliceGroups * 16; // x slice staging (block_dim <= 16 at 128 groups)
-constexpr int kAccRows = 3584;               // rows per work item that can park an accumulator
+constexpr int kAccRows = 6912;               // rows per work item that can park an accumulator
 constexpr int kChunk = 32;                   // code bytes per row per ring stage
 constexpr int kStages = 4;
 constexpr int kStageBytes = 32 * kChunk;     // 32 rows x 32 bytes
@@ -35,7 +37,7 @@ struct alignas(16) CoreSmem {
     float xs[kXsFloats];
     uint8_t ring[kWarps * kStages * kStageBytes];
 };
-static_assert(sizeof(CoreSmem) <= 227 * 1024, "shared memory budget");
+static_assert(kCtasPerSm * (sizeof(CoreSmem) + 1024) <= 228 * 1024, "shared memory budget of one SM");
 
 // Rows of a work item: local row lr < n0 lives at base0 + lr*G, the rest at base1 + (lr-n0)*G
 // (two ranges so that an expert's gate rows and up rows can share one table pass).
@@ -142,18 +144,40 @@ struct RowWalker {
 
     // Build table slice s: lut[gl*256 + k] = sum_d x[(g0+gl)*D + d] * cb[k*D + d], d ascending,
     // separate multiply and add (no fused multiply-add), as ojasx_lut_cpu.cpp:93-100 compiles
-    // to on a baseline x86-64 build.  c[] holds this thread's centroid (tid & 255).
+    // to on a baseline x86-64 build.  c[] holds this thread's centroid (tid & 255).  Four groups
+    // are in flight per thread so that the four dependent add chains overlap.
+    // (The packed fp32x2 forms of sm_100 are not used: ptxas contracts a packed mul.rn + add.rn
+    // pair into one FMA -- 76 % of 8-term dot products changed in a direct test -- also when
+    // they are spelled as a*b+(-0) and a*1+b, and that changes table values.)
     __device__ __forceinline__ void build_slice(int s, const XLoad& xl, const float (&c)[D], int Kcb) const {
+        constexpr int U = 4;
         const int g0 = s * SG, ng = slice_ng(s);
         for (int i = threadIdx.x; i < ng * D; i += kThreads) sm.xs[i] = xl(g0 * D + i);
         __syncthreads();
         const int kc = threadIdx.x & 255;
-        for (int gl = threadIdx.x >> 8; gl < ng; gl += kThreads / 256) {
-            const float* xg = sm.xs + gl * D;
-            float dot = __fmul_rn(xg[0], c[0]);
+        const bool ok = kc < Kcb;
+        constexpr int GS = kThreads / 256;  // groups advanced per step by the CTA's two halves
+        for (int gb = threadIdx.x >> 8; gb < ng; gb += GS * U) {
+            float dot[U];
 #pragma unroll
-            for (int d = 1; d < D; ++d) dot = __fadd_rn(dot, __fmul_rn(xg[d], c[d]));
-            sm.lut[gl * 256 + kc] = kc < Kcb ? dot : 0.0f;
+            for (int u = 0; u < U; ++u) {
+                const int gl = gb + u * GS;
+                const float4* xp = reinterpret_cast<const float4*>(sm.xs + (gl < ng ? gl : gb) * D);
+#pragma unroll
+                for (int q = 0; q < D / 4; ++q) {
+                    const float4 xx = xp[q];
+                    if (q == 0) dot[u] = __fmul_rn(xx.x, c[0]);
+                    else dot[u] = __fadd_rn(dot[u], __fmul_rn(xx.x, c[4 * q]));
+                    dot[u] = __fadd_rn(dot[u], __fmul_rn(xx.y, c[4 * q + 1]));
+                    dot[u] = __fadd_rn(dot[u], __fmul_rn(xx.z, c[4 * q + 2]));
+                    dot[u] = __fadd_rn(dot[u], __fmul_rn(xx.w, c[4 * q + 3]));
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int gl = gb + u * GS;
+                if (gl < ng) sm.lut[gl * 256 + kc] = ok ? dot[u] : 0.0f;
+            }
         }
         __syncthreads();
     }
@@ -191,8 +215,11 @@ struct RowWalker {
     }
 
     // Leaves sm.acc[lr] = sum_{g<G} LUT_x[g, code[lr, g]] for lr < rs.n.  All threads of the
-    // CTA must call it; on return a __syncthreads() has NOT yet been executed.
-    __device__ void run(const XLoad& xl, const float* __restrict__ codebook, int Kcb) const {
+    // CTA must call it; on return a __syncthreads() has NOT yet been executed.  `before_last`
+    // runs once, right after the table of the last slice is built (used to ask L2 for the data
+    // the epilogue will want).
+    template <class F>
+    __device__ void run(const XLoad& xl, const float* __restrict__ codebook, int Kcb, F before_last) const {
         float c[D];
         {
             const int kc = threadIdx.x & 255;
@@ -211,6 +238,7 @@ struct RowWalker {
         for (int s = 0; s < nslices; ++s) {
             __syncthreads();  // every warp has left the previous slice's table (and sm.xs)
             build_slice(s, xl, c, Kcb);
+            if (s == nslices - 1) before_last();
             const int nch = slice_chunks(s);
             for (int rb = warp; rb < nrb; rb += kWarps) {
                 const int lr = rb * 32 + lane;
@@ -232,13 +260,73 @@ struct RowWalker {
     }
 };
 
-// CSR outlier row sum, reference order (ojasx_lut_cpu.cpp:117-126): acc = 0; j ascending;
-// acc += val * x[col] with separate multiply and add.
-__device__ __forceinline__ float csr_row_sum(const CsrView& csr, int row, const XLoad& xl) {
-    float acc = 0.0f;
-    const int e = csr.row_ptrs[row + 1];
-    for (int j = csr.row_ptrs[row]; j < e; ++j) acc = __fadd_rn(acc, __fmul_rn(csr.vals[j], xl(csr.cols[j])));
-    return acc;
+// CSR outlier row sums for the rows [row0, row0+n) of a work item, reference order
+// (ojasx_lut_cpu.cpp:117-126): acc = 0; j ascending; acc += val * x[col], multiply then add.
+// The products are independent of one another, so they are computed by all threads with
+// coalesced loads of (col, val) and staged in the table area of shared memory (free once the
+// row walk is over); only the short in-order additions run one row per thread.  Results land in
+// sm.lut[oacc_off + lr].  Every thread of the CTA must call it, after a __syncthreads() that
+// follows the row walk; it ends with a __syncthreads().
+constexpr int kCsrOaccFloats = 8192;                                   // >= kAccRows
+constexpr int kCsrXFloats = 8192;                                      // activations staged when K fits
+constexpr int kCsrChunk = kSliceGroups * 256 - kCsrOaccFloats - kCsrXFloats;  // products per pass
+constexpr int kCsrUnroll = 8;
+static_assert(kCsrOaccFloats >= kAccRows, "outlier sums need one slot per row");
+static_assert((kAccRows + 1) * sizeof(int) <= sizeof(CoreSmem::ring), "row pointers are staged in the ring area");
+
+// Ask L2 for the CSR arrays of rows [row0, row0+n) (called before the row walk, so the data is
+// near by the time the epilogue wants it).
+__device__ __forceinline__ void csr_prefetch_l2(const CsrView& csr, int row0, int n) {
+    const int jb = csr.row_ptrs[row0], je = csr.row_ptrs[row0 + n];
+    for (int j = jb + threadIdx.x * 32; j < je; j += kThreads * 32) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(csr.cols + j));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(csr.vals + j));
+    }
+    for (int r = threadIdx.x * 32; r <= n; r += kThreads * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(csr.row_ptrs + row0 + r));
+}
+
+__device__ __forceinline__ void csr_rows_to_smem(CoreSmem& sm, const CsrView& csr, int row0, int n, int oacc_off,
+                                                 const XLoad& xl) {
+    float* oacc = sm.lut + oacc_off;
+    float* xsm = sm.lut + kCsrOaccFloats;
+    float* prod = xsm + kCsrXFloats;
+    int* rp = reinterpret_cast<int*>(sm.ring);  // the code ring is idle between row walks
+    const bool x_in_smem = xl.K <= kCsrXFloats;
+    for (int lr = threadIdx.x; lr <= n; lr += kThreads) rp[lr] = csr.row_ptrs[row0 + lr];
+    for (int lr = threadIdx.x; lr < n; lr += kThreads) oacc[lr] = 0.0f;
+    if (x_in_smem)
+        for (int k = threadIdx.x; k < xl.K; k += kThreads) xsm[k] = xl(k);
+    __syncthreads();
+    const int jb = rp[0], je = rp[n];
+    for (int jc = jb; jc < je; jc += kCsrChunk) {
+        const int ce = min(jc + kCsrChunk, je);
+        for (int base = jc + threadIdx.x; base < ce; base += kThreads * kCsrUnroll) {
+            int col[kCsrUnroll];
+            float val[kCsrUnroll];
+#pragma unroll
+            for (int u = 0; u < kCsrUnroll; ++u) {
+                const int j = base + u * kThreads;
+                col[u] = j < ce ? csr.cols[j] : 0;
+                val[u] = j < ce ? csr.vals[j] : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < kCsrUnroll; ++u) {
+                const int j = base + u * kThreads;
+                const float xv = x_in_smem ? xsm[col[u]] : xl(col[u]);
+                if (j < ce) prod[j - jc] = __fmul_rn(val[u], xv);
+            }
+        }
+        __syncthreads();
+        for (int lr = threadIdx.x; lr < n; lr += kThreads) {
+            const int s = max(rp[lr], jc), e = min(rp[lr + 1], ce);
+            if (s < e) {
+                float acc = oacc[lr];
+                for (int j = s; j < e; ++j) acc = __fadd_rn(acc, prod[j - jc]);
+                oacc[lr] = acc;
+            }
+        }
+        __syncthreads();
+    }
 }
 
 }  // namespace ojx

@@ -42,7 +42,7 @@ __device__ __forceinline__ MoePair decode_pair(const MoeProblem& P, int pair) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(kThreads, 1) moe_gate_up_kernel(const __grid_constant__ MoeProblem P) {
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) moe_gate_up_kernel(const __grid_constant__ MoeProblem P) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     CoreSmem& sm = *reinterpret_cast<CoreSmem*>(smem_raw);
     const int total = P.n_tokens * P.k_active * P.gu_tiles;
@@ -64,15 +64,24 @@ __global__ void __launch_bounds__(kThreads, 1) moe_gate_up_kernel(const __grid_c
         RowWalker<D> walker(sm, rs);
         if (walker.nslices == 0)
             for (int lr = threadIdx.x; lr < 2 * n; lr += kThreads) sm.acc[lr] = 0.0f;
-        walker.run(xl, P.cb_in, P.Kcb);
+        walker.run(xl, P.cb_in, P.Kcb, [&]() {
+            if (P.gu_csr.nnz > 0) {
+                csr_prefetch_l2(P.gu_csr, (int)(row0 + i0), n);
+                csr_prefetch_l2(P.gu_csr, (int)(row0 + P.I + i0), n);
+            }
+        });
         __syncthreads();
+        if (P.gu_csr.nnz > 0) {
+            csr_rows_to_smem(sm, P.gu_csr, (int)(row0 + i0), n, 0, xl);
+            csr_rows_to_smem(sm, P.gu_csr, (int)(row0 + P.I + i0), n, n, xl);
+        }
         for (int lr = threadIdx.x; lr < n; lr += kThreads) {
             const size_t rg = row0 + i0 + lr, ru = row0 + P.I + i0 + lr;
             float gate = sm.acc[lr], up = sm.acc[n + lr];
             if (P.gu_scales) { gate = __fmul_rn(gate, P.gu_scales[rg]); up = __fmul_rn(up, P.gu_scales[ru]); }
             if (P.gu_csr.nnz > 0) {
-                gate = __fadd_rn(gate, csr_row_sum(P.gu_csr, (int)rg, xl));
-                up = __fadd_rn(up, csr_row_sum(P.gu_csr, (int)ru, xl));
+                gate = __fadd_rn(gate, sm.lut[lr]);
+                up = __fadd_rn(up, sm.lut[n + lr]);
             }
             P.inter[(size_t)pair * P.I + i0 + lr] = __fmul_rn(silu_ref(gate), up);
         }
@@ -81,7 +90,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_gate_up_kernel(const __grid_c
 }
 
 template <int D>
-__global__ void __launch_bounds__(kThreads, 1) moe_down_kernel(const __grid_constant__ MoeProblem P) {
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) moe_down_kernel(const __grid_constant__ MoeProblem P) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     CoreSmem& sm = *reinterpret_cast<CoreSmem*>(smem_raw);
     const int total = P.n_tokens * P.k_active * P.dn_tiles;
@@ -102,13 +111,14 @@ __global__ void __launch_bounds__(kThreads, 1) moe_down_kernel(const __grid_cons
         RowWalker<D> walker(sm, rs);
         if (walker.nslices == 0)
             for (int lr = threadIdx.x; lr < n; lr += kThreads) sm.acc[lr] = 0.0f;
-        walker.run(xl, P.cb_down, P.Kcb);
+        walker.run(xl, P.cb_down, P.Kcb, [&]() { if (P.dn_csr.nnz > 0) csr_prefetch_l2(P.dn_csr, (int)(row0 + h0), n); });
         __syncthreads();
+        if (P.dn_csr.nnz > 0) csr_rows_to_smem(sm, P.dn_csr, (int)(row0 + h0), n, 0, xl);
         for (int lr = threadIdx.x; lr < n; lr += kThreads) {
             const size_t r = row0 + h0 + lr;
             float v = sm.acc[lr];
             if (P.dn_scales) v = __fmul_rn(v, P.dn_scales[r]);
-            if (P.dn_csr.nnz > 0) v = __fadd_rn(v, csr_row_sum(P.dn_csr, (int)r, xl));
+            if (P.dn_csr.nnz > 0) v = __fadd_rn(v, sm.lut[lr]);
             P.expert_out[(size_t)pair * P.H + h0 + lr] = v;
         }
         __syncthreads();
@@ -230,7 +240,7 @@ static int launch_moe_experts_t(const MoeProblem& P, cudaStream_t s) {
     int rc;
     if ((rc = set_smem(moe_gate_up_kernel<D>)) != OJX_OK) return rc;
     if ((rc = set_smem(moe_down_kernel<D>)) != OJX_OK) return rc;
-    const int pairs = P.n_tokens * P.k_active, sms = num_sms();
+    const int pairs = P.n_tokens * P.k_active, sms = kCtasPerSm * num_sms();
     const int gu_items = pairs * P.gu_tiles, dn_items = pairs * P.dn_tiles;
     moe_gate_up_kernel<D><<<gu_items < sms ? gu_items : sms, kThreads, sizeof(CoreSmem), s>>>(P);
     OJX_CUDA_TRY(cudaGetLastError());
@@ -246,7 +256,7 @@ static int launch_moe_experts_t(const MoeProblem& P, cudaStream_t s) {
 int launch_moe_experts(MoeProblem P, cudaStream_t s) {
     if (!P.x || !P.y || !P.topk_idx || !P.topk_w || !P.inter || !P.expert_out) return OJX_ERR_ARG;
     if (P.n_tokens <= 0 || P.k_active <= 0) return OJX_ERR_ARG;
-    const int pairs = P.n_tokens * P.k_active, sms = num_sms();
+    const int pairs = P.n_tokens * P.k_active, sms = kCtasPerSm * num_sms();
     // Tiles: spread few pairs over the SMs, keep tiles whole when there are many pairs.
     int want = (sms + pairs - 1) / pairs;
     P.gu_tile = round_up((P.I + want - 1) / want, 16);
