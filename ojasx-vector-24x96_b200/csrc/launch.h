@@ -10,6 +10,9 @@ int validate_linear(const LinearProblem& P);
 int launch_linear(LinearProblem P, cudaStream_t stream);
 int launch_linear_group(const LinearProblem* d_probs, int nprobs, int total_items, int D, cudaStream_t stream);
 
+// --- linear_cluster.cu: OJX_ERR_UNSUPPORTED means "use the persistent kernel"
+int try_launch_linear_cluster(const LinearProblem& P, cudaStream_t stream);
+
 // --- moe.cu
 int launch_moe_experts(MoeProblem P, cudaStream_t stream);
 int launch_moe_router(const float* Wr, const void* x, int io_dtype, int n_tokens, int H, int E, int k,

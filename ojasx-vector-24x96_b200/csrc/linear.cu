@@ -8,6 +8,8 @@
 #include "launch.h"
 #include "handles.h"
 
+#include <cstdlib>
+
 namespace ojx {
 
 __device__ __forceinline__ const LinearProblem& find_problem(const LinearProblem* probs, int nprobs, int item) {
@@ -104,6 +106,13 @@ int plan_tile_rows(int rows, int parallel_items) {
     return tr;
 }
 
+// OJASX_B200_LINEAR_KERNEL=persistent keeps single problems on the persistent kernel (used by
+// the tests to cover both kernels on the same inputs).
+static bool force_persistent() {
+    const char* e = getenv("OJASX_B200_LINEAR_KERNEL");
+    return e && e[0] == 'p';
+}
+
 int validate_linear(const LinearProblem& P) {
     if (!P.codes || !P.codebook || !P.x || !P.y) return OJX_ERR_ARG;
     if (P.batch <= 0 || P.K <= 0 || P.G < 0 || P.row_stop <= P.row_start || P.row_start < 0) return OJX_ERR_ARG;
@@ -117,6 +126,11 @@ int launch_linear(LinearProblem P, cudaStream_t stream) {
     int rc = validate_linear(P);
     if (rc != OJX_OK) return rc;
     const int rows = P.row_stop - P.row_start;
+    if (P.tile_rows <= 0 && !force_persistent()) {
+        // Small single problems: the cluster kernel spreads the table build over the GPU.
+        rc = try_launch_linear_cluster(P, stream);
+        if (rc != OJX_ERR_UNSUPPORTED) return rc;
+    }
     if (P.tile_rows <= 0) P.tile_rows = plan_tile_rows(rows, P.batch);
     P.tiles = (rows + P.tile_rows - 1) / P.tile_rows;
     P.item_begin = 0;

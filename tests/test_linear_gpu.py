@@ -33,6 +33,23 @@ def test_linear_device_bit_exact(cuda, oracle, K, M, D, sc, bi, frac):
     assert np.array_equal(got, want), f"max abs diff {np.abs(got - want).max()}"
 
 
+@pytest.mark.parametrize("K,M,D,batch", [(2560, 6912, 8, 1), (6912, 2560, 8, 3), (2560, 151936 // 8, 8, 1), (640, 2560, 8, 2),
+                                         (256, 128, 16, 1), (2560, 1024, 8, 5)])
+def test_linear_cluster_and_persistent_kernels_agree(cuda, oracle, monkeypatch, K, M, D, batch):
+    """Single problems normally take the cluster kernel; OJASX_B200_LINEAR_KERNEL=persistent forces the
+    streaming kernel.  Both must reproduce the oracle bit for bit."""
+    w = synth.make_vq_linear(K + M, K, M, block_dim=D, with_scales=True, with_bias=True)
+    x = np.random.default_rng(8).standard_normal((batch, K)).astype(np.float32)
+    want = oracle.linear_forward(w.codebook, w.codes, w.scales, w.bias, w.csr, x, block_dim=D)
+    layer = ops.VQLinear.from_weights(w)
+    xt = torch.from_numpy(x).to(cuda)
+    got_default = layer(xt).cpu().numpy()
+    monkeypatch.setenv("OJASX_B200_LINEAR_KERNEL", "persistent")
+    got_persistent = layer(xt).cpu().numpy()
+    assert np.array_equal(got_persistent, want)
+    assert np.array_equal(got_default, want)
+
+
 def test_linear_host_abi_matches_reference_bindings(cuda, oracle):
     """The reference's ctypes class, bound to this library, on host arrays."""
     w = synth.make_vq_linear(3, 2560, 2560, block_dim=8)
