@@ -54,6 +54,30 @@ int ensure_capacity(void** dptr, size_t* cap, size_t bytes) {
     return OJX_OK;
 }
 
+int ensure_pinned(void** hptr, size_t* cap, size_t bytes) {
+    if (*cap >= bytes && *hptr) return OJX_OK;
+    if (*hptr) OJX_CUDA_TRY(cudaFreeHost(*hptr));
+    *hptr = nullptr;
+    *cap = 0;
+    size_t want = bytes < 65536 ? 65536 : bytes;
+    OJX_CUDA_TRY(cudaHostAlloc(hptr, want, cudaHostAllocMapped));
+    *cap = want;
+    return OJX_OK;
+}
+
+// Waits for a stream by polling: the host-pointer entry points are latency-bound (one small
+// kernel per call) and a polled query returns a few microseconds sooner than a blocking
+// synchronise.  Falls back to the blocking call after ~2 ms of polling.
+int wait_stream(cudaStream_t s) {
+    for (int i = 0; i < 20000; ++i) {
+        cudaError_t e = cudaStreamQuery(s);
+        if (e == cudaSuccess) return OJX_OK;
+        if (e != cudaErrorNotReady) { set_last_error("cudaStreamQuery", e); return OJX_ERR_CUDA; }
+    }
+    OJX_CUDA_TRY(cudaStreamSynchronize(s));
+    return OJX_OK;
+}
+
 DeviceGuard::DeviceGuard(int dev) : prev_(-1) {
     if (cudaGetDevice(&prev_) != cudaSuccess) prev_ = -1;
     if (prev_ != dev) cudaSetDevice(dev); else prev_ = -1;
@@ -64,6 +88,8 @@ LinearHandle::~LinearHandle() {
     DeviceGuard g(dev);
     cudaFree(codes); cudaFree(codebook); cudaFree(scales); cudaFree(bias);
     cudaFree(row_ptrs); cudaFree(cols); cudaFree(vals); cudaFree(d_x); cudaFree(d_y);
+    if (pin_x) cudaFreeHost(pin_x);
+    if (pin_y) cudaFreeHost(pin_y);
     if (stream) cudaStreamDestroy(stream);
 }
 
@@ -168,12 +194,19 @@ int ojasx_linear_forward(OjasxLinearHandle handle, const float* x, float* y, int
     const size_t xb = sizeof(float) * (size_t)batch_size * h->in, yb = sizeof(float) * (size_t)batch_size * h->out;
     int rc;
     if ((rc = ensure_capacity(&h->d_x, &h->cap_x, xb)) != OJX_OK) return rc;
-    if ((rc = ensure_capacity(&h->d_y, &h->cap_y, yb)) != OJX_OK) return rc;
-    OJX_CUDA_TRY(cudaMemcpyAsync(h->d_x, x, xb, cudaMemcpyHostToDevice, h->stream));
-    rc = launch_linear(h->problem(h->d_x, h->d_y, batch_size, OJX_F32, 0, h->out), h->stream);
+    if ((rc = ensure_pinned(&h->pin_x, &h->cap_pin_x, xb)) != OJX_OK) return rc;
+    if ((rc = ensure_pinned(&h->pin_y, &h->cap_pin_y, yb)) != OJX_OK) return rc;
+    // x: host copy into pinned staging, then one asynchronous H2D copy.  y: the kernel stores its
+    // results straight into device-mapped pinned memory, so no D2H copy is enqueued; after the
+    // stream synchronises the results are in host memory and are copied to the caller's buffer.
+    void* y_dev = nullptr;
+    OJX_CUDA_TRY(cudaHostGetDevicePointer(&y_dev, h->pin_y, 0));
+    std::memcpy(h->pin_x, x, xb);
+    OJX_CUDA_TRY(cudaMemcpyAsync(h->d_x, h->pin_x, xb, cudaMemcpyHostToDevice, h->stream));
+    rc = launch_linear(h->problem(h->d_x, y_dev, batch_size, OJX_F32, 0, h->out), h->stream);
     if (rc != OJX_OK) return rc;
-    OJX_CUDA_TRY(cudaMemcpyAsync(y, h->d_y, yb, cudaMemcpyDeviceToHost, h->stream));
-    OJX_CUDA_TRY(cudaStreamSynchronize(h->stream));
+    if ((rc = wait_stream(h->stream)) != OJX_OK) return rc;
+    std::memcpy(y, h->pin_y, yb);
     return OJX_OK;
 }
 

@@ -8,6 +8,8 @@ namespace ojx {
 void count_launch(int n);
 int upload(void** dptr, const void* host, size_t bytes);          // cudaMalloc + copy (zero-fill when host == null)
 int ensure_capacity(void** dptr, size_t* cap, size_t bytes);      // grow-only device staging buffer
+int wait_stream(cudaStream_t s);                                  // low-latency stream wait
+int ensure_pinned(void** hptr, size_t* cap, size_t bytes);        // grow-only pinned, device-mapped host buffer
 
 // Makes `dev` current for the lifetime of the guard.
 class DeviceGuard {
@@ -34,6 +36,9 @@ struct LinearHandle {
     void* d_x = nullptr;
     void* d_y = nullptr;
     size_t cap_x = 0, cap_y = 0;
+    void* pin_x = nullptr;     // pinned host staging for x (source of an asynchronous copy)
+    void* pin_y = nullptr;     // pinned, device-mapped host staging for y (written by the kernel itself)
+    size_t cap_pin_x = 0, cap_pin_y = 0;
     cudaStream_t stream = nullptr;
 
     ~LinearHandle();

@@ -18,9 +18,7 @@
 namespace ojx {
 
 constexpr int kKvThreads = 256;
-constexpr int kKvMaxRep = 8;      // query heads per KV head
 constexpr int kKvMaxGroups = 32;  // head_dim / block_dim
-constexpr int kKvMaxD = 16;
 
 __device__ __forceinline__ float load_io(const void* p, size_t i, int dtype) {
     return dtype == OJX_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i])
@@ -28,69 +26,80 @@ __device__ __forceinline__ float load_io(const void* p, size_t i, int dtype) {
 }
 
 // ------------------------------------------------------------------------------ kvq append
-// One CTA per sequence.  Task = (k|v, kv head, group); one warp per task scans the 256
-// centroids.  dist = (|v|^2 - 2 v.c) + |c|^2 with every dot product a sequential fp32 sum
-// (separate multiply and add); arg-min takes the first minimum.
+// grid = (ceil(tasks / warps per CTA), B).  Task = (k|v, kv head, group); one warp per task scans
+// the 256 centroids.  dist = (|v|^2 - 2 v.c) + |c|^2 with every dot product a sequential fp32 sum
+// (separate multiply and add); arg-min takes the first minimum.  The sequence length is bumped
+// by kvq_bump_kernel once every task has written its code.
+template <int D>
 __global__ void __launch_bounds__(kKvThreads) kvq_append_kernel(const __grid_constant__ KvqProblem P) {
-    const int b = blockIdx.x;
+    const int b = blockIdx.y;
     const int T = P.seq_lens[b];
-    if (T >= P.max_seq) {
-        if (threadIdx.x == 0) atomicExch(P.error_flag, 1);
-        return;
-    }
+    if (T >= P.max_seq) return;  // reported by kvq_bump_kernel
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-    const int D = P.D, G = P.G, hd = P.head_dim;
+    const int G = P.G, hd = P.head_dim;
     const int tasks = 2 * P.Hkv * G;
-    for (int task = warp; task < tasks; task += nwarps) {
-        const int which = task / (P.Hkv * G);
-        const int rem = task - which * P.Hkv * G;
-        const int h = rem / G, g = rem - h * G;
-        const void* src = which ? P.new_v : P.new_k;
-        const float* cb = (which ? P.v_cb : P.k_cb) + (size_t)h * P.Kcb * D;
-        float v[kKvMaxD];
-        float vv = 0.0f;
-        for (int d = 0; d < D; ++d) {
-            v[d] = load_io(src, ((size_t)b * P.Hkv + h) * hd + g * D + d, P.io_dtype);
-            vv = __fadd_rn(vv, __fmul_rn(v[d], v[d]));
-        }
-        float bd = INFINITY;
-        int bi = 0x7fffffff;
-        for (int c = lane; c < P.Kcb; c += 32) {
-            const float* cv = cb + (size_t)c * D;
-            float vc = 0.0f, cc = 0.0f;
-            for (int d = 0; d < D; ++d) vc = __fadd_rn(vc, __fmul_rn(v[d], cv[d]));
-            for (int d = 0; d < D; ++d) cc = __fadd_rn(cc, __fmul_rn(cv[d], cv[d]));
-            const float dist = __fadd_rn(__fsub_rn(vv, __fmul_rn(2.0f, vc)), cc);
-            if (dist < bd) { bd = dist; bi = c; }
-        }
+    const int task = blockIdx.x * nwarps + warp;
+    if (task >= tasks) return;
+    const int which = task / (P.Hkv * G);
+    const int rem = task - which * P.Hkv * G;
+    const int h = rem / G, g = rem - h * G;
+    const void* src = which ? P.new_v : P.new_k;
+    const float* cb = (which ? P.v_cb : P.k_cb) + (size_t)h * P.Kcb * D;
+    float v[D];
+    float vv = 0.0f;
 #pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) {
-            const float od = __shfl_xor_sync(0xffffffffu, bd, off);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
-            if (od < bd || (od == bd && oi < bi)) { bd = od; bi = oi; }
-        }
-        if (lane == 0) {
-            uint8_t* codes = which ? P.v_codes : P.k_codes;
-            codes[(((size_t)b * P.Hkv + h) * P.max_seq + T) * G + g] = (uint8_t)bi;
-        }
+    for (int d = 0; d < D; ++d) {
+        v[d] = load_io(src, ((size_t)b * P.Hkv + h) * hd + g * D + d, P.io_dtype);
+        vv = __fadd_rn(vv, __fmul_rn(v[d], v[d]));
     }
-    __syncthreads();
-    if (threadIdx.x == 0) P.seq_lens[b] = T + 1;
+    float bd = INFINITY;
+    int bi = 0x7fffffff;
+    for (int c = lane; c < P.Kcb; c += 32) {
+        float cv[D];
+#pragma unroll
+        for (int d = 0; d < D; ++d) cv[d] = cb[(size_t)c * D + d];
+        float vc = 0.0f, cc = 0.0f;
+#pragma unroll
+        for (int d = 0; d < D; ++d) vc = __fadd_rn(vc, __fmul_rn(v[d], cv[d]));
+#pragma unroll
+        for (int d = 0; d < D; ++d) cc = __fadd_rn(cc, __fmul_rn(cv[d], cv[d]));
+        const float dist = __fadd_rn(__fsub_rn(vv, __fmul_rn(2.0f, vc)), cc);
+        if (dist < bd) { bd = dist; bi = c; }
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+        const float od = __shfl_xor_sync(0xffffffffu, bd, off);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+        if (od < bd || (od == bd && oi < bi)) { bd = od; bi = oi; }
+    }
+    if (lane == 0) {
+        uint8_t* codes = which ? P.v_codes : P.k_codes;
+        codes[(((size_t)b * P.Hkv + h) * P.max_seq + T) * G + g] = (uint8_t)bi;
+    }
+}
+
+__global__ void kvq_bump_kernel(int* seq_lens, int B, int max_seq, int* error_flag) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= B) return;
+    if (seq_lens[b] >= max_seq) atomicExch(error_flag, 1);
+    else seq_lens[b] += 1;
 }
 
 // ------------------------------------------------------------------------------ kvq decode
 // grid = (chunks, Hkv, B).  Shared memory: query table [G,256,R] fp32, value codebook [256,D],
-// the chunk's scores/probabilities [chunk, R] and its value codes [chunk, G].
-template <int R>
+// the R queries, the chunk's scores/probabilities [chunk, R] and its key and value codes.
+template <int R, int D>
 __global__ void __launch_bounds__(kKvThreads) kvq_decode_kernel(const __grid_constant__ KvqProblem P) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int G = P.G, D = P.D, hd = P.head_dim, tid = threadIdx.x;
+    const int G = P.G, hd = P.head_dim, tid = threadIdx.x;
     float* lut = reinterpret_cast<float*>(smem_raw);               // [G*256*R]
     float* vcb = lut + (size_t)G * 256 * R;                        // [256*D]
-    float* sc = vcb + 256 * D;                                     // [chunk*R]
+    float* qs = vcb + 256 * D;                                     // [R*hd]
+    float* sc = qs + R * hd;                                       // [chunk*R]
     float* red = sc + (size_t)P.chunk * R;                         // [kKvThreads]
-    float* osum = red + kKvThreads;                                // [2][R*hd] partial outputs of the two token halves
-    uint8_t* vcs = reinterpret_cast<uint8_t*>(osum + 2 * R * hd);  // [chunk*G]
+    float* osum = red + kKvThreads;                                // [R*hd]
+    uint8_t* kcs = reinterpret_cast<uint8_t*>(osum + R * hd);      // [chunk*G]
+    uint8_t* vcs = kcs + (size_t)P.chunk * G;                      // [chunk*G]
 
     const int b = blockIdx.z, h = blockIdx.y, ch = blockIdx.x;
     const int T = P.seq_lens[b];
@@ -98,30 +107,46 @@ __global__ void __launch_bounds__(kKvThreads) kvq_decode_kernel(const __grid_con
     const int n = min(P.chunk, T - t0);
     float* part = P.partials + ((((size_t)b * P.Hkv + h) * P.n_chunks + ch) * R) * (hd + 2);
     if (n <= 0) {  // chunk beyond this sequence: neutral partial
-        for (int i = tid; i < R * (hd + 2); i += blockDim.x) {
-            const int w = i % (hd + 2);
-            part[i] = w == 0 ? -INFINITY : 0.0f;
-        }
+        for (int i = tid; i < R * (hd + 2); i += blockDim.x) part[i] = (i % (hd + 2)) == 0 ? -INFINITY : 0.0f;
         return;
     }
     const uint8_t* kc = P.k_codes + (((size_t)b * P.Hkv + h) * P.max_seq + t0) * G;
     const uint8_t* vc = P.v_codes + (((size_t)b * P.Hkv + h) * P.max_seq + t0) * G;
 
+    // stage codes (coalesced 16-byte copies when the chunk start is aligned), queries, value codebook
+    {
+        const size_t bytes = (size_t)n * G;
+        if (((reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc)) & 15) == 0) {
+            const int n16 = (int)(bytes >> 4);
+            for (int i = tid; i < n16; i += blockDim.x) {
+                reinterpret_cast<uint4*>(kcs)[i] = reinterpret_cast<const uint4*>(kc)[i];
+                reinterpret_cast<uint4*>(vcs)[i] = reinterpret_cast<const uint4*>(vc)[i];
+            }
+            for (int i = (n16 << 4) + tid; i < (int)bytes; i += blockDim.x) { kcs[i] = kc[i]; vcs[i] = vc[i]; }
+        } else {
+            for (int i = tid; i < (int)bytes; i += blockDim.x) { kcs[i] = kc[i]; vcs[i] = vc[i]; }
+        }
+        for (int i = tid; i < R * hd; i += blockDim.x) qs[i] = load_io(P.q, ((size_t)b * P.Hq + (size_t)h * R) * hd + i, P.io_dtype);
+        for (int i = tid; i < 256 * D; i += blockDim.x) vcb[i] = i < P.Kcb * D ? P.v_cb[(size_t)h * P.Kcb * D + i] : 0.0f;
+    }
+    __syncthreads();
     // query table: thread c owns centroid c
     {
-        const float* kcb = P.k_cb + ((size_t)h * P.Kcb + (tid < P.Kcb ? tid : 0)) * D;
-        float c[kKvMaxD];
-        for (int d = 0; d < D; ++d) c[d] = tid < P.Kcb ? kcb[d] : 0.0f;
-        for (int r = 0; r < R; ++r) {
-            const size_t qoff = ((size_t)b * P.Hq + (size_t)h * R + r) * hd;
-            for (int g = 0; g < G; ++g) {
+        float c[D];
+#pragma unroll
+        for (int d = 0; d < D; ++d) c[d] = tid < P.Kcb ? P.k_cb[((size_t)h * P.Kcb + tid) * D + d] : 0.0f;
+        for (int g = 0; g < G; ++g) {
+            float e[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
                 float dot = 0.0f;
-                for (int d = 0; d < D; ++d) dot = fmaf(load_io(P.q, qoff + g * D + d, P.io_dtype), c[d], dot);
-                lut[((size_t)g * 256 + tid) * R + r] = dot;
+#pragma unroll
+                for (int d = 0; d < D; ++d) dot = fmaf(qs[r * hd + g * D + d], c[d], dot);
+                e[r] = dot;
             }
+#pragma unroll
+            for (int r = 0; r < R; ++r) lut[((size_t)g * 256 + tid) * R + r] = e[r];
         }
-        for (int i = tid; i < 256 * D; i += blockDim.x) vcb[i] = i < P.Kcb * D ? P.v_cb[(size_t)h * P.Kcb * D + i] : 0.0f;
-        for (int i = tid; i < n * G; i += blockDim.x) vcs[i] = vc[i];
     }
     __syncthreads();
 
@@ -133,7 +158,7 @@ __global__ void __launch_bounds__(kKvThreads) kvq_decode_kernel(const __grid_con
         float acc[R];
 #pragma unroll
         for (int r = 0; r < R; ++r) acc[r] = 0.0f;
-        const uint8_t* row = kc + (size_t)t * G;
+        const uint8_t* row = kcs + (size_t)t * G;
         for (int g = 0; g < G; ++g) {
             const float* e = lut + ((size_t)g * 256 + row[g]) * R;
 #pragma unroll
@@ -182,21 +207,19 @@ __global__ void __launch_bounds__(kKvThreads) kvq_decode_kernel(const __grid_con
         __syncthreads();
     }
 
-    // values: thread = (token half, output column); R accumulators
+    // values: thread = (token stripe, output column); R accumulators
     {
         const int col = tid % hd, half = tid / hd, halves = blockDim.x / hd;  // blockDim.x is a multiple of hd
         const int g = col / D, d = col - g * D;
         float o[R];
 #pragma unroll
         for (int r = 0; r < R; ++r) o[r] = 0.0f;
-        if (half < halves) {
-            for (int t = half; t < n; t += halves) {
-                const float v = vcb[(int)vcs[(size_t)t * G + g] * D + d];
+        for (int t = half; t < n; t += halves) {
+            const float v = vcb[(int)vcs[(size_t)t * G + g] * D + d];
 #pragma unroll
-                for (int r = 0; r < R; ++r) o[r] = fmaf(sc[(size_t)t * R + r], v, o[r]);
-            }
+            for (int r = 0; r < R; ++r) o[r] = fmaf(sc[(size_t)t * R + r], v, o[r]);
         }
-        // combine the token halves in a fixed order
+        // combine the token stripes in a fixed order
         for (int hh = 0; hh < halves; ++hh) {
             if (half == hh) {
 #pragma unroll
@@ -245,25 +268,42 @@ __global__ void kvq_combine_kernel(const __grid_constant__ KvqProblem P, int R) 
 }
 
 size_t kvq_decode_smem(const KvqProblem& P, int R) {
-    return sizeof(float) * ((size_t)P.G * 256 * R + 256 * (size_t)P.D + (size_t)P.chunk * R + kKvThreads +
-                            2 * (size_t)R * P.head_dim) + (size_t)P.chunk * P.G;
+    return sizeof(float) * ((size_t)P.G * 256 * R + 256 * (size_t)P.D + 2 * (size_t)R * P.head_dim + (size_t)P.chunk * R +
+                            kKvThreads) + 2 * (size_t)P.chunk * P.G;
+}
+
+template <int D>
+static int launch_append_t(const KvqProblem& P, cudaStream_t s) {
+    const int tasks = 2 * P.Hkv * P.G, wpb = kKvThreads / 32;
+    kvq_append_kernel<D><<<dim3((tasks + wpb - 1) / wpb, P.B), kKvThreads, 0, s>>>(P);
+    OJX_CUDA_TRY(cudaGetLastError());
+    kvq_bump_kernel<<<(P.B + 127) / 128, 128, 0, s>>>(P.seq_lens, P.B, P.max_seq, P.error_flag);
+    OJX_CUDA_TRY(cudaGetLastError());
+    count_launch(2);
+    return OJX_OK;
 }
 
 int launch_kvq_append(const KvqProblem& P, cudaStream_t s) {
     if (!P.new_k || !P.new_v || !P.k_codes || !P.v_codes || !P.seq_lens) return OJX_ERR_ARG;
-    if (P.D > kKvMaxD || P.G > kKvMaxGroups) return OJX_ERR_UNSUPPORTED;
-    kvq_append_kernel<<<P.B, kKvThreads, 0, s>>>(P);
-    OJX_CUDA_TRY(cudaGetLastError());
-    count_launch(1);
-    return OJX_OK;
+    if (P.G > kKvMaxGroups) return OJX_ERR_UNSUPPORTED;
+    switch (P.D) {
+        case 4: return launch_append_t<4>(P, s);
+        case 8: return launch_append_t<8>(P, s);
+        case 16: return launch_append_t<16>(P, s);
+        default: return OJX_ERR_UNSUPPORTED;
+    }
 }
 
-template <int R>
+template <int R, int D>
 static int launch_decode_t(const KvqProblem& P, cudaStream_t s) {
     const size_t smem = kvq_decode_smem(P, R);
     if (smem > 227 * 1024) return OJX_ERR_TOO_LARGE;
-    OJX_CUDA_TRY(cudaFuncSetAttribute(kvq_decode_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kvq_decode_kernel<R><<<dim3(P.n_chunks, P.Hkv, P.B), kKvThreads, smem, s>>>(P);
+    static thread_local size_t configured = 0;  // largest opt-in made for this instantiation
+    if (smem > configured) {
+        OJX_CUDA_TRY(cudaFuncSetAttribute(kvq_decode_kernel<R, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = smem;
+    }
+    kvq_decode_kernel<R, D><<<dim3(P.n_chunks, P.Hkv, P.B), kKvThreads, smem, s>>>(P);
     OJX_CUDA_TRY(cudaGetLastError());
     kvq_combine_kernel<<<dim3(P.Hq, P.B), 128, 0, s>>>(P, R);
     OJX_CUDA_TRY(cudaGetLastError());
@@ -271,15 +311,25 @@ static int launch_decode_t(const KvqProblem& P, cudaStream_t s) {
     return OJX_OK;
 }
 
+template <int R>
+static int launch_decode_r(const KvqProblem& P, cudaStream_t s) {
+    switch (P.D) {
+        case 4: return launch_decode_t<R, 4>(P, s);
+        case 8: return launch_decode_t<R, 8>(P, s);
+        case 16: return launch_decode_t<R, 16>(P, s);
+        default: return OJX_ERR_UNSUPPORTED;
+    }
+}
+
 int launch_kvq_decode(const KvqProblem& P, cudaStream_t s) {
     if (!P.q || !P.out || !P.partials || !P.seq_lens) return OJX_ERR_ARG;
-    if (P.D > kKvMaxD || P.G > kKvMaxGroups || P.Hq % P.Hkv != 0) return OJX_ERR_UNSUPPORTED;
+    if (P.G > kKvMaxGroups || P.Hq % P.Hkv != 0) return OJX_ERR_UNSUPPORTED;
     if (P.head_dim > kKvThreads || kKvThreads % P.head_dim != 0) return OJX_ERR_UNSUPPORTED;
     switch (P.Hq / P.Hkv) {
-        case 1: return launch_decode_t<1>(P, s);
-        case 2: return launch_decode_t<2>(P, s);
-        case 4: return launch_decode_t<4>(P, s);
-        case 8: return launch_decode_t<8>(P, s);
+        case 1: return launch_decode_r<1>(P, s);
+        case 2: return launch_decode_r<2>(P, s);
+        case 4: return launch_decode_r<4>(P, s);
+        case 8: return launch_decode_r<8>(P, s);
         default: return OJX_ERR_UNSUPPORTED;
     }
 }
