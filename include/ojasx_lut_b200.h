@@ -116,6 +116,17 @@ OJASX_API int ojasx_b200_linear_forward_raw(const uint8_t* d_codes, const float*
                                             int batch_size, int io_dtype, int block_dim, int codebook_size,
                                             int rows, int columns, int row_start, int row_stop, void* stream);
 
+/* Device twin of the vtable entry rvq_fused_gemm (ojasx_24x96/native/ojasx_backend_abi.h:97-111)
+ * with the argument list of ojasx_cuda_rvq_fused_gemm (ojasx_24x96/native/vq_kernels_cuda.cu:230-245):
+ * bit-packed residual-VQ codes of any supported width (1, 2, 4, 8) and stage count, fp32 in and
+ * out, output [batch, row_stop-row_start].  8-bit single-stage layers run on the table kernels;
+ * other layouts run on a compatibility kernel.  Returns -1 for invalid arguments and -2 for an
+ * unsupported bit width, as ojasx_rvq_fused_gemm does (leech24_cpu.cpp:386-397). */
+OJASX_API int ojasx_b200_rvq_fused_gemm(const uint8_t* packed_codes, const float* codebooks, const float* row_scales,
+                                        const float* bias, const float* inputs, int batch_size, int stages,
+                                        int bits_per_stage, int block_size, int rows, int columns, int row_start,
+                                        int row_stop, float* output, void* stream);
+
 /* One launch over many independent linear handles (no counterpart in the reference, which
  * runs one layer per call): problem p reads d_x + p*x_stride_bytes and writes
  * d_y + p*y_stride_bytes.  x_stride_bytes == 0 feeds every layer the same activations

@@ -26,6 +26,7 @@ SIGNATURES = {
     "ojasx_b200_linear_forward": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "ojasx_b200_linear_forward_raw": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp,
                                            _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "ojasx_b200_rvq_fused_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "ojasx_b200_create_linear_group": (_vp, [_vp, _i]),
     "ojasx_b200_linear_group_forward": (_i, [_vp, _vp, _sz, _vp, _sz, _i, _vp]),
     "ojasx_b200_destroy_linear_group": (None, [_vp]),

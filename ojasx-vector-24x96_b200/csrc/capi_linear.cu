@@ -185,6 +185,28 @@ int ojasx_b200_linear_forward_raw(const uint8_t* d_codes, const float* d_codeboo
     return launch_linear(P, static_cast<cudaStream_t>(stream));
 }
 
+int ojasx_b200_rvq_fused_gemm(const uint8_t* packed_codes, const float* codebooks, const float* row_scales,
+                              const float* bias, const float* inputs, int batch_size, int stages, int bits_per_stage,
+                              int block_size, int rows, int columns, int row_start, int row_stop, float* output,
+                              void* stream) {
+    // Argument checks and codes of ojasx_rvq_fused_gemm (leech24_cpu.cpp:386-397).
+    if (stages <= 0 || bits_per_stage <= 0 || block_size <= 0 || rows <= 0 || columns <= 0 || row_start < 0 ||
+        row_stop <= row_start || row_stop > rows || batch_size <= 0 || !packed_codes || !codebooks || !row_scales ||
+        !inputs || !output)
+        return OJX_ERR_ARG;
+    if (bits_per_stage != 1 && bits_per_stage != 2 && bits_per_stage != 4 && bits_per_stage != 8) return OJX_ERR_RANGE;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool table_path = bits_per_stage == 8 && stages == 1 &&
+                            (block_size == 4 || block_size == 8 || block_size == 16 || block_size == 32);
+    if (table_path)
+        return ojasx_b200_linear_forward_raw(packed_codes, codebooks, row_scales, bias, 0, nullptr, nullptr, nullptr, inputs,
+                                             output, batch_size, OJX_F32, block_size, 256, rows, columns, row_start,
+                                             row_stop, stream);
+    if (stages > 8) return OJX_ERR_ARG;
+    return launch_rvq_generic(packed_codes, codebooks, row_scales, bias, inputs, batch_size, stages, bits_per_stage,
+                              block_size, rows, columns, row_start, row_stop, output, s);
+}
+
 int ojasx_linear_forward(OjasxLinearHandle handle, const float* x, float* y, int batch_size, int num_threads) {
     (void)num_threads;
     if (!handle || !x || !y) return OJX_ERR_ARG;  // ojasx_lut_c_api.cpp:100

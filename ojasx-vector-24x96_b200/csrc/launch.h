@@ -13,6 +13,11 @@ int launch_linear_group(const LinearProblem* d_probs, int nprobs, int total_item
 // --- linear_cluster.cu: OJX_ERR_UNSUPPORTED means "use the persistent kernel"
 int try_launch_linear_cluster(const LinearProblem& P, cudaStream_t stream);
 
+// --- rvq_generic.cu
+int launch_rvq_generic(const uint8_t* packed, const float* codebooks, const float* row_scales, const float* bias,
+                       const float* x, int batch, int stages, int bits, int D, int rows, int columns, int row_start,
+                       int row_stop, float* out, cudaStream_t stream);
+
 // --- moe.cu
 int launch_moe_experts(MoeProblem P, cudaStream_t stream);
 int launch_moe_router(const float* Wr, const void* x, int io_dtype, int n_tokens, int H, int E, int k,

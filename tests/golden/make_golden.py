@@ -98,6 +98,10 @@ def kv_legacy_inputs():
             rng.standard_normal(128).astype(np.float32))
 
 
+def pack_case(bits):
+    return np.random.default_rng(40 + bits).integers(0, 1 << bits, size=1003, dtype=np.int64)
+
+
 def main():
     ref = O.RefLib()
     assert ref.backend() == "Portable_ANSI_C20", ref.backend()
@@ -123,6 +127,13 @@ def main():
     for D in (16, 8):
         out[f"kv_legacy/d{D}/out"] = ref.kv_run(ks, vs, q, block_dim=D)
     out["kv_legacy/sha"] = np.array(digest(ks, vs, q))
+    # bit-packing of the package container (ojasx_24x96/codec.py:176-214), from the reference's own Python
+    sys.path.insert(0, "/root/reference")
+    import torch
+    from ojasx_24x96.codec import pack_codes as ref_pack
+    for bits in (1, 2, 4, 8):
+        codes = torch.from_numpy(pack_case(bits))
+        out[f"pack/bits{bits}"] = ref_pack(codes, bits).numpy()
     np.savez_compressed(OUT, **out)
     print("wrote", OUT, os.path.getsize(OUT), "bytes,", len(out), "arrays")
 

@@ -167,3 +167,14 @@ def test_fp32_order_versus_exact_sum(oracle):
     assert np.abs(y - f).max() < 5e-5
     viol = int(np.sum(np.abs(y - f) > 1e-6 + 1e-5 * np.abs(f)))
     assert viol > 0  # a result rounded differently from the reference would miss the 1e-5/1e-6 bar here
+
+
+def test_pack_codes_matches_reference_bit_layout():
+    """codec.pack_codes / unpack_codes against bytes produced by the reference's own pack_codes."""
+    from ojasx_b200 import codec
+    for bits in (1, 2, 4, 8):
+        codes = torch.from_numpy(mg.pack_case(bits))
+        packed = codec.pack_codes(codes, bits)
+        assert np.array_equal(packed.numpy(), GOLD[f"pack/bits{bits}"])
+        assert torch.equal(codec.unpack_codes(packed, bits, codes.numel()).long(), codes)
+    assert codec.pack_codes(torch.tensor([1, 2, 3, 0]), 2).tolist() == [0b00111001]
