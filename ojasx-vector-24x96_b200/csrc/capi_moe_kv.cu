@@ -16,7 +16,7 @@ MoeHandle::~MoeHandle() {
     DeviceGuard g(dev);
     cudaFree(cb_in); cudaFree(cb_down); cudaFree(gu_codes); cudaFree(gu_scales); cudaFree(dn_codes); cudaFree(dn_scales);
     for (int i = 0; i < 2; ++i) { cudaFree(csr_rp[i]); cudaFree(csr_cols[i]); cudaFree(csr_vals[i]); }
-    cudaFree(router); cudaFree(scratch); cudaFree(route_scratch); cudaFree(stage);
+    cudaFree(router); cudaFree(scratch); cudaFree(lut_scratch); cudaFree(route_scratch); cudaFree(stage);
     if (stream) cudaStreamDestroy(stream);
 }
 
@@ -25,6 +25,11 @@ int MoeHandle::reserve(int n_tokens, int k) {
     const size_t need = sizeof(float) * pairs * ((size_t)I + H);
     int rc = ensure_capacity(&scratch, &scratch_cap, need);
     if (rc != OJX_OK) return rc;
+    // Token tables [n_tokens, G, 256] fp32, shared by the k experts of a token (up to 1 GiB).
+    const size_t lut_need = sizeof(float) * (size_t)n_tokens * (H / D) * 256;
+    if (lut_need <= ((size_t)1 << 30)) {
+        if ((rc = ensure_capacity(&lut_scratch, &lut_cap, lut_need)) != OJX_OK) return rc;
+    }
     if (router) {
         const size_t rneed = sizeof(float) * (size_t)n_tokens * 2 * E_total + pairs * (sizeof(int) + sizeof(float));
         rc = ensure_capacity(&route_scratch, &route_cap, rneed);
@@ -39,6 +44,8 @@ MoeProblem MoeHandle::problem(const void* x, void* y, const int* idx, const floa
     P.dn_codes = dn_codes; P.dn_scales = dn_scales;
     P.gu_csr = CsrView{csr_rp[0], csr_cols[0], csr_vals[0], csr_nnz[0]};
     P.dn_csr = CsrView{csr_rp[1], csr_cols[1], csr_vals[1], csr_nnz[1]};
+    const size_t lut_need = sizeof(float) * (size_t)n_tokens * (H / D) * 256;
+    P.lut_in = (lut_scratch && lut_cap >= lut_need) ? static_cast<const float*>(lut_scratch) : nullptr;
     P.inter = static_cast<float*>(scratch);
     P.expert_out = P.inter + (size_t)n_tokens * k * I;
     P.n_tokens = n_tokens; P.k_active = k; P.E = E; P.expert_offset = expert_offset;

@@ -65,6 +65,7 @@ struct MoeProblem {
     const float* dn_scales;   // [E, H] or null
     CsrView gu_csr;           // rows of the flattened [E*2I, H] matrix
     CsrView dn_csr;           // rows of the flattened [E*H, I] matrix
+    const float* lut_in;      // optional scratch [n_tokens, G, 256]: tables of the tokens, built once per token
     float* inter;             // scratch [pairs, I]
     float* expert_out;        // scratch [pairs, H]
     int n_tokens, k_active;

@@ -76,6 +76,8 @@ struct MoeHandle {
     float* router = nullptr;                 // [E_total, H]
     void* scratch = nullptr;                 // inter [pairs, I] + expert_out [pairs, H]
     size_t scratch_cap = 0;
+    void* lut_scratch = nullptr;             // token tables [tokens, G, 256]
+    size_t lut_cap = 0;
     void* route_scratch = nullptr;           // logits, probs [tokens, E_total], idx, w [pairs]
     size_t route_cap = 0;
     void* stage = nullptr;                   // host-pointer forward staging

@@ -149,9 +149,25 @@ struct RowWalker {
     // (The packed fp32x2 forms of sm_100 are not used: ptxas contracts a packed mul.rn + add.rn
     // pair into one FMA -- 76 % of 8-term dot products changed in a direct test -- also when
     // they are spelled as a*b+(-0) and a*1+b, and that changes table values.)
-    __device__ __forceinline__ void build_slice(int s, const XLoad& xl, const float (&c)[D], int Kcb) const {
+    __device__ __forceinline__ void build_slice(int s, const XLoad& xl, const float (&c)[D], int Kcb,
+                                                const float* __restrict__ prebuilt) const {
         constexpr int U = 4;
         const int g0 = s * SG, ng = slice_ng(s);
+        if (prebuilt) {
+            // The table of this activation vector was built once by lut_prebuild_kernel (same
+            // arithmetic, so the same bits); copy this slice of it, 16 bytes per thread per step.
+            const float4* src = reinterpret_cast<const float4*>(prebuilt + (size_t)g0 * 256);
+            float4* dst = reinterpret_cast<float4*>(sm.lut);
+            const int n4 = ng * 64;
+            int i = threadIdx.x;
+            for (; i + 3 * kThreads < n4; i += 4 * kThreads) {
+                const float4 a = src[i], b = src[i + kThreads], c4 = src[i + 2 * kThreads], d4 = src[i + 3 * kThreads];
+                dst[i] = a; dst[i + kThreads] = b; dst[i + 2 * kThreads] = c4; dst[i + 3 * kThreads] = d4;
+            }
+            for (; i < n4; i += kThreads) dst[i] = src[i];
+            __syncthreads();
+            return;
+        }
         for (int i = threadIdx.x; i < ng * D; i += kThreads) sm.xs[i] = xl(g0 * D + i);
         __syncthreads();
         const int kc = threadIdx.x & 255;
@@ -219,7 +235,8 @@ struct RowWalker {
     // runs once, right after the table of the last slice is built (used to ask L2 for the data
     // the epilogue will want).
     template <class F>
-    __device__ void run(const XLoad& xl, const float* __restrict__ codebook, int Kcb, F before_last) const {
+    __device__ void run(const XLoad& xl, const float* __restrict__ codebook, int Kcb, F before_last,
+                        const float* __restrict__ prebuilt = nullptr) const {
         float c[D];
         {
             const int kc = threadIdx.x & 255;
@@ -237,7 +254,7 @@ struct RowWalker {
         }
         for (int s = 0; s < nslices; ++s) {
             __syncthreads();  // every warp has left the previous slice's table (and sm.xs)
-            build_slice(s, xl, c, Kcb);
+            build_slice(s, xl, c, Kcb, prebuilt);
             if (s == nslices - 1) before_last();
             const int nch = slice_chunks(s);
             for (int rb = warp; rb < nrb; rb += kWarps) {
@@ -259,6 +276,32 @@ struct RowWalker {
         cp_async_wait<0>();
     }
 };
+
+// Whole table of one activation vector, built once and shared by every work item that uses that
+// vector (the routed experts of a token): out[t, g, k] with the arithmetic of build_slice.
+// grid = (ceil(G / 16), n_vectors), 256 threads (thread = centroid).
+template <int D>
+__global__ void __launch_bounds__(256) lut_prebuild_kernel(const void* __restrict__ x, int io_dtype, int K, int G,
+                                                           const float* __restrict__ codebook, int Kcb,
+                                                           float* __restrict__ out) {
+    __shared__ float xs[16 * D];
+    const int t = blockIdx.y, g0 = blockIdx.x * 16, ng = min(16, G - g0), kc = threadIdx.x;
+    const size_t esz = io_dtype == OJX_BF16 ? 2 : 4;
+    const XLoad xl{static_cast<const char*>(x) + (size_t)t * K * esz, K, io_dtype};
+    for (int i = threadIdx.x; i < ng * D; i += 256) xs[i] = xl(g0 * D + i);
+    float c[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) c[d] = kc < Kcb ? codebook[kc * D + d] : 0.0f;
+    __syncthreads();
+    float* o = out + ((size_t)t * G + g0) * 256 + kc;
+    for (int gl = 0; gl < ng; ++gl) {
+        const float* xg = xs + gl * D;
+        float dot = __fmul_rn(xg[0], c[0]);
+#pragma unroll
+        for (int d = 1; d < D; ++d) dot = __fadd_rn(dot, __fmul_rn(xg[d], c[d]));
+        o[(size_t)gl * 256] = kc < Kcb ? dot : 0.0f;
+    }
+}
 
 // CSR outlier row sums for the rows [row0, row0+n) of a work item, reference order
 // (ojasx_lut_cpu.cpp:117-126): acc = 0; j ascending; acc += val * x[col], multiply then add.

@@ -69,7 +69,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) moe_gate_up_kernel(const
                 csr_prefetch_l2(P.gu_csr, (int)(row0 + i0), n);
                 csr_prefetch_l2(P.gu_csr, (int)(row0 + P.I + i0), n);
             }
-        });
+        }, P.lut_in ? P.lut_in + (size_t)pr.token * P.G * 256 : nullptr);
         __syncthreads();
         if (P.gu_csr.nnz > 0) {
             csr_rows_to_smem(sm, P.gu_csr, (int)(row0 + i0), n, 0, xl);
@@ -242,6 +242,13 @@ static int launch_moe_experts_t(const MoeProblem& P, cudaStream_t s) {
     if ((rc = set_smem(moe_down_kernel<D>)) != OJX_OK) return rc;
     const int pairs = P.n_tokens * P.k_active, sms = kCtasPerSm * num_sms();
     const int gu_items = pairs * P.gu_tiles, dn_items = pairs * P.dn_tiles;
+    int extra = 0;
+    if (P.lut_in) {
+        lut_prebuild_kernel<D><<<dim3((P.G + 15) / 16, P.n_tokens), 256, 0, s>>>(P.x, P.io_dtype, P.H, P.G, P.cb_in, P.Kcb,
+                                                                                const_cast<float*>(P.lut_in));
+        OJX_CUDA_TRY(cudaGetLastError());
+        extra = 1;
+    }
     moe_gate_up_kernel<D><<<gu_items < sms ? gu_items : sms, kThreads, sizeof(CoreSmem), s>>>(P);
     OJX_CUDA_TRY(cudaGetLastError());
     moe_down_kernel<D><<<dn_items < sms ? dn_items : sms, kThreads, sizeof(CoreSmem), s>>>(P);
@@ -249,7 +256,7 @@ static int launch_moe_experts_t(const MoeProblem& P, cudaStream_t s) {
     const int n = P.n_tokens * P.H;
     moe_combine_kernel<<<(n + 255) / 256, 256, 0, s>>>(P);
     OJX_CUDA_TRY(cudaGetLastError());
-    count_launch(3);
+    count_launch(3 + extra);
     return OJX_OK;
 }
 
@@ -337,6 +344,7 @@ extern "C" int ojasx_b200_moe_forward_noalloc(OjasxMoEHandle handle, const void*
     // Nothing in the scratch has to start at zero: every (pair, index) slot that a later stage
     // reads was written by the stage before it in this same call, and slots of skipped pairs are
     // never read.  What an earlier call left there is therefore harmless.
+    P.lut_in = nullptr;  // tables are rebuilt inside the gate/up kernel: no further scratch
     P.inter = scratch;
     P.expert_out = scratch + (size_t)n_tokens * k_active * h->I;
     return launch_moe_experts(P, static_cast<cudaStream_t>(stream));
