@@ -22,7 +22,7 @@ MoeHandle::~MoeHandle() {
 
 int MoeHandle::reserve(int n_tokens, int k) {
     const size_t pairs = (size_t)n_tokens * k;
-    const size_t need = sizeof(float) * pairs * ((size_t)I + H);
+    const size_t need = sizeof(float) * pairs * ((size_t)I + H) + sizeof(int) * (pairs + 1);
     int rc = ensure_capacity(&scratch, &scratch_cap, need);
     if (rc != OJX_OK) return rc;
     // Token tables [n_tokens, G, 256] fp32, shared by the k experts of a token (up to 1 GiB).
@@ -48,6 +48,8 @@ MoeProblem MoeHandle::problem(const void* x, void* y, const int* idx, const floa
     P.lut_in = (lut_scratch && lut_cap >= lut_need) ? static_cast<const float*>(lut_scratch) : nullptr;
     P.inter = static_cast<float*>(scratch);
     P.expert_out = P.inter + (size_t)n_tokens * k * I;
+    P.pair_list = reinterpret_cast<const int*>(P.expert_out + (size_t)n_tokens * k * H);
+    P.E_total = E_total;
     P.n_tokens = n_tokens; P.k_active = k; P.E = E; P.expert_offset = expert_offset;
     P.H = H; P.I = I; P.G = H / D; P.Gi = I / D; P.D = D; P.Kcb = 256; P.io_dtype = io;
     return P;

@@ -66,10 +66,13 @@ struct MoeProblem {
     CsrView gu_csr;           // rows of the flattened [E*2I, H] matrix
     CsrView dn_csr;           // rows of the flattened [E*H, I] matrix
     const float* lut_in;      // optional scratch [n_tokens, G, 256]: tables of the tokens, built once per token
+    const int* pair_list;     // optional scratch [pairs + 1]: [0] = number of pairs this handle evaluates, then
+                              // their ids grouped by expert; null = every pair is visited and skipped if not local
     float* inter;             // scratch [pairs, I]
     float* expert_out;        // scratch [pairs, H]
     int n_tokens, k_active;
     int E;                    // experts held by this handle
+    int E_total;              // experts the router scores (>= E)
     int expert_offset;        // global id of local expert 0 (expert-parallel shards)
     int H, I, G, Gi, D, Kcb;
     int io_dtype;

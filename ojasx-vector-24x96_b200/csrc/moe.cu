@@ -45,10 +45,11 @@ template <int D>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm) moe_gate_up_kernel(const __grid_constant__ MoeProblem P) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     CoreSmem& sm = *reinterpret_cast<CoreSmem*>(smem_raw);
-    const int total = P.n_tokens * P.k_active * P.gu_tiles;
+    const int total = (P.pair_list ? P.pair_list[0] : P.n_tokens * P.k_active) * P.gu_tiles;
     const size_t esz = P.io_dtype == OJX_BF16 ? 2 : 4;
     for (int item = blockIdx.x; item < total; item += gridDim.x) {
-        const int pair = item / P.gu_tiles, tile = item - pair * P.gu_tiles;
+        const int slot = item / P.gu_tiles, tile = item - slot * P.gu_tiles;
+        const int pair = P.pair_list ? P.pair_list[1 + slot] : slot;
         const MoePair pr = decode_pair(P, pair);
         if (pr.expert < 0) continue;  // uniform across the CTA
         const int i0 = tile * P.gu_tile, n = min(P.gu_tile, P.I - i0);
@@ -93,9 +94,10 @@ template <int D>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm) moe_down_kernel(const __grid_constant__ MoeProblem P) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     CoreSmem& sm = *reinterpret_cast<CoreSmem*>(smem_raw);
-    const int total = P.n_tokens * P.k_active * P.dn_tiles;
+    const int total = (P.pair_list ? P.pair_list[0] : P.n_tokens * P.k_active) * P.dn_tiles;
     for (int item = blockIdx.x; item < total; item += gridDim.x) {
-        const int pair = item / P.dn_tiles, tile = item - pair * P.dn_tiles;
+        const int slot = item / P.dn_tiles, tile = item - slot * P.dn_tiles;
+        const int pair = P.pair_list ? P.pair_list[1 + slot] : slot;
         const MoePair pr = decode_pair(P, pair);
         if (pr.expert < 0) continue;
         const int h0 = tile * P.dn_tile, n = min(P.dn_tile, P.H - h0);
@@ -122,6 +124,32 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) moe_down_kernel(const __
             P.expert_out[(size_t)pair * P.H + h0 + lr] = v;
         }
         __syncthreads();
+    }
+}
+
+// Work list of one forward: the (token, expert) pairs this handle evaluates -- expert held here,
+// |w| >= 1e-8 -- grouped by expert so that pairs of one expert run close together in time and
+// share its code rows in L2, and so that every CTA of the expert kernels gets real work (with
+// expert-parallel shards most routed pairs belong to other ranks).  One CTA; a counting sort on
+// the local expert id.  list[0] = count, list[1..] = pair ids.
+__global__ void __launch_bounds__(1024) moe_plan_kernel(const __grid_constant__ MoeProblem P, int* __restrict__ list) {
+    extern __shared__ int hist[];  // [E + 1]
+    const int pairs = P.n_tokens * P.k_active;
+    for (int e = threadIdx.x; e <= P.E; e += blockDim.x) hist[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = decode_pair(P, p).expert;
+        if (e >= 0) atomicAdd(&hist[e + 1], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int e = 0; e < P.E; ++e) hist[e + 1] += hist[e];  // hist[e] = first slot of expert e
+        list[0] = hist[P.E];
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = decode_pair(P, p).expert;
+        if (e >= 0) list[1 + atomicAdd(&hist[e], 1)] = p;
     }
 }
 
@@ -243,11 +271,18 @@ static int launch_moe_experts_t(const MoeProblem& P, cudaStream_t s) {
     const int pairs = P.n_tokens * P.k_active, sms = kCtasPerSm * num_sms();
     const int gu_items = pairs * P.gu_tiles, dn_items = pairs * P.dn_tiles;
     int extra = 0;
+    if (P.pair_list) {
+        const size_t hs = sizeof(int) * ((size_t)P.E + 1);
+        if (hs > 48 * 1024) OJX_CUDA_TRY(cudaFuncSetAttribute(moe_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hs));
+        moe_plan_kernel<<<1, 1024, hs, s>>>(P, const_cast<int*>(P.pair_list));
+        OJX_CUDA_TRY(cudaGetLastError());
+        ++extra;
+    }
     if (P.lut_in) {
         lut_prebuild_kernel<D><<<dim3((P.G + 15) / 16, P.n_tokens), 256, 0, s>>>(P.x, P.io_dtype, P.H, P.G, P.cb_in, P.Kcb,
                                                                                 const_cast<float*>(P.lut_in));
         OJX_CUDA_TRY(cudaGetLastError());
-        extra = 1;
+        ++extra;
     }
     moe_gate_up_kernel<D><<<gu_items < sms ? gu_items : sms, kThreads, sizeof(CoreSmem), s>>>(P);
     OJX_CUDA_TRY(cudaGetLastError());
@@ -264,8 +299,10 @@ int launch_moe_experts(MoeProblem P, cudaStream_t s) {
     if (!P.x || !P.y || !P.topk_idx || !P.topk_w || !P.inter || !P.expert_out) return OJX_ERR_ARG;
     if (P.n_tokens <= 0 || P.k_active <= 0) return OJX_ERR_ARG;
     const int pairs = P.n_tokens * P.k_active, sms = kCtasPerSm * num_sms();
-    // Tiles: spread few pairs over the SMs, keep tiles whole when there are many pairs.
-    int want = (sms + pairs - 1) / pairs;
+    // Tiles: spread few pairs over the SMs, keep tiles whole when there are many pairs.  An
+    // expert-parallel shard expects only its share of the routed pairs.
+    const int expect = P.E_total > P.E ? (int)(((long long)pairs * P.E + P.E_total - 1) / P.E_total) : pairs;
+    int want = (sms + expect - 1) / (expect > 0 ? expect : 1);
     P.gu_tile = round_up((P.I + want - 1) / want, 16);
     if (P.gu_tile > kAccRows / 2) P.gu_tile = kAccRows / 2;
     P.gu_tiles = (P.I + P.gu_tile - 1) / P.gu_tile;
@@ -345,6 +382,7 @@ extern "C" int ojasx_b200_moe_forward_noalloc(OjasxMoEHandle handle, const void*
     // reads was written by the stage before it in this same call, and slots of skipped pairs are
     // never read.  What an earlier call left there is therefore harmless.
     P.lut_in = nullptr;  // tables are rebuilt inside the gate/up kernel: no further scratch
+    P.pair_list = nullptr;  // every pair is visited in order and skipped if it is not evaluated here
     P.inter = scratch;
     P.expert_out = scratch + (size_t)n_tokens * k_active * h->I;
     return launch_moe_experts(P, static_cast<cudaStream_t>(stream));
