@@ -133,23 +133,52 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) moe_down_kernel(const __
 // expert-parallel shards most routed pairs belong to other ranks).  One CTA; a counting sort on
 // the local expert id.  list[0] = count, list[1..] = pair ids.
 __global__ void __launch_bounds__(1024) moe_plan_kernel(const __grid_constant__ MoeProblem P, int* __restrict__ list) {
-    extern __shared__ int hist[];  // [E + 1]
+    extern __shared__ int plan_smem[];
+    int* cnt = plan_smem;          // [E] pairs per local expert
+    int* start = plan_smem + P.E;  // [E] next free slot of the expert
+    __shared__ int warp_tot[32];
     const int pairs = P.n_tokens * P.k_active;
-    for (int e = threadIdx.x; e <= P.E; e += blockDim.x) hist[e] = 0;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    for (int e = threadIdx.x; e < P.E; e += blockDim.x) cnt[e] = 0;
     __syncthreads();
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
         const int e = decode_pair(P, p).expert;
-        if (e >= 0) atomicAdd(&hist[e + 1], 1);
+        if (e >= 0) atomicAdd(&cnt[e], 1);
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        for (int e = 0; e < P.E; ++e) hist[e + 1] += hist[e];  // hist[e] = first slot of expert e
-        list[0] = hist[P.E];
+    // exclusive prefix: each thread owns a contiguous run of experts; warp-shuffle scans join the runs
+    const int per = (P.E + (int)blockDim.x - 1) / (int)blockDim.x;
+    const int lo = min(P.E, (int)threadIdx.x * per), hi = min(P.E, lo + per);
+    int run = 0;
+    for (int e = lo; e < hi; ++e) run += cnt[e];
+    int inc = run;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, inc, off);
+        if (lane >= off) inc += v;
     }
+    if (lane == 31) warp_tot[wid] = inc;
+    __syncthreads();
+    if (wid == 0) {
+        int t = lane < nwarp ? warp_tot[lane] : 0;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, t, off);
+            if (lane >= off) t += v;
+        }
+        warp_tot[lane] = t;
+    }
+    __syncthreads();
+    int base = inc - run + (wid > 0 ? warp_tot[wid - 1] : 0);
+    for (int e = lo; e < hi; ++e) {
+        start[e] = base;
+        base += cnt[e];
+    }
+    if (threadIdx.x == 0) list[0] = warp_tot[nwarp - 1];
     __syncthreads();
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
         const int e = decode_pair(P, p).expert;
-        if (e >= 0) list[1 + atomicAdd(&hist[e], 1)] = p;
+        if (e >= 0) list[1 + atomicAdd(&start[e], 1)] = p;
     }
 }
 
@@ -159,10 +188,19 @@ __global__ void moe_combine_kernel(const __grid_constant__ MoeProblem P) {
     if (idx >= P.n_tokens * P.H) return;
     const int t = idx / P.H, h = idx - t * P.H;
     float y = 0.0f;
-    for (int k = 0; k < P.k_active; ++k) {
-        const int pair = t * P.k_active + k;
-        if (decode_pair(P, pair).expert < 0) continue;
-        y = __fadd_rn(y, __fmul_rn(P.expert_out[(size_t)pair * P.H + h], P.topk_w[pair]));
+    for (int k0 = 0; k0 < P.k_active; k0 += 8) {  // eight loads in flight, additions in caller order
+        float v[8], w[8];
+        bool ok[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int k = k0 + u, pair = t * P.k_active + k;
+            ok[u] = k < P.k_active && decode_pair(P, pair).expert >= 0;
+            v[u] = ok[u] ? P.expert_out[(size_t)pair * P.H + h] : 0.0f;
+            w[u] = ok[u] ? P.topk_w[pair] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (ok[u]) y = __fadd_rn(y, __fmul_rn(v[u], w[u]));
     }
     if (P.io_dtype == OJX_BF16) reinterpret_cast<__nv_bfloat16*>(P.y)[idx] = __float2bfloat16_rn(y);
     else reinterpret_cast<float*>(P.y)[idx] = y;
@@ -184,76 +222,76 @@ __global__ void __launch_bounds__(256) moe_router_logits_kernel(const float* __r
     for (int t = blockIdx.y; t < n_tokens; t += gridDim.y) {
         const XLoad xl{static_cast<const char*>(x) + (size_t)t * H * esz, H, io_dtype};
         float part = 0.0f;
-        for (int c = lane; c < H; c += 32) part = __fadd_rn(part, __fmul_rn(w[c], xl(c)));
+        int c = lane;
+        for (; c + 7 * 32 < H; c += 8 * 32) {  // eight loads in flight, additions still in column order
+            float wv[8], xv[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) { wv[u] = w[c + 32 * u]; xv[u] = xl(c + 32 * u); }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) part = __fadd_rn(part, __fmul_rn(wv[u], xv[u]));
+        }
+        for (; c < H; c += 32) part = __fadd_rn(part, __fmul_rn(w[c], xl(c)));
 #pragma unroll
         for (int off = 16; off >= 1; off >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, off));
         if (lane == 0) logits[(size_t)t * E + warp] = part;
     }
 }
 
-// One CTA per token: softmax over E logits, k rounds of arg-max (ties to the lower index),
-// renormalise.  The normaliser and the weight sum are accumulated sequentially in fp32 so the
-// result does not depend on the thread count.
-__global__ void __launch_bounds__(256) moe_router_topk_kernel(const float* __restrict__ logits, int E, int k,
-                                                              int* __restrict__ idx_out, float* __restrict__ w_out,
-                                                              float* __restrict__ probs /* [n_tokens, E] scratch */) {
-    __shared__ float red_v[256];
-    __shared__ int red_i[256];
-    __shared__ float s_bcast;
-    const int t = blockIdx.x, tid = threadIdx.x;
+// One warp per token: softmax over E logits, k rounds of arg-max (ties to the lower index),
+// renormalise.  The probabilities live in the warp's slice of shared memory.  The normaliser and
+// the weight sum are accumulated sequentially in fp32 (lane 0), so the result does not depend on
+// the thread count; max and arg-max are order-independent.
+constexpr int kTopkWarps = 4;
+
+__global__ void __launch_bounds__(kTopkWarps * 32) moe_router_topk_kernel(const float* __restrict__ logits, int n_tokens, int E,
+                                                                         int k, int* __restrict__ idx_out,
+                                                                         float* __restrict__ w_out,
+                                                                         float* __restrict__ probs /* [n_tokens, E] scratch */) {
+    extern __shared__ float topk_smem[];  // [kTopkWarps][E]
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int t = blockIdx.x * kTopkWarps + wid;
+    if (t >= n_tokens) return;
+    float* p = topk_smem + (size_t)wid * E;
     const float* l = logits + (size_t)t * E;
-    float* p = probs + (size_t)t * E;
     float m = -INFINITY;
-    for (int e = tid; e < E; e += blockDim.x) m = fmaxf(m, l[e]);
-    red_v[tid] = m;
-    __syncthreads();
-    for (int s = blockDim.x / 2; s > 0; s >>= 1) {
-        if (tid < s) red_v[tid] = fmaxf(red_v[tid], red_v[tid + s]);
-        __syncthreads();
-    }
-    m = red_v[0];
-    __syncthreads();
-    for (int e = tid; e < E; e += blockDim.x) p[e] = (float)exp((double)__fsub_rn(l[e], m));
-    __syncthreads();
-    if (tid == 0) {
-        float s = 0.0f;
+    for (int e = lane; e < E; e += 32) { const float v = l[e]; p[e] = v; m = fmaxf(m, v); }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    for (int e = lane; e < E; e += 32) p[e] = (float)exp((double)__fsub_rn(p[e], m));
+    __syncwarp();
+    float s = 0.0f;
+    if (lane == 0)
         for (int e = 0; e < E; ++e) s = __fadd_rn(s, p[e]);
-        s_bcast = s;
+    s = __shfl_sync(0xffffffffu, s, 0);
+    for (int e = lane; e < E; e += 32) {
+        const float v = __fdiv_rn(p[e], s);
+        p[e] = v;
+        probs[(size_t)t * E + e] = v;
     }
-    __syncthreads();
-    const float s = s_bcast;
-    for (int e = tid; e < E; e += blockDim.x) p[e] = __fdiv_rn(p[e], s);
-    __syncthreads();
+    __syncwarp();
+    float ws = 0.0f;
     for (int r = 0; r < k; ++r) {
         float bv = -INFINITY;
         int bi = 0x7fffffff;
-        for (int e = tid; e < E; e += blockDim.x) {
+        for (int e = lane; e < E; e += 32) {
             const float v = p[e];
-            if (v > bv) { bv = v; bi = e; }  // ascending e per thread keeps the lowest index on ties
+            if (v > bv) { bv = v; bi = e; }  // ascending e per lane keeps the lowest index on ties
         }
-        red_v[tid] = bv;
-        red_i[tid] = bi;
-        __syncthreads();
-        for (int st = blockDim.x / 2; st > 0; st >>= 1) {
-            if (tid < st) {
-                const float ov = red_v[tid + st];
-                const int oi = red_i[tid + st];
-                if (ov > red_v[tid] || (ov == red_v[tid] && oi < red_i[tid])) { red_v[tid] = ov; red_i[tid] = oi; }
-            }
-            __syncthreads();
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
         }
-        if (tid == 0) {
-            idx_out[(size_t)t * k + r] = red_i[0];
-            w_out[(size_t)t * k + r] = red_v[0];
-            p[red_i[0]] = -1.0f;  // taken (probabilities are >= 0)
+        if (lane == 0) {
+            idx_out[(size_t)t * k + r] = bi;
+            w_out[(size_t)t * k + r] = bv;
+            p[bi] = -1.0f;  // taken (probabilities are >= 0)
         }
-        __syncthreads();
+        ws = __fadd_rn(ws, bv);  // same value in every lane, selection order
+        __syncwarp();
     }
-    if (tid == 0) {
-        float ws = 0.0f;
-        for (int r = 0; r < k; ++r) ws = __fadd_rn(ws, w_out[(size_t)t * k + r]);
-        for (int r = 0; r < k; ++r) w_out[(size_t)t * k + r] = __fdiv_rn(w_out[(size_t)t * k + r], ws);
-    }
+    for (int r = lane; r < k; r += 32) w_out[(size_t)t * k + r] = __fdiv_rn(w_out[(size_t)t * k + r], ws);
 }
 
 // ------------------------------------------------------------------------------- host side
@@ -272,7 +310,7 @@ static int launch_moe_experts_t(const MoeProblem& P, cudaStream_t s) {
     const int gu_items = pairs * P.gu_tiles, dn_items = pairs * P.dn_tiles;
     int extra = 0;
     if (P.pair_list) {
-        const size_t hs = sizeof(int) * ((size_t)P.E + 1);
+        const size_t hs = sizeof(int) * 2 * (size_t)P.E;
         if (hs > 48 * 1024) OJX_CUDA_TRY(cudaFuncSetAttribute(moe_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hs));
         moe_plan_kernel<<<1, 1024, hs, s>>>(P, const_cast<int*>(P.pair_list));
         OJX_CUDA_TRY(cudaGetLastError());
@@ -326,7 +364,10 @@ int launch_moe_router(const float* Wr, const void* x, int io_dtype, int n_tokens
     const dim3 lgrid((E + warps_per_block - 1) / warps_per_block, n_tokens < 32 ? n_tokens : 32);
     moe_router_logits_kernel<<<lgrid, 256, 0, s>>>(Wr, x, io_dtype, n_tokens, H, E, logits);
     OJX_CUDA_TRY(cudaGetLastError());
-    moe_router_topk_kernel<<<n_tokens, 256, 0, s>>>(logits, E, k, idx_out, w_out, probs);
+    const size_t tsm = sizeof(float) * kTopkWarps * (size_t)E;
+    if (tsm > 200 * 1024) return OJX_ERR_TOO_LARGE;
+    if (tsm > 48 * 1024) OJX_CUDA_TRY(cudaFuncSetAttribute(moe_router_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tsm));
+    moe_router_topk_kernel<<<(n_tokens + kTopkWarps - 1) / kTopkWarps, kTopkWarps * 32, tsm, s>>>(logits, n_tokens, E, k, idx_out, w_out, probs);
     OJX_CUDA_TRY(cudaGetLastError());
     count_launch(2);
     return OJX_OK;
