@@ -106,6 +106,19 @@ OJASX_API unsigned long long ojasx_b200_launch_count(void);
 OJASX_API int ojasx_b200_linear_forward(OjasxLinearHandle handle, const void* d_x, void* d_y, int batch_size,
                                         int io_dtype, int row_start, int row_stop, void* stream);
 
+/* The same layer on the tensor cores (tcgen05): bf16 d_x [batch, in] and d_y [batch, row_stop-row_start],
+ * weights dequantised tile by tile into shared memory (rounded to bf16), fp32 accumulation.  No
+ * counterpart in the reference (its GPU kernels are CUDA-core GEMVs, ojasx_lut_cuda.cu:59-87).
+ * Results follow the bf16-activation tolerance (rel 2e-2), not the bit-exact order of the table
+ * kernels.  ojasx_b200_linear_forward picks this path by itself for bf16 batches >= 32
+ * (OJASX_B200_TENSOR_MIN_BATCH overrides; 0 disables).  Needs block_dim 8, 256 centroids,
+ * in_features % 64 == 0 and CSR columns ascending inside each row; otherwise -4. */
+OJASX_API int ojasx_b200_linear_forward_tensor(OjasxLinearHandle handle, const void* d_x, void* d_y, int batch_size,
+                                               int row_start, int row_stop, void* stream);
+/* 1 if a tensor-core launch since the last call gave up on a bounded barrier wait (its output is then
+ * invalid), 0 otherwise; synchronises the device.  Negative = CUDA error. */
+OJASX_API int ojasx_b200_take_device_error(void);
+
 /* Same computation on borrowed device arrays, no handle: the device twin of
  * ojasx_cuda_rvq_fused_gemm (ojasx_24x96/native/vq_kernels_cuda.cu:230-258) for the
  * 8-bit single-stage layout, plus the CSR outliers of ojasx_set_linear_outliers. */
@@ -164,6 +177,12 @@ OJASX_API int ojasx_b200_moe_route(OjasxMoEHandle handle, const void* d_x, int n
 /* Router followed by the experts, one stream, no host round trip. */
 OJASX_API int ojasx_b200_moe_forward_routed(OjasxMoEHandle handle, const void* d_x, void* d_y, int n_tokens, int top_k,
                                             int io_dtype, void* stream);
+
+/* out[i] = silu(gate[i]) * up[i] on device arrays of io_dtype: the SwiGLU step between the gate/up and
+ * down linears of a dense VQ MLP block, with the silu of the expert kernels
+ * (v / (1 + exp(-v)), ojasx_lut_cpu.cpp:209-211; :325 for the product). */
+OJASX_API int ojasx_b200_silu_mul(const void* d_gate, const void* d_up, void* d_out, size_t count, int io_dtype,
+                                  void* stream);
 
 /* MoE forward that obtains no memory.  It has no counterpart in the reference.
  *

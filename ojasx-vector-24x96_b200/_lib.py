@@ -24,6 +24,8 @@ SIGNATURES = {
     "ojasx_b200_last_error": (C.c_char_p, []),
     "ojasx_b200_launch_count": (C.c_ulonglong, []),
     "ojasx_b200_linear_forward": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "ojasx_b200_linear_forward_tensor": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
+    "ojasx_b200_take_device_error": (_i, []),
     "ojasx_b200_linear_forward_raw": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp,
                                            _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "ojasx_b200_rvq_fused_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]),
@@ -43,6 +45,7 @@ SIGNATURES = {
     "ojasx_destroy_moe": (None, [_vp]),
     "ojasx_b200_moe_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "ojasx_b200_moe_forward_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "ojasx_b200_silu_mul": (_i, [_vp, _vp, _vp, _sz, _i, _vp]),
     "ojasx_b200_moe_reserve": (_i, [_vp, _i, _i]),
     "ojasx_b200_moe_set_outliers": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "ojasx_b200_moe_set_router": (_i, [_vp, _vp, _i]),

@@ -200,6 +200,11 @@ int ojasx_b200_moe_forward_routed(OjasxMoEHandle handle, const void* d_x, void* 
     return launch_moe_experts(h->problem(d_x, d_y, idx, w, n_tokens, top_k, io_dtype), s);
 }
 
+int ojasx_b200_silu_mul(const void* d_gate, const void* d_up, void* d_out, size_t count, int io_dtype, void* stream) {
+    if (io_dtype != OJX_F32 && io_dtype != OJX_BF16) return OJX_ERR_ARG;
+    return launch_silu_mul(d_gate, d_up, d_out, count, io_dtype, static_cast<cudaStream_t>(stream));
+}
+
 int ojasx_moe_forward(OjasxMoEHandle handle, const float* x, const int* top_k_indices, const float* top_k_weights,
                       float* y_out, int k_active) {
     if (!handle || !x || !top_k_indices || !top_k_weights || !y_out) return OJX_ERR_ARG;  // ojasx_lut_c_api.cpp:267

@@ -1,0 +1,378 @@
+// Batched VQ linear on the 5th-generation tensor cores (tcgen05 + TMEM), for bf16 activations and
+// batches large enough that the operation is a dense contraction:
+//     Y[b, m] = scale[m] * sum_k X[b, k] * W[m, k] (+ bias[m]),   W[m, 8g + d] = codebook[code[m, g]][d] (+ outlier)
+// The weights are never materialised in global memory: per 128-row x 64-column tile the four
+// producer warps turn code bytes into bf16 (one 16-byte shared-memory gather from a bf16 copy of
+// the codebook per code byte), add the row's CSR outliers that fall in the tile, and store the
+// tile in the 128-byte-swizzled K-major layout that tcgen05.mma reads; the same threads stage the
+// matching X tile.  One thread of a fifth warp issues the MMAs (M = 128, N = padded batch, K = 16
+// per instruction, fp32 accumulation in tensor memory) and signals stage reuse with
+// tcgen05.commit.  After the last K tile the producer warps become the epilogue: tcgen05.ld the
+// accumulator rows, scale, bias, store bf16.
+//
+// This path trades the bit-exactness of the table kernels for throughput (weights are rounded to
+// bf16), so it is used only for bf16 I/O, inside the rel 2e-2 tolerance of the bf16 activation path.
+// Every wait on an mbarrier is bounded; on a timeout the kernel raises a flag that the host reads.
+#include "common.cuh"
+#include "launch.h"
+#include "handles.h"
+
+namespace ojx {
+
+constexpr int kDqThreads = 160;      // 4 producer/epilogue warps + 1 MMA warp
+constexpr int kDqBlockM = 128;
+constexpr int kDqBlockK = 64;        // bf16 elements per K tile = one 128-byte swizzle row
+constexpr int kDqStages = 4;        // most stages; wide batch tiles use 3 to fit shared memory
+constexpr int kDqSpin = 1 << 22;     // bounded mbarrier polling
+
+// Per-phase cycle counters for tuning; compiled out unless OJX_PHASE_TIMING is defined.
+#ifdef OJX_PHASE_TIMING
+__device__ unsigned long long g_dq_phase[16];
+#define DQ_TICK(i) do { if (blockIdx.x == 0 && blockIdx.y == 0) { long long n_ = clock64(); atomicAdd(&g_dq_phase[i], (unsigned long long)(n_ - t_)); t_ = n_; } } while (0)
+#define DQ_TICK_INIT long long t_ = clock64()
+#else
+#define DQ_TICK(i) do { } while (0)
+#define DQ_TICK_INIT do { } while (0)
+#endif
+
+constexpr int kDqCodeStride = 144;   // bytes between the code slots of neighbouring threads (128 + 16: fewer bank conflicts)
+
+__device__ __forceinline__ void cp_async16_zfill(void* smem_dst, const void* gsrc, int src_bytes) {
+    unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(src_bytes) : "memory");
+}
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Returns false if the phase did not complete within the polling budget.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
+    for (int i = 0; i < kDqSpin; ++i) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+// Shared-memory matrix descriptor of a K-major tile stored with the 128-byte swizzle: rows of 128
+// bytes, groups of 8 rows 1024 bytes apart.
+__device__ __forceinline__ unsigned long long make_desc_sw128(unsigned smem_addr) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_addr >> 4) & 0x3fff);        // start address
+    d |= (unsigned long long)1 << 16;                            // leading byte offset (unused with swizzle)
+    d |= (unsigned long long)(1024 >> 4) << 32;                  // stride byte offset: 8 rows
+    d |= (unsigned long long)1 << 46;                            // descriptor version of sm_100
+    d |= (unsigned long long)2 << 61;                            // SWIZZLE_128B
+    return d;
+}
+
+struct DequantGemmProblem {
+    const uint8_t* codes;       // [M, G]
+    const float* codebook;      // [256, 8] fp32 (rounded to bf16 inside the kernel)
+    const float* scales;        // [M] or null
+    const float* bias;          // [M] or null
+    CsrView csr;                // column indices ascending inside each row, or nnz == 0
+    const __nv_bfloat16* x;     // [B, K]
+    __nv_bfloat16* y;           // [B, row_stop - row_start]
+    int* error_flag;
+    int K, G, row_start, row_stop, batch;
+    int n_pad;                  // MMA N: batch tile rounded up to 16 (<= 256)
+    int tmem_cols;              // power of two >= n_pad, >= 32
+    int stages;                 // 3 or 4 stage buffers
+    int csr_cap;                // outlier entries of the CTA's rows that fit in shared memory
+};
+
+__global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __grid_constant__ DequantGemmProblem P) {
+    extern __shared__ unsigned char dq_smem_raw[];
+    // swizzled tiles need 1024-byte alignment; the dynamic segment only promises 16
+    unsigned char* dq_smem = dq_smem_raw + ((1024u - (smem_u32(dq_smem_raw) & 1023u)) & 1023u);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int N = P.n_pad;
+    const int S = P.stages;
+    const int a_bytes = kDqBlockM * 128, b_bytes = N * 128, stage_bytes = a_bytes + b_bytes;
+    unsigned char* tiles = dq_smem;                                   // [stages][A | B], 1024-byte aligned
+    uint4* cb16 = reinterpret_cast<uint4*>(tiles + S * stage_bytes);   // [256] centroids as 8 bf16
+    unsigned char* code_stage = reinterpret_cast<unsigned char*>(cb16 + 256);   // [2][128 threads][kDqCodeStride], 16-byte aligned
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(code_stage + 2 * 128 * kDqCodeStride);
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * kDqStages + 1);
+    int2* csr_s = reinterpret_cast<int2*>(tmem_slot + 2);                     // [csr_cap] (col, value bits), 8-byte aligned
+    const unsigned full0 = smem_u32(bars), empty0 = full0 + 8 * kDqStages, accum = empty0 + 8 * kDqStages;
+
+    const int m0 = P.row_start + blockIdx.x * kDqBlockM;
+    const int b0 = blockIdx.y * 256;
+    const int nb = min(256, P.batch - b0);
+    const int rows_out = P.row_stop - P.row_start;
+    const int KT = P.K / kDqBlockK;
+
+    // codebook -> bf16, one 16-byte entry per centroid
+    for (int c = tid; c < 256; c += kDqThreads) {
+        __nv_bfloat162 h[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(P.codebook[c * 8 + 2 * q], P.codebook[c * 8 + 2 * q + 1]);
+        cb16[c] = *reinterpret_cast<uint4*>(h);
+    }
+    // outliers of this CTA's rows: one contiguous CSR range, copied once with coalesced loads
+    int csr_base = 0, csr_staged = 0;
+    if (P.csr.nnz > 0 && m0 < P.row_stop) {
+        csr_base = P.csr.row_ptrs[m0];
+        csr_staged = min(P.csr_cap, P.csr.row_ptrs[min(m0 + kDqBlockM, P.row_stop)] - csr_base);
+        for (int i = tid; i < csr_staged; i += kDqThreads)
+            csr_s[i] = make_int2(P.csr.cols[csr_base + i], __float_as_int(P.csr.vals[csr_base + i]));
+    }
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) { mbar_init(full0 + 8 * s, 128); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((unsigned)P.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem_base = *tmem_slot;
+    bool ok = true;
+
+    if (warp < 4) {
+        // ---------------- producers: row m = m0 + tid
+        const int m = m0 + tid;
+        const bool row_ok = m < P.row_stop;
+        const uint8_t* crow = P.codes + (size_t)(row_ok ? m : P.row_start) * P.G;
+        int cur = 0, cend = 0;
+        if (row_ok && P.csr.nnz > 0) { cur = P.csr.row_ptrs[m]; cend = P.csr.row_ptrs[m + 1]; }
+        // The reference adds the outlier row sum AFTER the row scale (ojasx_lut_cpu.cpp:178-182, 127), so an
+        // outlier folded into the weight tile is pre-divided by the scale that the epilogue applies.
+        const float row_scale = (row_ok && P.scales) ? P.scales[m] : 1.0f;
+        const float inv_scale = row_scale != 0.0f ? 1.0f / row_scale : 0.0f;
+        const int csr_begin = cur;
+        const int r7 = tid & 7;
+        // Global-memory latency is kept off the per-tile critical path by asynchronous copies:
+        //  * this row's code bytes arrive in blocks of 16 K tiles (128 bytes) into a private,
+        //    double-buffered slot of shared memory, one block ahead of use;
+        //  * this thread's share of the X tile (N/16 chunks of 16 bytes) is copied straight into its
+        //    swizzled place in the stage buffer two K tiles ahead of use;
+        //  * the next outlier of the row is held in registers.
+        constexpr int kPF = 2;
+        const int nx = (N * 8) >> 7;
+        unsigned char* my_codes = code_stage + tid * kDqCodeStride;           // [2][kDqCodeBlock] at stride 128*stride
+        auto issue_codes = [&](int blk) {   // K tiles [16*blk, 16*blk+16) -> buffer blk & 1
+            const int k0 = blk * 16;
+            if (k0 >= KT) return;
+            unsigned char* dst = my_codes + (blk & 1) * (128 * kDqCodeStride);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const int bytes = min(16, max(0, (KT - k0) * 8 - c * 16));
+                if (bytes > 0) cp_async16_zfill(dst + c * 16, crow + (size_t)k0 * 8 + c * 16, bytes);
+            }
+        };
+        auto issue_x = [&](int kt) {       // requires the stage of tile kt to be free
+            if (kt >= KT) return;
+            unsigned char* B = tiles + (kt % S) * stage_bytes + a_bytes;
+            for (int q = 0; q < nx; ++q) {
+                const int i = tid + q * 128, r = i >> 3, c = i & 7;
+                const bool in = r < nb;
+                cp_async16_zfill(B + (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4),
+                                 P.x + (size_t)(b0 + (in ? r : 0)) * P.K + kt * kDqBlockK + c * 8, in ? 16 : 0);
+            }
+        };
+        // prologue: code blocks 0 and (later) 1, X tiles 0 .. kPF-1; one commit group per K tile from here on
+        issue_codes(0);
+        for (int t = 0; t < kPF; ++t) { issue_x(t); asm volatile("cp.async.commit_group;" ::: "memory"); }
+        int col_next = 0x7fffffff;
+        float val_next = 0.0f;
+        auto fetch_outlier = [&]() {   // entry `cur` of this row: from shared memory when it was staged
+            if (cur >= cend) { col_next = 0x7fffffff; return; }
+            const int i = cur - csr_base;
+            if (i < csr_staged) { const int2 e = csr_s[i]; col_next = e.x; val_next = __int_as_float(e.y) * inv_scale; }
+            else { col_next = P.csr.cols[cur]; val_next = P.csr.vals[cur] * inv_scale; }
+        };
+        fetch_outlier();
+        DQ_TICK_INIT;
+        for (int kt = 0; kt < KT && ok; ++kt) {
+            const int s = kt % S;
+            // stage of tile kt+kPF: wait until the MMAs that read its previous contents are done, then start its X copy
+            const int kn = kt + kPF;
+            if (kn < KT && kn >= S) ok = mbar_wait(empty0 + 8 * (kn % S), ((kn / S) - 1) & 1);
+            if (!ok) break;
+            if (tid == 0) DQ_TICK(0);
+            issue_x(kn);
+            if ((kt & 15) == 0) issue_codes((kt >> 4) + 1);   // next code block rides in this tile's group
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group %0;" ::"n"(kPF) : "memory");   // copies of tile kt (and its code block) have landed
+            if (tid == 0) DQ_TICK(1);
+            unsigned char* A = tiles + s * stage_bytes;
+            const uint2 cw = *reinterpret_cast<const uint2*>(my_codes + ((kt >> 4) & 1) * (128 * kDqCodeStride) + (kt & 15) * 8);
+            // A: eight codes of this row -> eight 16-byte chunks, chunk index XOR (row % 8)
+            unsigned char* arow = A + (tid >> 3) * 1024 + r7 * 128;
+            uint4 wv[8];   // all eight gathers first, then the eight stores (the compiler cannot reorder them itself)
+#pragma unroll
+            for (int gl = 0; gl < 8; ++gl) {
+                const unsigned code = ((gl < 4 ? cw.x : cw.y) >> ((gl & 3) * 8)) & 0xffu;
+                wv[gl] = row_ok ? cb16[code] : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int gl = 0; gl < 8; ++gl) *reinterpret_cast<uint4*>(arow + ((gl ^ r7) << 4)) = wv[gl];
+            // CSR outliers of this row inside the tile (columns ascending): w += value / scale, rounded to bf16
+            const int kend = (kt + 1) * kDqBlockK;
+            while (col_next < kend) {
+                const int kk = col_next - kt * kDqBlockK;
+                if (kk >= 0) {
+                    __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(arow + (((kk >> 3) ^ r7) << 4)) + (kk & 7);
+                    *e = __float2bfloat16_rn(__bfloat162float(*e) + val_next);
+                }
+                ++cur;
+                fetch_outlier();
+            }
+            if (tid == 0) DQ_TICK(2);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic and cp.async stores -> visible to the tensor core
+            mbar_arrive(full0 + 8 * s);
+            if (tid == 0) DQ_TICK(3);
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        // ---------------- epilogue: accumulator row tid of the tile
+        if (ok) ok = mbar_wait(accum, 0);
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float sc = (row_ok && P.scales) ? P.scales[m] : 1.0f;
+            const float bi = (row_ok && P.bias) ? P.bias[m] : 0.0f;
+            for (int c0 = 0; c0 < N; c0 += 16) {
+                unsigned v[16];
+                const unsigned taddr = tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)c0;
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                      "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                    : "r"(taddr));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row_ok) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int b = c0 + j;
+                        if (b < nb) {
+                            float r = fmaf(__uint_as_float(v[j]), sc, bi);
+                            if (sc == 0.0f)  // a zero row scale cannot carry the folded outliers: add them here
+                                for (int q = csr_begin; q < cend; ++q)
+                                    r += P.csr.vals[q] * __bfloat162float(P.x[(size_t)(b0 + b) * P.K + P.csr.cols[q]]);
+                            P.y[(size_t)(b0 + b) * rows_out + (m - P.row_start)] = __float2bfloat16_rn(r);
+                        }
+                    }
+                }
+            }
+        }
+    } else if (lane == 0) {
+        // ---------------- MMA issuer
+        const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(N >> 3) << 17) | ((unsigned)(kDqBlockM >> 4) << 24);
+        DQ_TICK_INIT;
+        for (int kt = 0; kt < KT && ok; ++kt) {
+            const int s = kt % S;
+            ok = mbar_wait(full0 + 8 * s, (kt / S) & 1);
+            if (!ok) break;
+            DQ_TICK(4);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const unsigned a_addr = smem_u32(tiles + s * stage_bytes), b_addr = a_addr + a_bytes;
+#pragma unroll
+            for (int j = 0; j < kDqBlockK / 16; ++j) {
+                const unsigned long long da = make_desc_sw128(a_addr + j * 32), db = make_desc_sw128(b_addr + j * 32);
+                const unsigned acc = (kt > 0 || j > 0) ? 1u : 0u;
+                asm volatile(
+                    "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                    "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                    ::"r"(tmem_base), "l"(da), "l"(db), "r"(idesc), "r"(acc)
+                    : "memory");
+            }
+            // frees the stage when the MMAs that read it have completed
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(empty0 + 8 * s) : "memory");
+            DQ_TICK(5);
+        }
+        if (ok) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(accum) : "memory");
+    }
+    if (!ok && P.error_flag) atomicExch(P.error_flag, 1);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 4) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)P.tmem_cols) : "memory");
+    }
+}
+
+size_t dequant_gemm_smem(int n_pad, int stages, int csr_cap) {
+    return (size_t)stages * (kDqBlockM * 128 + (size_t)n_pad * 128) + 256 * 16 + (2 * kDqStages + 1) * 8 + 16 +
+           2 * 128 * kDqCodeStride + (size_t)csr_cap * 8 + 1024;
+}
+
+static __device__ int g_dq_error;  // raised when a bounded wait inside the kernel ran out
+
+// Reads and clears the flag (synchronises the device).  1 = some dequant-GEMM launch since the last
+// call gave up waiting on a barrier and its output must not be trusted.
+int take_dequant_gemm_error(int* out) {
+    int v = 0, zero = 0;
+    OJX_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_dq_error, sizeof(int)));
+    if (v) OJX_CUDA_TRY(cudaMemcpyToSymbol(g_dq_error, &zero, sizeof(int)));
+    *out = v;
+    return OJX_OK;
+}
+
+// Conditions under which the tensor-core path may stand in for the table kernels.
+bool dequant_gemm_supported(const LinearProblem& P, bool csr_sorted) {
+    return P.io_dtype == OJX_BF16 && P.D == 8 && P.Kcb == 256 && P.K == P.G * 8 && (P.K % kDqBlockK) == 0 &&
+           (P.csr.nnz == 0 || csr_sorted) && (reinterpret_cast<uintptr_t>(P.codes) & 15) == 0 && (P.G & 15) == 0 &&
+           (reinterpret_cast<uintptr_t>(P.x) & 15) == 0;
+}
+
+int launch_dequant_gemm(const LinearProblem& L, cudaStream_t stream) {
+    DequantGemmProblem P{};
+    int* error_flag = nullptr;
+    OJX_CUDA_TRY(cudaGetSymbolAddress((void**)&error_flag, g_dq_error));
+    P.codes = L.codes; P.codebook = L.codebook; P.scales = L.scales; P.bias = L.bias; P.csr = L.csr;
+    P.x = static_cast<const __nv_bfloat16*>(L.x); P.y = static_cast<__nv_bfloat16*>(L.y);
+    P.error_flag = error_flag;
+    P.K = L.K; P.G = L.G; P.row_start = L.row_start; P.row_stop = L.row_stop; P.batch = L.batch;
+    const int nb = L.batch < 256 ? L.batch : 256;
+    P.n_pad = round_up(nb, 16);
+    int cols = 32;
+    while (cols < P.n_pad) cols <<= 1;
+    P.tmem_cols = cols;
+    P.stages = dequant_gemm_smem(P.n_pad, kDqStages, 4096) <= 227 * 1024 ? kDqStages : 3;
+    // shared-memory room for the outliers of 128 rows: whatever is left, up to 8192 entries; the
+    // kernel reads entries beyond that from global memory
+    P.csr_cap = 0;
+    if (L.csr.nnz > 0) {
+        const size_t left = 227 * 1024 - dequant_gemm_smem(P.n_pad, P.stages, 0);
+        P.csr_cap = (int)(left / 8 < 8192 ? left / 8 : 8192);
+    }
+    const size_t smem = dequant_gemm_smem(P.n_pad, P.stages, P.csr_cap);
+    static thread_local size_t configured = 0;
+    if (smem > configured) {
+        OJX_CUDA_TRY(cudaFuncSetAttribute(vq_dequant_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = smem;
+    }
+    const int rows = L.row_stop - L.row_start;
+    const dim3 grid((rows + kDqBlockM - 1) / kDqBlockM, (L.batch + 255) / 256);
+    vq_dequant_gemm_kernel<<<grid, kDqThreads, smem, stream>>>(P);
+    OJX_CUDA_TRY(cudaGetLastError());
+    count_launch(1);
+    return OJX_OK;
+}
+
+}  // namespace ojx
+
+#ifdef OJX_PHASE_TIMING
+extern "C" __attribute__((visibility("default"))) int ojx_read_dq_phases(unsigned long long* out, int reset) {
+    cudaMemcpyFromSymbol(out, ojx::g_dq_phase, sizeof(unsigned long long) * 16);
+    if (reset) { unsigned long long z[16] = {}; cudaMemcpyToSymbol(ojx::g_dq_phase, z, sizeof(z)); }
+    return 0;
+}
+#endif

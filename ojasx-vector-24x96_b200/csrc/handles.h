@@ -29,6 +29,7 @@ struct LinearHandle {
     float* bias = nullptr;     // null = none
     int nnz = 0;
     bool has_outlier_arrays = false;
+    bool csr_sorted = true;    // column indices ascending inside every row (needed by the tensor-core path)
     int* row_ptrs = nullptr;
     int* cols = nullptr;
     float* vals = nullptr;

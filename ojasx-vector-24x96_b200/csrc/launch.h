@@ -18,8 +18,14 @@ int launch_rvq_generic(const uint8_t* packed, const float* codebooks, const floa
                        const float* x, int batch, int stages, int bits, int D, int rows, int columns, int row_start,
                        int row_stop, float* out, cudaStream_t stream);
 
+// --- dequant_gemm.cu (tcgen05 path for bf16 batches)
+bool dequant_gemm_supported(const LinearProblem& P, bool csr_sorted);
+int launch_dequant_gemm(const LinearProblem& P, cudaStream_t stream);
+int take_dequant_gemm_error(int* out);
+
 // --- moe.cu
 int launch_moe_experts(MoeProblem P, cudaStream_t stream);
+int launch_silu_mul(const void* gate, const void* up, void* out, size_t n, int io_dtype, cudaStream_t stream);
 int launch_moe_router(const float* Wr, const void* x, int io_dtype, int n_tokens, int H, int E, int k,
                       float* logits, float* probs, int* idx_out, float* w_out, cudaStream_t stream);
 

@@ -294,6 +294,31 @@ __global__ void __launch_bounds__(kTopkWarps * 32) moe_router_topk_kernel(const 
     for (int r = lane; r < k; r += 32) w_out[(size_t)t * k + r] = __fdiv_rn(w_out[(size_t)t * k + r], ws);
 }
 
+// out = silu(gate) * up, elementwise, computed in fp32 with the expert kernels' silu and rounded once
+// to the io dtype (the SwiGLU step of a dense VQ MLP block: gate and up are separate VQ linears).
+__global__ void silu_mul_kernel(const void* __restrict__ gate, const void* __restrict__ up, void* __restrict__ out,
+                                size_t n, int io_dtype) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    if (io_dtype == OJX_BF16) {
+        const float g = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(gate)[i]);
+        const float u = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(up)[i]);
+        reinterpret_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(__fmul_rn(silu_ref(g), u));
+    } else {
+        reinterpret_cast<float*>(out)[i] = __fmul_rn(silu_ref(reinterpret_cast<const float*>(gate)[i]),
+                                                     reinterpret_cast<const float*>(up)[i]);
+    }
+}
+
+int launch_silu_mul(const void* gate, const void* up, void* out, size_t n, int io_dtype, cudaStream_t s) {
+    if (!gate || !up || !out) return OJX_ERR_ARG;
+    if (n == 0) return OJX_OK;
+    silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(gate, up, out, n, io_dtype);
+    OJX_CUDA_TRY(cudaGetLastError());
+    count_launch(1);
+    return OJX_OK;
+}
+
 // ------------------------------------------------------------------------------- host side
 template <typename K>
 static int set_smem(K kern) {

@@ -94,6 +94,18 @@ class VQLinear:
 
     __call__ = forward
 
+    def forward_tensor(self, x: torch.Tensor, row_start: int = 0, row_stop: Optional[int] = None) -> torch.Tensor:
+        """bf16 batch on the tensor cores (tcgen05 dequant GEMM); tolerance of the bf16 path, not bit-exact."""
+        _require_cuda(x, "x")
+        if x.dtype != torch.bfloat16:
+            raise TypeError("forward_tensor needs bfloat16 activations")
+        row_stop = self.out_features if row_stop is None else row_stop
+        x2 = x.reshape(-1, self.in_features).contiguous()
+        out = torch.empty((x2.shape[0], row_stop - row_start), device=x.device, dtype=torch.bfloat16)
+        check(lib().ojasx_b200_linear_forward_tensor(self._h, x2.data_ptr(), out.data_ptr(), x2.shape[0], row_start,
+                                                     row_stop, _stream_ptr(x.device)), "ojasx_b200_linear_forward_tensor")
+        return out.reshape(*x.shape[:-1], row_stop - row_start)
+
     def close(self):
         if getattr(self, "_h", None):
             lib().ojasx_destroy_linear(self._h)
@@ -135,6 +147,31 @@ class VQLinearGroup:
             self.close()
         except Exception:
             pass
+
+
+def silu_mul(gate: torch.Tensor, up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _require_cuda(gate, "gate")
+    g, u = gate.contiguous(), up.contiguous()
+    o = torch.empty_like(g) if out is None else out
+    check(lib().ojasx_b200_silu_mul(g.data_ptr(), u.data_ptr(), o.data_ptr(), g.numel(), _dtype_code(g),
+                                    _stream_ptr(g.device)), "ojasx_b200_silu_mul")
+    return o
+
+
+class VQMLP:
+    """Dense SwiGLU block of three VQ linears: ``down(silu(gate(x)) * up(x))`` (config 1 of the benchmark set).
+    Every linear keeps its own codebook and outliers; intermediate activations are of the input dtype."""
+
+    def __init__(self, gate: VQLinear, up: VQLinear, down: VQLinear):
+        assert gate.in_features == up.in_features and gate.out_features == up.out_features == down.in_features
+        self.gate, self.up, self.down = gate, up, down
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        g = self.gate(x)
+        u = self.up(x)
+        return self.down(silu_mul(g, u, out=g))
+
+    __call__ = forward
 
 
 class VQMoE:

@@ -74,7 +74,7 @@ def test_linear_row_slices_and_bf16(cuda, oracle):
     parts = [layer(xt, r0, r1).cpu().numpy() for r0, r1 in ((0, 864), (864, 3456), (3456, 6912))]
     assert np.array_equal(np.concatenate(parts, axis=1), want)
     # bf16 activations: exact widening, fp32 compute, round-to-nearest-even on the way out
-    got = layer(xt.to(torch.bfloat16)).float().cpu().numpy()
+    got = layer(xt.to(torch.bfloat16)).float().cpu().numpy()   # batch 4: below the tensor-core switch-over (32)
     assert np.array_equal(got, synth.to_bf16_f32(want))
 
 
@@ -104,3 +104,48 @@ def test_linear_errors(cuda):
     L = ojasx_b200.lib()
     assert L.ojasx_linear_forward(None, None, None, 1, 0) == -1
     assert L.ojasx_b200_linear_forward(layer.handle, None, None, 1, 0, 0, 32, None) == -1
+
+
+@pytest.mark.parametrize("batch", [1, 4, 16])
+def test_mlp_block_fp32_and_bf16(cuda, oracle, batch):
+    """Config-1 block: gate/up 2560->6912, SiLU gate, down 6912->2560, each with its own codebook and outliers."""
+    ws = [synth.make_vq_linear(70 + i, *shape, block_dim=8) for i, shape in enumerate([(2560, 6912), (2560, 6912), (6912, 2560)])]
+    mlp = ops.VQMLP(*[ops.VQLinear.from_weights(w) for w in ws])
+    x = np.random.default_rng(batch).standard_normal((batch, 2560)).astype(np.float32)
+
+    def lin(w, a):
+        return oracle.linear_forward(w.codebook, w.codes, w.scales, w.bias, w.csr, a, block_dim=8)
+
+    def silu(v):
+        return (v / (np.float32(1) + np.exp(-v.astype(np.float64)).astype(np.float32))).astype(np.float32)
+
+    g, u = lin(ws[0], x), lin(ws[1], x)
+    want = lin(ws[2], (silu(g) * u).astype(np.float32))
+    got = mlp(torch.from_numpy(x).to(cuda)).cpu().numpy()
+    assert np.all(np.abs(got - want) <= 1e-6 + 1e-5 * np.abs(want)), np.abs(got - want).max()
+    # bf16 activations: every stage rounds to bf16 on the way out; tolerance of the bf16 path (rel 2e-2)
+    bf = synth.to_bf16_f32
+    xb = bf(x)
+    gb, ub = bf(lin(ws[0], xb)), bf(lin(ws[1], xb))
+    want_b = bf(lin(ws[2], bf(silu(gb) * ub)))
+    got_b = mlp(torch.from_numpy(xb).to(cuda).bfloat16()).float().cpu().numpy()
+    assert np.allclose(got_b, want_b, rtol=2e-2, atol=2e-3), np.abs(got_b - want_b).max()
+
+
+@pytest.mark.parametrize("K,M,batch", [(2560, 6912, 64), (6912, 2560, 256), (2560, 2560, 5), (640, 2560, 300), (2560, 200, 33), (1152, 130, 16)])
+def test_tensor_core_dequant_gemm_bf16(cuda, oracle, K, M, batch):
+    """tcgen05 path: bf16 weights (codebook rounded once) and fp32 accumulation against the fp32 oracle on
+    bf16 activations; tolerance of the bf16-activation path (rel 2e-2) plus an absolute term for the
+    bf16 rounding of the weights (|y| ~ 1-3 here)."""
+    w = synth.make_vq_linear(K + batch, K, M, block_dim=8, with_scales=True, with_bias=True)
+    xb = synth.to_bf16_f32(np.random.default_rng(batch).standard_normal((batch, K)).astype(np.float32))
+    want = oracle.linear_forward(w.codebook, w.codes, w.scales, w.bias, w.csr, xb, block_dim=8)
+    layer = ops.VQLinear.from_weights(w)
+    got = layer.forward_tensor(torch.from_numpy(xb).to(cuda).bfloat16()).float().cpu().numpy()
+    assert ojasx_b200.lib().ojasx_b200_take_device_error() == 0
+    err = np.abs(got - want)
+    assert np.all(err <= 2e-2 * np.abs(want) + 3e-2), (err.max(), np.abs(want).max())
+    # the automatic switch-over (bf16, batch >= 32) takes the same path
+    if batch >= 32:
+        auto = layer(torch.from_numpy(xb).to(cuda).bfloat16()).float().cpu().numpy()
+        assert np.array_equal(auto, got)
