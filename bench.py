@@ -274,6 +274,12 @@ def run_ours(args):
         except Exception as ex:
             extras["kv"] = {"error": repr(ex)}
 
+    if args.stack and rank == 0 and world == 1:
+        try:
+            extras["stack"] = bench_stack(args, dev)
+        except Exception as ex:
+            extras["stack"] = {"error": repr(ex)}
+
     if rank == 0:
         peak, which = measured_peak_hbm()
         achieved = P * alg / (ms_step * 1e-3) / 1e9   # per GPU: the launch processes this rank's P layers
@@ -347,6 +353,38 @@ def bench_moe(args, dev, rank, world):
     return out
 
 
+def bench_stack(args, dev):
+    """Config 4: 24-layer decoder stack (hidden 2560, 32/8 heads of 128, RoPE 1e6, RMSNorm, 512-expert top-10
+    MoE per layer, VQ lm_head over 151936 tokens, quantised KV), 512 random prompt ids then 256 greedy steps.
+    One host weight set, 24 distinct device copies (every layer streams its own HBM bytes)."""
+    import torch
+    from ojasx_b200 import inference_engine as ie
+    out = {}
+    cfg = ie.StackConfig(max_seq_len=args.stack_prompt + args.stack_new + 8)
+    t0 = time.perf_counter()
+    W = ie.make_stack_weights(2024, cfg)
+    out["host_weight_seconds"] = round(time.perf_counter() - t0, 1)
+    for B in args.stack_batches:
+        stack = ie.VQDecoderStack(W, cfg, batch=B, use_graph=not args.stack_eager)
+        ids = torch.randint(0, cfg.vocab, (B, args.stack_prompt), device=dev, generator=torch.Generator(device=dev).manual_seed(3))
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        logits = stack.prefill(ids)
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        for _ in range(args.stack_new):
+            logits = stack.decode_step(torch.argmax(logits, dim=-1))
+        torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        out[f"B{B}"] = {"prefill_tokens_per_s": round(B * args.stack_prompt / (t1 - t0), 1),
+                        "decode_tokens_per_s": round(B * args.stack_new / (t2 - t1), 1),
+                        "ms_per_decode_step": round((t2 - t1) / args.stack_new * 1e3, 3),
+                        "prompt": args.stack_prompt, "new_tokens": args.stack_new}
+        del stack
+        torch.cuda.empty_cache()
+    return out
+
+
 def bench_kv(args, dev):
     """Config 3: append one token + one decode query, 32 q heads / 8 kv heads, head_dim 128, bf16 q."""
     import torch
@@ -392,6 +430,11 @@ def main():
     ap.add_argument("--no-moe", dest="moe", action="store_false")
     ap.add_argument("--no-moe-csr", dest="moe_csr", action="store_false")
     ap.add_argument("--no-kv", dest="kv", action="store_false")
+    ap.add_argument("--stack", action="store_true", help="also time the 24-layer decoder stack (adds about a minute)")
+    ap.add_argument("--stack-eager", action="store_true", help="launch the decode step eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--stack-prompt", type=int, default=512)
+    ap.add_argument("--stack-new", type=int, default=256)
+    ap.add_argument("--stack-batches", type=int, nargs="+", default=[1, 32])
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

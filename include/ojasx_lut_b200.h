@@ -235,6 +235,24 @@ OJASX_API int ojasx_b200_kvq_decode(OjasxKvqHandle handle, const void* d_q, void
                                     void* stream);
 OJASX_API void ojasx_b200_kvq_destroy(OjasxKvqHandle handle);
 
+/* ---- Per-token operators of a decoder step (no counterpart in the reference, which leaves them to the
+ * HuggingFace model it drives, ojasx_24x96/engine.py:176-199); they exist so that one decode step is a
+ * fixed sequence of launches of this library and can be captured in a CUDA graph.
+ * rmsnorm: if d_add is not NULL, d_x += d_add first (residual), then d_out = d_x * rsqrt(mean(d_x^2)+eps) * w.
+ * rope_qk: rotate-half rotary embedding in place on q [batch, q_heads, head_dim] and k [batch, kv_heads,
+ * head_dim] at the per-sequence positions d_positions (int32, device).  add_int: d_values[i] += delta. */
+OJASX_API int ojasx_b200_rmsnorm(void* d_x, const void* d_add, const float* d_weight, void* d_out, int rows, int hidden,
+                                 float eps, int io_dtype, void* stream);
+OJASX_API int ojasx_b200_rope_qk(void* d_q, void* d_k, const int* d_positions, int batch, int q_heads, int kv_heads,
+                                 int head_dim, float theta, int io_dtype, void* stream);
+OJASX_API int ojasx_b200_add_int(int* d_values, int count, int delta, void* stream);
+/* Plan decode launches for the cache's capacity instead of its current length, and let the device-side
+ * length be the only one consulted: the launch sequence of append/decode then never changes as the
+ * context grows, so it can be replayed from a CUDA graph.  ojasx_b200_kvq_seq_len stays at the value of
+ * the last eager call until ojasx_b200_kvq_sync_len reads the device length back (synchronises). */
+OJASX_API int ojasx_b200_kvq_set_static_plan(OjasxKvqHandle handle, int enabled);
+OJASX_API int ojasx_b200_kvq_sync_len(OjasxKvqHandle handle);
+
 #ifdef __cplusplus
 }
 #endif

@@ -60,6 +60,11 @@ SIGNATURES = {
     "ojasx_b200_kvq_append": (_i, [_vp, _vp, _vp, _i, _vp]),
     "ojasx_b200_kvq_decode": (_i, [_vp, _vp, _vp, _f, _i, _vp]),
     "ojasx_b200_kvq_destroy": (None, [_vp]),
+    "ojasx_b200_kvq_set_static_plan": (_i, [_vp, _i]),
+    "ojasx_b200_kvq_sync_len": (_i, [_vp]),
+    "ojasx_b200_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
+    "ojasx_b200_rope_qk": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp]),
+    "ojasx_b200_add_int": (_i, [_vp, _i, _i, _vp]),
 }
 
 _lib = None

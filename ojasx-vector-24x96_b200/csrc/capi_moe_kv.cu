@@ -327,23 +327,23 @@ static KvqProblem kvq_problem(const KvqHandle* h, int io) {
 int ojasx_b200_kvq_append(OjasxKvqHandle handle, const void* d_k, const void* d_v, int io_dtype, void* stream) {
     if (!handle || !d_k || !d_v || (io_dtype != OJX_F32 && io_dtype != OJX_BF16)) return OJX_ERR_ARG;
     auto* h = static_cast<KvqHandle*>(handle);
-    if (h->host_len >= h->max_seq) return OJX_ERR_RANGE;
+    if (!h->static_plan && h->host_len >= h->max_seq) return OJX_ERR_RANGE;
     KvqProblem P = kvq_problem(h, io_dtype);
     P.new_k = d_k; P.new_v = d_v;
     int rc = launch_kvq_append(P, static_cast<cudaStream_t>(stream));
-    if (rc == OJX_OK) h->host_len += 1;
+    if (rc == OJX_OK && !h->static_plan) h->host_len += 1;
     return rc;
 }
 
 int ojasx_b200_kvq_decode(OjasxKvqHandle handle, const void* d_q, void* d_out, float scale, int io_dtype, void* stream) {
     if (!handle || !d_q || !d_out || (io_dtype != OJX_F32 && io_dtype != OJX_BF16)) return OJX_ERR_ARG;
     auto* h = static_cast<KvqHandle*>(handle);
-    if (h->host_len <= 0) return OJX_ERR_RANGE;
+    if (!h->static_plan && h->host_len <= 0) return OJX_ERR_RANGE;
     KvqProblem P = kvq_problem(h, io_dtype);
     P.q = d_q; P.out = d_out;
     P.scale = scale > 0.0f ? scale : 1.0f / std::sqrt((float)h->head_dim);
     // Context chunks: enough CTAs to fill the GPU about twice, chunks of 256..2048 tokens.
-    const int T = h->host_len, heads = h->B * h->Hkv, sms = num_sms();
+    const int T = h->static_plan ? h->max_seq : h->host_len, heads = h->B * h->Hkv, sms = num_sms();
     int want = std::max(1, (2 * sms + heads - 1) / heads);
     int chunk = round_up((T + want - 1) / want, 256);
     chunk = std::min(2048, std::max(256, chunk));
@@ -356,6 +356,30 @@ int ojasx_b200_kvq_decode(OjasxKvqHandle handle, const void* d_q, void* d_out, f
     if (rc != OJX_OK) return rc;
     P.partials = static_cast<float*>(h->partials);
     return launch_kvq_decode(P, static_cast<cudaStream_t>(stream));
+}
+
+int ojasx_b200_kvq_set_static_plan(OjasxKvqHandle handle, int enabled) {
+    if (!handle) return OJX_ERR_ARG;
+    auto* h = static_cast<KvqHandle*>(handle);
+    h->static_plan = enabled != 0;
+    if (h->static_plan) {   // size the chunk scratch for the full capacity now, so that decode never allocates
+        DeviceGuard g(h->dev);
+        const int heads = h->B * h->Hkv, R = h->Hq / h->Hkv;
+        const int n_chunks = (h->max_seq + 255) / 256;
+        const size_t need = sizeof(float) * (size_t)heads * n_chunks * R * (h->head_dim + 2);
+        return ensure_capacity(&h->partials, &h->partials_cap, need);
+    }
+    return OJX_OK;
+}
+
+int ojasx_b200_kvq_sync_len(OjasxKvqHandle handle) {
+    if (!handle) return OJX_ERR_ARG;
+    auto* h = static_cast<KvqHandle*>(handle);
+    DeviceGuard g(h->dev);
+    std::vector<int> lens(h->B);
+    OJX_CUDA_TRY(cudaMemcpy(lens.data(), h->seq_lens, sizeof(int) * lens.size(), cudaMemcpyDeviceToHost));
+    h->host_len = *std::max_element(lens.begin(), lens.end());
+    return h->host_len;
 }
 
 void ojasx_b200_kvq_destroy(OjasxKvqHandle handle) {

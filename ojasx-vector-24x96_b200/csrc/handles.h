@@ -94,6 +94,7 @@ struct KvqHandle {
     int dev = 0;
     int B = 0, Hkv = 0, Hq = 0, head_dim = 0, D = 0, G = 0, max_seq = 0;
     int host_len = 0;                        // host mirror of the (uniform) cached length
+    bool static_plan = false;                // plan launches for max_seq; only the device-side lengths are consulted
     uint8_t* k_codes = nullptr;
     uint8_t* v_codes = nullptr;
     float* k_cb = nullptr;

@@ -6,9 +6,9 @@ method names of the reference engines (``OjasXInferenceEngine.prefill / decode_s
 
 The reference drives HuggingFace model classes; here the stack is spelled out (RMSNorm, RoPE, GQA
 attention, top-k MoE, residuals) because no checkpoint is involved: weights are seeded synthetic
-tensors with the shapes and distributions of the benchmark configuration.  Norms, rotary embedding,
-residual adds and the arg-max are plain torch ops; everything that touches VQ codes goes through
-libojasx_lut_b200.so.
+tensors with the shapes and distributions of the benchmark configuration.  The embedding lookup and the
+arg-max are torch ops; norms (with the residual adds folded in), rotary embedding and everything that
+touches VQ codes are kernels of libojasx_lut_b200.so, so one decode step is a fixed launch sequence.
 """
 from __future__ import annotations
 
@@ -19,7 +19,7 @@ import numpy as np
 import torch
 
 from . import synth
-from .ops import VQKVCache, VQLinear, VQMoE
+from .ops import VQKVCache, VQLinear, VQMoE, add_int_, rmsnorm, rope_qk_
 
 
 @dataclass
@@ -89,22 +89,6 @@ def make_stack_weights(seed: int, cfg: StackConfig) -> StackWeights:
                                      outlier_frac=cfg.outlier_frac))
 
 
-def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
-    xf = x.float()
-    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w).to(x.dtype)
-
-
-def rope(x: torch.Tensor, pos: torch.Tensor, theta: float) -> torch.Tensor:
-    """Rotate-half rotary embedding; x [B, heads, head_dim], pos [B] (absolute positions)."""
-    hd = x.shape[-1]
-    inv = 1.0 / (theta ** (torch.arange(0, hd, 2, device=x.device, dtype=torch.float32) / hd))
-    ang = pos.float()[:, None] * inv[None, :]                       # [B, hd/2]
-    cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
-    xf = x.float()
-    x1, x2 = xf[..., : hd // 2], xf[..., hd // 2:]
-    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).to(x.dtype)
-
-
 class _Layer:
     def __init__(self, w: LayerWeights, cfg: StackConfig, batch: int, device):
         self.q, self.k, self.v, self.o = (VQLinear.from_weights(a) for a in (w.q, w.k, w.v, w.o))
@@ -117,43 +101,83 @@ class _Layer:
 
 
 class VQDecoderStack:
-    """``batch`` independent sequences decoded in lock step (all at the same position)."""
+    """``batch`` independent sequences decoded in lock step (all at the same position).
+
+    ``use_graph=True`` captures one decode step in a CUDA graph after a warm-up step and replays it for
+    every token: the step is a fixed sequence of launches (positions and cache lengths live on the device,
+    the KV kernels are planned for the cache capacity), so per-token host work is one graph launch.
+    """
 
     def __init__(self, weights: StackWeights, cfg: StackConfig, batch: int = 1, dtype: torch.dtype = torch.float32,
-                 device: Optional[torch.device] = None):
-        self.cfg, self.batch, self.dtype = cfg, batch, dtype
+                 device: Optional[torch.device] = None, use_graph: bool = False):
+        self.cfg, self.batch, self.dtype, self.use_graph = cfg, batch, dtype, use_graph
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.embed = torch.from_numpy(weights.embed).to(self.device)
         self.final_norm = torch.from_numpy(weights.final_norm).to(self.device)
         self.lm_head = VQLinear.from_weights(weights.lm_head)
         n = len(weights.layers)
         self.layers = [_Layer(weights.layers[i % n], cfg, batch, self.device) for i in range(cfg.layers)]
+        self.pos = torch.zeros(batch, dtype=torch.int32, device=self.device)
         self.position = 0
+        self._graph = None
+        self._ids = torch.zeros(batch, dtype=torch.int64, device=self.device)
+        self._logits = None
+        if use_graph:
+            for l in self.layers:
+                l.cache.set_static_plan(True)
 
     def reset(self) -> None:
         for l in self.layers:
             l.cache.reset()
+        self.pos.zero_()
         self.position = 0
+
+    def _enqueue_step(self, ids: torch.Tensor) -> torch.Tensor:
+        cfg, B = self.cfg, self.batch
+        h = self.embed[ids].to(self.dtype)
+        pending = None                       # residual branch not yet added to h (added inside the next norm)
+        for l in self.layers:
+            a = rmsnorm(h, l.norm1, cfg.rms_eps, add=pending)
+            q = l.q(a).view(B, cfg.q_heads, cfg.head_dim)
+            k = l.k(a).view(B, cfg.kv_heads, cfg.head_dim)
+            v = l.v(a).view(B, cfg.kv_heads, cfg.head_dim)
+            rope_qk_(q, k, self.pos, cfg.rope_theta)
+            l.cache.append(k, v)
+            att = l.cache.decode(q)
+            o = l.o(att.view(B, cfg.q_heads * cfg.head_dim))
+            m = rmsnorm(h, l.norm2, cfg.rms_eps, add=o)
+            pending = l.moe.forward_routed(m, cfg.top_k)
+        a = rmsnorm(h, self.final_norm, cfg.rms_eps, add=pending)
+        add_int_(self.pos, 1)
+        return self.lm_head(a).float()
 
     @torch.no_grad()
     def decode_step(self, token_ids: torch.Tensor) -> torch.Tensor:
         """One token per sequence in, fp32 logits ``[batch, vocab]`` out; the KV caches grow by one."""
-        cfg = self.cfg
-        B = token_ids.shape[0]
-        pos = torch.full((B,), self.position, device=self.device, dtype=torch.int64)
-        h = self.embed[token_ids.to(self.device)].to(self.dtype)
-        for l in self.layers:
-            a = rms_norm(h, l.norm1, cfg.rms_eps)
-            q = rope(l.q(a).view(B, cfg.q_heads, cfg.head_dim), pos, cfg.rope_theta)
-            k = rope(l.k(a).view(B, cfg.kv_heads, cfg.head_dim), pos, cfg.rope_theta)
-            v = l.v(a).view(B, cfg.kv_heads, cfg.head_dim)
-            l.cache.append(k.contiguous(), v.contiguous())
-            att = l.cache.decode(q.contiguous())
-            h = h + l.o(att.view(B, cfg.q_heads * cfg.head_dim))
-            m = rms_norm(h, l.norm2, cfg.rms_eps)
-            h = h + l.moe.forward_routed(m, cfg.top_k)
+        ids = token_ids.to(self.device).to(torch.int64)
         self.position += 1
-        return self.lm_head(rms_norm(h, self.final_norm, cfg.rms_eps)).float()
+        if not self.use_graph:
+            return self._enqueue_step(ids)
+        if self._graph is None:
+            if self.position != 1:
+                raise RuntimeError("the first graph-mode step must come right after reset(): capture starts on empty caches")
+            # warm-up on a side stream (lazy kernel attributes, occupancy queries, scratch growth) ...
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self._ids.copy_(ids)
+                self._enqueue_step(self._ids)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            # ... whose token is dropped again before the capture; a capture records launches, it runs nothing
+            self.reset()
+            self.position = 1
+            self._graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self._graph):
+                self._logits = self._enqueue_step(self._ids)
+        self._ids.copy_(ids)
+        self._graph.replay()
+        return self._logits
 
     @torch.no_grad()
     def prefill(self, prompt_ids: torch.Tensor) -> torch.Tensor:

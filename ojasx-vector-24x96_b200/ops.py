@@ -158,6 +158,29 @@ def silu_mul(gate: torch.Tensor, up: torch.Tensor, out: Optional[torch.Tensor] =
     return o
 
 
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, add: Optional[torch.Tensor] = None,
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x += add`` (in place, when given) then ``out = x * rsqrt(mean(x^2) + eps) * weight``; x is [rows, hidden]."""
+    _require_cuda(x, "x")
+    assert x.is_contiguous() and x.dim() == 2 and weight.dtype == torch.float32
+    o = torch.empty_like(x) if out is None else out
+    check(lib().ojasx_b200_rmsnorm(x.data_ptr(), 0 if add is None else add.data_ptr(), weight.data_ptr(), o.data_ptr(),
+                                   x.shape[0], x.shape[1], eps, _dtype_code(x), _stream_ptr(x.device)), "ojasx_b200_rmsnorm")
+    return o
+
+
+def rope_qk_(q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor, theta: float) -> None:
+    """In-place rotary embedding of q [B, Hq, hd] and k [B, Hkv, hd] at int32 device positions [B]."""
+    assert q.is_contiguous() and k.is_contiguous() and positions.dtype == torch.int32 and q.dtype == k.dtype
+    check(lib().ojasx_b200_rope_qk(q.data_ptr(), k.data_ptr(), positions.data_ptr(), q.shape[0], q.shape[1], k.shape[1],
+                                   q.shape[2], theta, _dtype_code(q), _stream_ptr(q.device)), "ojasx_b200_rope_qk")
+
+
+def add_int_(values: torch.Tensor, delta: int) -> None:
+    assert values.dtype == torch.int32 and values.is_contiguous()
+    check(lib().ojasx_b200_add_int(values.data_ptr(), values.numel(), delta, _stream_ptr(values.device)), "ojasx_b200_add_int")
+
+
 class VQMLP:
     """Dense SwiGLU block of three VQ linears: ``down(silu(gate(x)) * up(x))`` (config 1 of the benchmark set).
     Every linear keeps its own codebook and outliers; intermediate activations are of the input dtype."""
@@ -298,6 +321,13 @@ class VQKVCache:
 
     def reset(self):
         check(lib().ojasx_b200_kvq_reset(self._h), "ojasx_b200_kvq_reset")
+
+    def set_static_plan(self, enabled: bool = True):
+        """Plan launches for the capacity and consult only device-side lengths (needed under CUDA-graph replay)."""
+        check(lib().ojasx_b200_kvq_set_static_plan(self._h, int(enabled)), "ojasx_b200_kvq_set_static_plan")
+
+    def sync_len(self) -> int:
+        return lib().ojasx_b200_kvq_sync_len(self._h)
 
     def append(self, k: torch.Tensor, v: torch.Tensor):
         _require_cuda(k, "k")

@@ -87,3 +87,17 @@ def test_decoder_stack_logits_and_greedy_tokens(cuda, oracle):
             logits = ref.step(nxt)
     with pytest.raises(ValueError):
         eng.generate(torch.from_numpy(prompt).to(cuda), max_new_tokens=40)
+
+
+def test_decoder_stack_graph_replay_equals_eager(cuda):
+    """One captured decode step replayed per token gives the same logits as the eager launch sequence."""
+    W = ie.make_stack_weights(12, CFG)
+    eager = ie.VQDecoderStack(W, CFG, batch=2)
+    graph = ie.VQDecoderStack(W, CFG, batch=2, use_graph=True)
+    toks = np.random.default_rng(0).integers(0, CFG.vocab, size=(2, 9))
+    for s in range(toks.shape[1]):
+        ids = torch.from_numpy(toks[:, s])
+        a = eager.decode_step(ids)
+        b = graph.decode_step(ids).clone()
+        assert torch.equal(a, b), s
+    assert graph.layers[0].cache.sync_len() == 9
