@@ -207,29 +207,47 @@ __global__ void __launch_bounds__(kKvThreads) kvq_decode_kernel(const __grid_con
         __syncthreads();
     }
 
-    // values: thread = (token stripe, output column); R accumulators
+    // values: thread = (group g, token stripe); it gathers whole centroids (D floats) and keeps the
+    // R x D partial outputs of its group in registers, so a token costs one code read, D/4 128-bit
+    // gathers and one read of its R probabilities per group.  Stripes are then added in a fixed order.
     {
-        const int col = tid % hd, half = tid / hd, halves = blockDim.x / hd;  // blockDim.x is a multiple of hd
-        const int g = col / D, d = col - g * D;
-        float o[R];
+        // threads per group; capped so that the stripe partials fit in the query-table area (G*256*R floats)
+        const int stripes = min((int)blockDim.x / G, 256 / D);
+        const int g = tid / stripes, st = tid - g * stripes;
+        float o[R][D];
 #pragma unroll
-        for (int r = 0; r < R; ++r) o[r] = 0.0f;
-        for (int t = half; t < n; t += halves) {
-            const float v = vcb[(int)vcs[(size_t)t * G + g] * D + d];
+        for (int r = 0; r < R; ++r)
 #pragma unroll
-            for (int r = 0; r < R; ++r) o[r] = fmaf(sc[(size_t)t * R + r], v, o[r]);
-        }
-        // combine the token stripes in a fixed order
-        for (int hh = 0; hh < halves; ++hh) {
-            if (half == hh) {
+            for (int d = 0; d < D; ++d) o[r][d] = 0.0f;
+        if (g < G) {
+            for (int t = st; t < n; t += stripes) {
+                const float* cv = vcb + (int)vcs[(size_t)t * G + g] * D;
+                float v[D], p[R];
 #pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    float* dst = osum + (size_t)r * hd + col;
-                    *dst = hh == 0 ? o[r] : *dst + o[r];
-                }
+                for (int d = 0; d < D; ++d) v[d] = cv[d];
+#pragma unroll
+                for (int r = 0; r < R; ++r) p[r] = sc[(size_t)t * R + r];
+#pragma unroll
+                for (int r = 0; r < R; ++r)
+#pragma unroll
+                    for (int d = 0; d < D; ++d) o[r][d] = fmaf(p[r], v[d], o[r][d]);
             }
-            __syncthreads();
         }
+        __syncthreads();                                      // the query table is dead: reuse it for the stripe partials
+        float* stripe_out = lut;                              // [stripes][R][hd]
+        if (g < G) {
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+                for (int d = 0; d < D; ++d) stripe_out[((size_t)st * R + r) * hd + g * D + d] = o[r][d];
+        }
+        __syncthreads();
+        for (int i = tid; i < R * hd; i += blockDim.x) {
+            float acc = 0.0f;
+            for (int s2 = 0; s2 < stripes; ++s2) acc += stripe_out[(size_t)s2 * R * hd + i];
+            osum[i] = acc;
+        }
+        __syncthreads();
     }
     for (int i = tid; i < R * hd; i += blockDim.x) {
         const int r = i / hd, c = i - r * hd;
