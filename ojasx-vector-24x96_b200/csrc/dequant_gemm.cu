@@ -19,7 +19,8 @@
 
 namespace ojx {
 
-constexpr int kDqThreads = 160;      // 4 producer/epilogue warps + 1 MMA warp
+constexpr int kDqProducers = 256;    // 8 producer/epilogue warps: two threads per tile row, four code bytes each
+constexpr int kDqThreads = kDqProducers + 32;   // + 1 MMA warp
 constexpr int kDqBlockM = 128;
 constexpr int kDqBlockK = 64;        // bf16 elements per K tile = one 128-byte swizzle row
 constexpr int kDqStages = 4;        // most stages; wide batch tiles use 3 to fit shared memory
@@ -35,7 +36,7 @@ __device__ unsigned long long g_dq_phase[16];
 #define DQ_TICK_INIT do { } while (0)
 #endif
 
-constexpr int kDqCodeStride = 144;   // bytes between the code slots of neighbouring threads (128 + 16: fewer bank conflicts)
+constexpr int kDqCodeStride = 144;   // bytes between the code slots of neighbouring threads (2 x 64 + 16: fewer bank conflicts)
 
 __device__ __forceinline__ void cp_async16_zfill(void* smem_dst, const void* gsrc, int src_bytes) {
     unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
@@ -104,8 +105,8 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
     const int a_bytes = kDqBlockM * 128, b_bytes = N * 128, stage_bytes = a_bytes + b_bytes;
     unsigned char* tiles = dq_smem;                                   // [stages][A | B], 1024-byte aligned
     uint4* cb16 = reinterpret_cast<uint4*>(tiles + S * stage_bytes);   // [256] centroids as 8 bf16
-    unsigned char* code_stage = reinterpret_cast<unsigned char*>(cb16 + 256);   // [2][128 threads][kDqCodeStride], 16-byte aligned
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(code_stage + 2 * 128 * kDqCodeStride);
+    unsigned char* code_stage = reinterpret_cast<unsigned char*>(cb16 + 256);   // [256 threads][kDqCodeStride], 16-byte aligned
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(code_stage + kDqProducers * kDqCodeStride);
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * kDqStages + 1);
     int2* csr_s = reinterpret_cast<int2*>(tmem_slot + 2);                     // [csr_cap] (col, value bits), 8-byte aligned
     const unsigned full0 = smem_u32(bars), empty0 = full0 + 8 * kDqStages, accum = empty0 + 8 * kDqStages;
@@ -132,11 +133,11 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
             csr_s[i] = make_int2(P.csr.cols[csr_base + i], __float_as_int(P.csr.vals[csr_base + i]));
     }
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) { mbar_init(full0 + 8 * s, 128); mbar_init(empty0 + 8 * s, 1); }
+        for (int s = 0; s < S; ++s) { mbar_init(full0 + 8 * s, kDqProducers); mbar_init(empty0 + 8 * s, 1); }
         mbar_init(accum, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 4) {
+    if (warp == kDqProducers / 32) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((unsigned)P.tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -146,9 +147,10 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
     const unsigned tmem_base = *tmem_slot;
     bool ok = true;
 
-    if (warp < 4) {
-        // ---------------- producers: row m = m0 + tid
-        const int m = m0 + tid;
+    if (warp < kDqProducers / 32) {
+        // ---------------- producers: tile row = tid & 127, this thread owns code bytes [4*half, 4*half+4) of each K tile
+        const int trow = tid & 127, half = tid >> 7;
+        const int m = m0 + trow;
         const bool row_ok = m < P.row_stop;
         const uint8_t* crow = P.codes + (size_t)(row_ok ? m : P.row_start) * P.G;
         int cur = 0, cend = 0;
@@ -158,22 +160,22 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
         const float row_scale = (row_ok && P.scales) ? P.scales[m] : 1.0f;
         const float inv_scale = row_scale != 0.0f ? 1.0f / row_scale : 0.0f;
         const int csr_begin = cur;
-        const int r7 = tid & 7;
+        const int r7 = trow & 7;
         // Global-memory latency is kept off the per-tile critical path by asynchronous copies:
-        //  * this row's code bytes arrive in blocks of 16 K tiles (128 bytes) into a private,
+        //  * the row's code bytes arrive in blocks of 8 K tiles (64 bytes) into a private,
         //    double-buffered slot of shared memory, one block ahead of use;
-        //  * this thread's share of the X tile (N/16 chunks of 16 bytes) is copied straight into its
+        //  * this thread's share of the X tile (N/32 chunks of 16 bytes) is copied straight into its
         //    swizzled place in the stage buffer two K tiles ahead of use;
-        //  * the next outlier of the row is held in registers.
+        //  * the next outlier of the row is held in registers (outliers are staged in shared memory).
         constexpr int kPF = 2;
-        const int nx = (N * 8) >> 7;
-        unsigned char* my_codes = code_stage + tid * kDqCodeStride;           // [2][kDqCodeBlock] at stride 128*stride
-        auto issue_codes = [&](int blk) {   // K tiles [16*blk, 16*blk+16) -> buffer blk & 1
-            const int k0 = blk * 16;
+        const int total_x = N * 8;
+        unsigned char* my_codes = code_stage + tid * kDqCodeStride;           // [2][64 B] per thread
+        auto issue_codes = [&](int blk) {   // K tiles [8*blk, 8*blk+8) -> buffer blk & 1
+            const int k0 = blk * 8;
             if (k0 >= KT) return;
-            unsigned char* dst = my_codes + (blk & 1) * (128 * kDqCodeStride);
+            unsigned char* dst = my_codes + (blk & 1) * 64;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
+            for (int c = 0; c < 4; ++c) {
                 const int bytes = min(16, max(0, (KT - k0) * 8 - c * 16));
                 if (bytes > 0) cp_async16_zfill(dst + c * 16, crow + (size_t)k0 * 8 + c * 16, bytes);
             }
@@ -181,14 +183,13 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
         auto issue_x = [&](int kt) {       // requires the stage of tile kt to be free
             if (kt >= KT) return;
             unsigned char* B = tiles + (kt % S) * stage_bytes + a_bytes;
-            for (int q = 0; q < nx; ++q) {
-                const int i = tid + q * 128, r = i >> 3, c = i & 7;
+            for (int i = tid; i < total_x; i += kDqProducers) {
+                const int r = i >> 3, c = i & 7;
                 const bool in = r < nb;
                 cp_async16_zfill(B + (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4),
                                  P.x + (size_t)(b0 + (in ? r : 0)) * P.K + kt * kDqBlockK + c * 8, in ? 16 : 0);
             }
         };
-        // prologue: code blocks 0 and (later) 1, X tiles 0 .. kPF-1; one commit group per K tile from here on
         issue_codes(0);
         for (int t = 0; t < kPF; ++t) { issue_x(t); asm volatile("cp.async.commit_group;" ::: "memory"); }
         int col_next = 0x7fffffff;
@@ -209,27 +210,27 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
             if (!ok) break;
             if (tid == 0) DQ_TICK(0);
             issue_x(kn);
-            if ((kt & 15) == 0) issue_codes((kt >> 4) + 1);   // next code block rides in this tile's group
+            if ((kt & 7) == 0) issue_codes((kt >> 3) + 1);   // next code block rides in this tile's group
             asm volatile("cp.async.commit_group;" ::: "memory");
             asm volatile("cp.async.wait_group %0;" ::"n"(kPF) : "memory");   // copies of tile kt (and its code block) have landed
             if (tid == 0) DQ_TICK(1);
             unsigned char* A = tiles + s * stage_bytes;
-            const uint2 cw = *reinterpret_cast<const uint2*>(my_codes + ((kt >> 4) & 1) * (128 * kDqCodeStride) + (kt & 15) * 8);
-            // A: eight codes of this row -> eight 16-byte chunks, chunk index XOR (row % 8)
-            unsigned char* arow = A + (tid >> 3) * 1024 + r7 * 128;
-            uint4 wv[8];   // all eight gathers first, then the eight stores (the compiler cannot reorder them itself)
+            const unsigned cw = *reinterpret_cast<const unsigned*>(my_codes + ((kt >> 3) & 1) * 64 + (kt & 7) * 8 + half * 4);
+            // A: four codes of this row -> four 16-byte chunks, chunk index XOR (row % 8)
+            unsigned char* arow = A + (trow >> 3) * 1024 + r7 * 128;
+            uint4 wv[4];   // all gathers first, then the stores (the compiler cannot reorder them itself)
 #pragma unroll
-            for (int gl = 0; gl < 8; ++gl) {
-                const unsigned code = ((gl < 4 ? cw.x : cw.y) >> ((gl & 3) * 8)) & 0xffu;
-                wv[gl] = row_ok ? cb16[code] : make_uint4(0, 0, 0, 0);
+            for (int q = 0; q < 4; ++q) {
+                const unsigned code = (cw >> (q * 8)) & 0xffu;
+                wv[q] = row_ok ? cb16[code] : make_uint4(0, 0, 0, 0);
             }
 #pragma unroll
-            for (int gl = 0; gl < 8; ++gl) *reinterpret_cast<uint4*>(arow + ((gl ^ r7) << 4)) = wv[gl];
-            // CSR outliers of this row inside the tile (columns ascending): w += value / scale, rounded to bf16
+            for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(arow + (((half * 4 + q) ^ r7) << 4)) = wv[q];
+            // CSR outliers of this row inside this thread's half of the tile (columns ascending): w += value / scale
             const int kend = (kt + 1) * kDqBlockK;
             while (col_next < kend) {
                 const int kk = col_next - kt * kDqBlockK;
-                if (kk >= 0) {
+                if (kk >= 0 && (kk >> 5) == half) {
                     __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(arow + (((kk >> 3) ^ r7) << 4)) + (kk & 7);
                     *e = __float2bfloat16_rn(__bfloat162float(*e) + val_next);
                 }
@@ -242,24 +243,24 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
             if (tid == 0) DQ_TICK(3);
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
-        // ---------------- epilogue: accumulator row tid of the tile
+        // ---------------- epilogue: accumulator row trow; the two threads of a row split the batch columns
         if (ok) ok = mbar_wait(accum, 0);
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float sc = (row_ok && P.scales) ? P.scales[m] : 1.0f;
+            const float sc = row_scale;
             const float bi = (row_ok && P.bias) ? P.bias[m] : 0.0f;
-            for (int c0 = 0; c0 < N; c0 += 16) {
-                unsigned v[16];
-                const unsigned taddr = tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)c0;
+            const int cbeg = half * (N >> 1), cstop = cbeg + (N >> 1);
+            for (int c0 = cbeg; c0 < cstop; c0 += 8) {
+                unsigned v[8];
+                const unsigned taddr = tmem_base + ((unsigned)((warp & 3) * 32) << 16) + (unsigned)c0;
                 asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                      "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                    "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
                     : "r"(taddr));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (row_ok) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
+                    for (int j = 0; j < 8; ++j) {
                         const int b = c0 + j;
                         if (b < nb) {
                             float r = fmaf(__uint_as_float(v[j]), sc, bi);
@@ -302,7 +303,7 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
     if (!ok && P.error_flag) atomicExch(P.error_flag, 1);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 4) {
+    if (warp == kDqProducers / 32) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)P.tmem_cols) : "memory");
     }
@@ -310,7 +311,7 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
 
 size_t dequant_gemm_smem(int n_pad, int stages, int csr_cap) {
     return (size_t)stages * (kDqBlockM * 128 + (size_t)n_pad * 128) + 256 * 16 + (2 * kDqStages + 1) * 8 + 16 +
-           2 * 128 * kDqCodeStride + (size_t)csr_cap * 8 + 1024;
+           kDqProducers * kDqCodeStride + (size_t)csr_cap * 8 + 1024;
 }
 
 static __device__ int g_dq_error;  // raised when a bounded wait inside the kernel ran out
