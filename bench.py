@@ -324,6 +324,7 @@ def bench_moe(args, dev, rank, world):
     per = E // world
     moe = ops.VQMoE(w, (rank * per, (rank + 1) * per))
     out = {"experts_per_gpu": per, "csr": bool(args.moe_csr)}
+    peak, _ = measured_peak_hbm()
     for B in (1, 32, 256):
         x = torch.randn(B, 2560, device=dev, generator=torch.Generator(device=dev).manual_seed(5))
         y = torch.empty_like(x)
@@ -349,7 +350,34 @@ def bench_moe(args, dev, rank, world):
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-        out[f"B{B}"] = {"ms_per_layer": round(ms, 4), "tokens_per_s": round(B / ms * 1e3, 1)}
+        # algorithmic code bytes: every distinct routed expert's 614,400 code bytes once, plus the router
+        idx, _w = moe.route(x, 10)
+        distinct = int(torch.unique(idx).numel())
+        code_bytes = distinct * w.code_bytes_per_expert() + w.router.nbytes
+        out[f"B{B}"] = {"ms_per_layer": round(ms, 4), "tokens_per_s": round(B / ms * 1e3, 1),
+                        "distinct_experts": distinct, "code_gbs": round(code_bytes / ms / 1e6, 1),
+                        "hbm_frac_of_measured": round(code_bytes / ms / 1e6 / peak / world, 4)}
+    if rank == 0 and world == 1 and args.cpu_seconds > 0:
+        # the reference's own CPU MoE (single token, single thread by construction, no outliers) beside it
+        try:
+            from oracle import oracle as O
+            if O.ref_available():
+                ref = O.RefLib()
+                h = ref.make_moe(w.codebook, w.down_codebook, w.gate_up_codes, w.gate_up_scales, w.down_codes,
+                                 w.down_scales, block_dim=8)
+                xi = np.random.default_rng(1).standard_normal(2560).astype(np.float32)
+                ii = np.arange(0, 500, 50, dtype=np.int32)
+                wi = np.full(10, 0.1, np.float32)
+                ref.moe_forward_handle(h, xi, ii, wi, 2560)
+                n, t0 = 0, time.perf_counter()
+                while time.perf_counter() - t0 < min(3.0, args.cpu_seconds):
+                    ref.moe_forward_handle(h, xi, ii, wi, 2560)
+                    n += 1
+                us = (time.perf_counter() - t0) / n * 1e6
+                out["cpu_reference"] = {"us_per_token": round(us, 1), "tokens_per_s": round(1e6 / us, 1), "cores": 1,
+                                        "kind": "reference", "sample": f"{n} calls of ojasx_moe_forward, top-10 of 512, no outliers"}
+        except Exception as ex:
+            out["cpu_reference"] = {"error": repr(ex)}
     return out
 
 
@@ -412,8 +440,17 @@ def bench_kv(args, dev):
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / reps
         bytes_ = B * ctx * 256
-        out[f"B{B}_ctx{ctx}"] = {"us_append_plus_decode": round(ms * 1e3, 2), "code_gbs": round(bytes_ / ms / 1e6, 1)}
+        out[f"B{B}_ctx{ctx}"] = {"us_append_plus_decode": round(ms * 1e3, 2), "code_gbs": round(bytes_ / ms / 1e6, 1),
+                                 "hbm_frac_of_measured": round(bytes_ / ms / 1e6 / measured_peak_hbm()[0], 4)}
         cache.close()
+    if args.cpu_seconds > 0:
+        # CPU restatement (fp64 port; the reference has no codebook-VQ cache) on one KV head of ctx 2048, scaled to 8 heads
+        from oracle import oracle as O
+        kv = synth.make_vq_kv(3, 1, 2048)
+        t0 = time.perf_counter()
+        O.kvq_decode(kv.q[0, :4], kv.k_codes[0, 0], kv.v_codes[0, 0], kv.k_codebook[0], kv.v_codebook[0], block_dim=8)
+        out["cpu_port_B1_ctx2048"] = {"us": round((time.perf_counter() - t0) * 8e6, 1), "cores": 1, "kind": "port",
+                                      "sample": "one KV head (4 query heads) x 8"}
     return out
 
 

@@ -252,8 +252,11 @@ int ojasx_linear_forward(OjasxLinearHandle handle, const float* x, float* y, int
     // x: host copy into pinned staging, then one asynchronous H2D copy.  y: the kernel stores its
     // results straight into device-mapped pinned memory, so no D2H copy is enqueued; after the
     // stream synchronises the results are in host memory and are copied to the caller's buffer.
-    void* y_dev = nullptr;
-    OJX_CUDA_TRY(cudaHostGetDevicePointer(&y_dev, h->pin_y, 0));
+    if (h->pin_y_dev == nullptr || h->pin_y_dev_of != h->pin_y) {
+        OJX_CUDA_TRY(cudaHostGetDevicePointer(&h->pin_y_dev, h->pin_y, 0));
+        h->pin_y_dev_of = h->pin_y;
+    }
+    void* y_dev = h->pin_y_dev;
     std::memcpy(h->pin_x, x, xb);
     OJX_CUDA_TRY(cudaMemcpyAsync(h->d_x, h->pin_x, xb, cudaMemcpyHostToDevice, h->stream));
     rc = launch_linear(h->problem(h->d_x, y_dev, batch_size, OJX_F32, 0, h->out), h->stream);

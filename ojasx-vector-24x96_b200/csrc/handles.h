@@ -40,6 +40,8 @@ struct LinearHandle {
     void* pin_x = nullptr;     // pinned host staging for x (source of an asynchronous copy)
     void* pin_y = nullptr;     // pinned, device-mapped host staging for y (written by the kernel itself)
     size_t cap_pin_x = 0, cap_pin_y = 0;
+    void* pin_y_dev = nullptr;     // device alias of pin_y (cached)
+    void* pin_y_dev_of = nullptr;  // the pin_y it was taken from
     cudaStream_t stream = nullptr;
 
     ~LinearHandle();

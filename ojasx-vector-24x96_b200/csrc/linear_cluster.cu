@@ -229,7 +229,8 @@ lut_linear_cluster_kernel(const __grid_constant__ LinearProblem P, const __grid_
 template <int D>
 static int launch_cluster_t(const LinearProblem& P, ClusterPlan plan, cudaStream_t stream, bool dry_run) {
     auto kern = lut_linear_cluster_kernel<D>;
-    OJX_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem));
+    // query_max_clusters<D> already opted this kernel in to kClSmemCap bytes of dynamic shared memory on
+    // this device (plans never exceed it), so nothing has to be set per launch.
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(kClThreads);
     cfg.dynamicSmemBytes = plan.smem;
