@@ -350,7 +350,8 @@ int ojasx_b200_kvq_decode(OjasxKvqHandle handle, const void* d_q, void* d_out, f
     P.chunk = chunk;
     P.n_chunks = (T + chunk - 1) / chunk;
     const int R = h->Hq / h->Hkv;
-    const size_t need = sizeof(float) * (size_t)heads * P.n_chunks * R * (h->head_dim + 2);
+    // sized once for the cache's capacity (chunks are at least 256 tokens), so a growing context never reallocates
+    const size_t need = sizeof(float) * (size_t)heads * ((h->max_seq + 255) / 256) * R * (h->head_dim + 2);
     DeviceGuard g(h->dev);
     int rc = ensure_capacity(&h->partials, &h->partials_cap, need);
     if (rc != OJX_OK) return rc;
