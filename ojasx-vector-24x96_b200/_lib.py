@@ -9,7 +9,29 @@ LIB_PATH = os.path.join(PKG_DIR, "libojasx_lut_b200.so")
 
 _vp, _i, _sz, _f = C.c_void_p, C.c_int, C.c_size_t, C.c_float
 
-# name -> (restype, argtypes); mirrors include/ojasx_lut_b200.h
+
+
+class GgmlTensor(C.Structure):
+    """``struct ojasx_ggml_tensor`` of include/ojasx_ggml_b200.h (ojasx_ggml_adapter.h:35-41)."""
+    _fields_ = [("type", C.c_int), ("ne", C.c_int64 * 4), ("nb", C.c_size_t * 4), ("data", C.c_void_p),
+                ("extra", C.c_void_p)]
+
+    @classmethod
+    def of(cls, array=None, extra=None, type_=0):
+        """Describes a C-contiguous float32 numpy array (GGML order: innermost extent first)."""
+        t = cls()
+        t.type = type_
+        shape = list(array.shape[::-1]) if array is not None else []
+        strides = list(array.strides[::-1]) if array is not None else []
+        for i in range(4):
+            t.ne[i] = shape[i] if i < len(shape) else 1
+            t.nb[i] = strides[i] if i < len(strides) else (strides[-1] * shape[-1] if strides else 0)
+        t.data = array.ctypes.data if array is not None else None
+        t.extra = extra
+        return t
+
+
+# name -> (restype, argtypes); mirrors include/ojasx_lut_b200.h and include/ojasx_ggml_b200.h
 SIGNATURES = {
     "ojasx_get_version": (C.c_char_p, []),
     "ojasx_get_backend_name": (C.c_char_p, []),
@@ -21,6 +43,10 @@ SIGNATURES = {
     "ojasx_get_lut_sram_size": (_sz, [_vp]),
     "ojasx_get_compression_ratio": (_f, [_vp]),
     "ojasx_destroy_linear": (None, [_vp]),
+    "ojasx_ggml_init": (_i, []),
+    "ojasx_ggml_forward_linear": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
+    "ojasx_ggml_forward_moe": (_i, [_vp, _vp, _vp, _vp, _i, _vp]),
+    "ojasx_ggml_forward_kv_attention": (_i, [_vp, _vp, _i, _f, _vp]),
     "ojasx_b200_last_error": (C.c_char_p, []),
     "ojasx_b200_launch_count": (C.c_ulonglong, []),
     "ojasx_b200_linear_forward": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),

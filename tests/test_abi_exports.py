@@ -67,6 +67,9 @@ def test_null_arguments_are_rejected_without_a_gpu(built_lib):
     assert L.ojasx_b200_linear_forward(None, None, None, 1, 0, 0, 1, None) == -1
     assert L.ojasx_b200_moe_forward(None, None, None, None, None, 1, 1, 0, None) == -1
     assert L.ojasx_b200_kvq_decode(None, None, None, 1.0, 0, None) == -1
+    assert L.ojasx_ggml_forward_linear(None, None, None, 0, 1, None) == -1       # ojasx_ggml_adapter.cpp:37
+    assert L.ojasx_ggml_forward_moe(None, None, None, None, 1, None) == -1           # :68
+    assert L.ojasx_ggml_forward_kv_attention(None, None, 0, 1.0, None) == -1         # :85
     L.ojasx_destroy_linear(None)
     L.ojasx_destroy_moe(None)
     L.ojasx_destroy_kv_cache(None)
