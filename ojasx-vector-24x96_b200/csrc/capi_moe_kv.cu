@@ -324,6 +324,8 @@ static KvqProblem kvq_problem(const KvqHandle* h, int io) {
     return P;
 }
 
+static int kvq_max_splits(int max_seq) { return std::min(kKvMaxSplits, (max_seq + 255) / 256); }
+
 int ojasx_b200_kvq_append(OjasxKvqHandle handle, const void* d_k, const void* d_v, int io_dtype, void* stream) {
     if (!handle || !d_k || !d_v || (io_dtype != OJX_F32 && io_dtype != OJX_BF16)) return OJX_ERR_ARG;
     auto* h = static_cast<KvqHandle*>(handle);
@@ -342,16 +344,11 @@ int ojasx_b200_kvq_decode(OjasxKvqHandle handle, const void* d_q, void* d_out, f
     KvqProblem P = kvq_problem(h, io_dtype);
     P.q = d_q; P.out = d_out;
     P.scale = scale > 0.0f ? scale : 1.0f / std::sqrt((float)h->head_dim);
-    // Context chunks: enough CTAs to fill the GPU about twice, chunks of 256..2048 tokens.
-    const int T = h->static_plan ? h->max_seq : h->host_len, heads = h->B * h->Hkv, sms = num_sms();
-    int want = std::max(1, (2 * sms + heads - 1) / heads);
-    int chunk = round_up((T + want - 1) / want, 256);
-    chunk = std::min(2048, std::max(256, chunk));
-    P.chunk = chunk;
-    P.n_chunks = (T + chunk - 1) / chunk;
+    const int T = h->static_plan ? h->max_seq : h->host_len, heads = h->B * h->Hkv;
+    plan_kvq_decode(P, T, num_sms());
     const int R = h->Hq / h->Hkv;
-    // sized once for the cache's capacity (chunks are at least 256 tokens), so a growing context never reallocates
-    const size_t need = sizeof(float) * (size_t)heads * ((h->max_seq + 255) / 256) * R * (h->head_dim + 2);
+    // sized once for the largest split count, so a growing context never reallocates
+    const size_t need = sizeof(float) * (size_t)heads * kvq_max_splits(h->max_seq) * R * (h->head_dim + 2);
     DeviceGuard g(h->dev);
     int rc = ensure_capacity(&h->partials, &h->partials_cap, need);
     if (rc != OJX_OK) return rc;
@@ -366,8 +363,7 @@ int ojasx_b200_kvq_set_static_plan(OjasxKvqHandle handle, int enabled) {
     if (h->static_plan) {   // size the chunk scratch for the full capacity now, so that decode never allocates
         DeviceGuard g(h->dev);
         const int heads = h->B * h->Hkv, R = h->Hq / h->Hkv;
-        const int n_chunks = (h->max_seq + 255) / 256;
-        const size_t need = sizeof(float) * (size_t)heads * n_chunks * R * (h->head_dim + 2);
+        const size_t need = sizeof(float) * (size_t)heads * kvq_max_splits(h->max_seq) * R * (h->head_dim + 2);
         return ensure_capacity(&h->partials, &h->partials_cap, need);
     }
     return OJX_OK;

@@ -11,6 +11,8 @@
 // (2) The reference's cache as shipped ("legacy"): int8 of each block's first coordinate with a
 //     per-token abs-max scale (ojasx_lut_kv_cache.cpp:16-132, softmax of
 //     ojasx_lut_c_api.cpp:178-191).
+#include <algorithm>
+
 #include "common.cuh"
 #include "launch.h"
 #include "handles.h"
@@ -19,6 +21,7 @@ namespace ojx {
 
 constexpr int kKvThreads = 256;
 constexpr int kKvMaxGroups = 32;  // head_dim / block_dim
+
 
 __device__ __forceinline__ float load_io(const void* p, size_t i, int dtype) {
     return dtype == OJX_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i])
@@ -86,48 +89,80 @@ __global__ void kvq_bump_kernel(int* seq_lens, int B, int max_seq, int* error_fl
 }
 
 // ------------------------------------------------------------------------------ kvq decode
-// grid = (chunks, Hkv, B).  Shared memory: query table [G,256,R] fp32, value codebook [256,D],
-// the R queries, the chunk's scores/probabilities [chunk, R] and its key and value codes.
-template <int R, int D>
-__global__ void __launch_bounds__(kKvThreads) kvq_decode_kernel(const __grid_constant__ KvqProblem P) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int G = P.G, hd = P.head_dim, tid = threadIdx.x;
-    float* lut = reinterpret_cast<float*>(smem_raw);               // [G*256*R]
-    float* vcb = lut + (size_t)G * 256 * R;                        // [256*D]
-    float* qs = vcb + 256 * D;                                     // [R*hd]
-    float* sc = qs + R * hd;                                       // [chunk*R]
-    float* red = sc + (size_t)P.chunk * R;                         // [kKvThreads]
-    float* osum = red + kKvThreads;                                // [R*hd]
-    uint8_t* kcs = reinterpret_cast<uint8_t*>(osum + R * hd);      // [chunk*G]
-    uint8_t* vcs = kcs + (size_t)P.chunk * G;                      // [chunk*G]
+// grid = (splits, Hkv, B); a CTA owns tokens [split*chunk, (split+1)*chunk) of one (sequence, KV head)
+// and walks them in passes of kKvSub tokens with a running maximum (online softmax), so the query
+// table is built once per CTA however long its range is.
+//
+// One pass: (1) thread per token: its K codes (one 16-byte load when G is a multiple of 16) index the
+// query table [G,256,R], R heads per 128-bit gather; its V codes are stored transposed, [g][token], for
+// the value phase; warp maxima go to shared memory.  (2) after a barrier every thread knows the new
+// running maximum, turns its own scores into probabilities, and rescales its accumulators.  (3) after
+// a second barrier thread = (group, token stripe) gathers whole centroids of the value codebook (stored
+// as D/4 arrays of float4 so that a gather's bank depends on all low code bits) and keeps the R x D
+// partial outputs of its group in registers.  Score, probability and code buffers are double-buffered,
+// so a pass costs two barriers.
+constexpr int kKvSub = 2 * kKvThreads;   // tokens per pass
+constexpr int kKvVctPad = 16;            // bytes of padding per transposed code row (bank spread)
 
-    const int b = blockIdx.z, h = blockIdx.y, ch = blockIdx.x;
+// R consecutive floats at a 4*R-byte aligned shared-memory address, as 128-bit (R % 4 == 0) or 64-bit (R == 2) accesses
+template <int R>
+__device__ __forceinline__ void ld_heads(const float* p, float (&o)[R]) {
+    if constexpr (R % 4 == 0) {
+#pragma unroll
+        for (int q = 0; q < R / 4; ++q) {
+            const float4 f = reinterpret_cast<const float4*>(p)[q];
+            o[q * 4 + 0] = f.x; o[q * 4 + 1] = f.y; o[q * 4 + 2] = f.z; o[q * 4 + 3] = f.w;
+        }
+    } else if constexpr (R == 2) {
+        const float2 f = *reinterpret_cast<const float2*>(p);
+        o[0] = f.x; o[1] = f.y;
+    } else {
+#pragma unroll
+        for (int r = 0; r < R; ++r) o[r] = p[r];
+    }
+}
+template <int R>
+__device__ __forceinline__ void st_heads(float* p, const float (&o)[R]) {
+    if constexpr (R % 4 == 0) {
+#pragma unroll
+        for (int q = 0; q < R / 4; ++q) reinterpret_cast<float4*>(p)[q] = make_float4(o[q * 4], o[q * 4 + 1], o[q * 4 + 2], o[q * 4 + 3]);
+    } else if constexpr (R == 2) {
+        *reinterpret_cast<float2*>(p) = make_float2(o[0], o[1]);
+    } else {
+#pragma unroll
+        for (int r = 0; r < R; ++r) p[r] = o[r];
+    }
+}
+
+template <int R, int D>
+__global__ void __launch_bounds__(kKvThreads, (R * 4 <= 16 ? 2 : 1)) kvq_decode_kernel(const __grid_constant__ KvqProblem P) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int kWarps = kKvThreads / 32, kPieces = D / 4, kTpt = kKvSub / kKvThreads;
+    const int G = P.G, hd = P.head_dim, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    float* lut = reinterpret_cast<float*>(smem_raw);               // [G][256][R]
+    float* vcb = lut + (size_t)G * 256 * R;                        // [D/4][256] float4
+    float* qs = vcb + 256 * D;                                     // [R*hd]; the summed output at the end
+    float* sc = qs + R * hd;                                       // [2][kKvSub*R]
+    float* wred = sc + 2 * (size_t)kKvSub * R;                     // [2][warps][R]
+    uint8_t* vct = reinterpret_cast<uint8_t*>(wred + 2 * kWarps * R);  // [2][G][kKvSub + pad]
+    const int vrow = kKvSub + kKvVctPad;
+
+    const int b = blockIdx.z, h = blockIdx.y, split = blockIdx.x;
     const int T = P.seq_lens[b];
-    const int t0 = ch * P.chunk;
-    const int n = min(P.chunk, T - t0);
-    float* part = P.partials + ((((size_t)b * P.Hkv + h) * P.n_chunks + ch) * R) * (hd + 2);
-    if (n <= 0) {  // chunk beyond this sequence: neutral partial
+    const int t_begin = split * P.chunk;
+    const int t_end = min(T, t_begin + P.chunk);
+    float* part = P.partials + ((((size_t)b * P.Hkv + h) * P.n_chunks + split) * R) * (hd + 2);
+    if (t_begin >= t_end) {  // range beyond this sequence: neutral partial
         for (int i = tid; i < R * (hd + 2); i += blockDim.x) part[i] = (i % (hd + 2)) == 0 ? -INFINITY : 0.0f;
         return;
     }
-    const uint8_t* kc = P.k_codes + (((size_t)b * P.Hkv + h) * P.max_seq + t0) * G;
-    const uint8_t* vc = P.v_codes + (((size_t)b * P.Hkv + h) * P.max_seq + t0) * G;
+    const uint8_t* kc = P.k_codes + (((size_t)b * P.Hkv + h) * P.max_seq) * G;
+    const uint8_t* vc = P.v_codes + (((size_t)b * P.Hkv + h) * P.max_seq) * G;
 
-    // stage codes (coalesced 16-byte copies when the chunk start is aligned), queries, value codebook
-    {
-        const size_t bytes = (size_t)n * G;
-        if (((reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc)) & 15) == 0) {
-            const int n16 = (int)(bytes >> 4);
-            for (int i = tid; i < n16; i += blockDim.x) {
-                reinterpret_cast<uint4*>(kcs)[i] = reinterpret_cast<const uint4*>(kc)[i];
-                reinterpret_cast<uint4*>(vcs)[i] = reinterpret_cast<const uint4*>(vc)[i];
-            }
-            for (int i = (n16 << 4) + tid; i < (int)bytes; i += blockDim.x) { kcs[i] = kc[i]; vcs[i] = vc[i]; }
-        } else {
-            for (int i = tid; i < (int)bytes; i += blockDim.x) { kcs[i] = kc[i]; vcs[i] = vc[i]; }
-        }
-        for (int i = tid; i < R * hd; i += blockDim.x) qs[i] = load_io(P.q, ((size_t)b * P.Hq + (size_t)h * R) * hd + i, P.io_dtype);
-        for (int i = tid; i < 256 * D; i += blockDim.x) vcb[i] = i < P.Kcb * D ? P.v_cb[(size_t)h * P.Kcb * D + i] : 0.0f;
+    for (int i = tid; i < R * hd; i += blockDim.x) qs[i] = load_io(P.q, ((size_t)b * P.Hq + (size_t)h * R) * hd + i, P.io_dtype);
+    for (int i = tid; i < 256 * D; i += blockDim.x) {
+        const int c = i / D, d = i - c * D;
+        vcb[((d >> 2) * 256 + c) * 4 + (d & 3)] = c < P.Kcb ? P.v_cb[((size_t)h * P.Kcb + c) * D + d] : 0.0f;
     }
     __syncthreads();
     // query table: thread c owns centroid c
@@ -144,118 +179,162 @@ __global__ void __launch_bounds__(kKvThreads) kvq_decode_kernel(const __grid_con
                 for (int d = 0; d < D; ++d) dot = fmaf(qs[r * hd + g * D + d], c[d], dot);
                 e[r] = dot;
             }
-#pragma unroll
-            for (int r = 0; r < R; ++r) lut[((size_t)g * 256 + tid) * R + r] = e[r];
+            st_heads<R>(lut + ((size_t)g * 256 + tid) * R, e);
         }
     }
     __syncthreads();
 
-    // scores: one thread per token, R heads at once
-    float mloc[R];
-#pragma unroll
-    for (int r = 0; r < R; ++r) mloc[r] = -INFINITY;
-    for (int t = tid; t < n; t += blockDim.x) {
-        float acc[R];
-#pragma unroll
-        for (int r = 0; r < R; ++r) acc[r] = 0.0f;
-        const uint8_t* row = kcs + (size_t)t * G;
-        for (int g = 0; g < G; ++g) {
-            const float* e = lut + ((size_t)g * 256 + row[g]) * R;
-#pragma unroll
-            for (int r = 0; r < R; ++r) acc[r] += e[r];
-        }
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const float s = acc[r] * P.scale;
-            sc[(size_t)t * R + r] = s;
-            mloc[r] = fmaxf(mloc[r], s);
-        }
-    }
-    // chunk max and normaliser per head (fixed-shape tree: deterministic)
-    float mch[R], lch[R];
+    // value phase mapping: threads per group capped so that the stripe partials fit in the query-table area
+    const int stripes = min((int)blockDim.x / G, 256 / D);
+    const int vg = tid / stripes, vst = tid - vg * stripes;
+    float o[R][D], m_run[R], l_loc[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        red[tid] = mloc[r];
-        __syncthreads();
-        for (int s = blockDim.x / 2; s > 0; s >>= 1) {
-            if (tid < s) red[tid] = fmaxf(red[tid], red[tid + s]);
-            __syncthreads();
-        }
-        mch[r] = red[0];
-        __syncthreads();
-    }
-    float lloc[R];
+        m_run[r] = -INFINITY;
+        l_loc[r] = 0.0f;
 #pragma unroll
-    for (int r = 0; r < R; ++r) lloc[r] = 0.0f;
-    for (int t = tid; t < n; t += blockDim.x) {
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const float p = __expf(sc[(size_t)t * R + r] - mch[r]);
-            sc[(size_t)t * R + r] = p;
-            lloc[r] += p;
-        }
-    }
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-        red[tid] = lloc[r];
-        __syncthreads();
-        for (int s = blockDim.x / 2; s > 0; s >>= 1) {
-            if (tid < s) red[tid] += red[tid + s];
-            __syncthreads();
-        }
-        lch[r] = red[0];
-        __syncthreads();
+        for (int d = 0; d < D; ++d) o[r][d] = 0.0f;
     }
 
-    // values: thread = (group g, token stripe); it gathers whole centroids (D floats) and keeps the
-    // R x D partial outputs of its group in registers, so a token costs one code read, D/4 128-bit
-    // gathers and one read of its R probabilities per group.  Stripes are then added in a fixed order.
-    {
-        // threads per group; capped so that the stripe partials fit in the query-table area (G*256*R floats)
-        const int stripes = min((int)blockDim.x / G, 256 / D);
-        const int g = tid / stripes, st = tid - g * stripes;
-        float o[R][D];
+    int buf = 0;
+    for (int base = t_begin; base < t_end; base += kKvSub, buf ^= 1) {
+        const int n = min(kKvSub, t_end - base);
+        float* scb = sc + (size_t)buf * kKvSub * R;
+        float* wr = wred + buf * kWarps * R;
+        uint8_t* vt = vct + (size_t)buf * G * vrow;
+
+        // (1) scores of this thread's tokens
+        float s[kTpt][R], mloc[R];
 #pragma unroll
-        for (int r = 0; r < R; ++r)
+        for (int r = 0; r < R; ++r) mloc[r] = -INFINITY;
 #pragma unroll
-            for (int d = 0; d < D; ++d) o[r][d] = 0.0f;
-        if (g < G) {
-            for (int t = st; t < n; t += stripes) {
-                const float* cv = vcb + (int)vcs[(size_t)t * G + g] * D;
+        for (int j = 0; j < kTpt; ++j) {
+            const int t = tid + j * kKvThreads;
+            float acc[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) acc[r] = 0.0f;
+            if (t < n) {
+                const uint8_t* krow = kc + (size_t)(base + t) * G;
+                const uint8_t* vrow_g = vc + (size_t)(base + t) * G;
+                auto one = [&](int g, unsigned kcode, unsigned vcode) {
+                    float e[R];
+                    ld_heads<R>(lut + ((size_t)g * 256 + kcode) * R, e);
+#pragma unroll
+                    for (int r = 0; r < R; ++r) acc[r] += e[r];
+                    vt[(size_t)g * vrow + t] = (uint8_t)vcode;
+                };
+                int g = 0;
+                if ((G & 15) == 0) {
+                    for (; g < G; g += 16) {
+                        const uint4 kw = *reinterpret_cast<const uint4*>(krow + g);
+                        const uint4 vw = *reinterpret_cast<const uint4*>(vrow_g + g);
+                        const unsigned ka[4] = {kw.x, kw.y, kw.z, kw.w}, va[4] = {vw.x, vw.y, vw.z, vw.w};
+#pragma unroll
+                        for (int w = 0; w < 4; ++w)
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) one(g + w * 4 + q, (ka[w] >> (8 * q)) & 255u, (va[w] >> (8 * q)) & 255u);
+                    }
+                } else {
+                    for (; g < G; ++g) one(g, krow[g], vrow_g[g]);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                s[j][r] = t < n ? acc[r] * P.scale : -INFINITY;
+                mloc[r] = fmaxf(mloc[r], s[j][r]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) mloc[r] = fmaxf(mloc[r], __shfl_xor_sync(0xffffffffu, mloc[r], off));
+            if (lane == 0) wr[warp * R + r] = mloc[r];
+        }
+        __syncthreads();
+
+        // (2) new running maximum, probabilities, rescale
+        float alpha[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            float m = m_run[r];
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) m = fmaxf(m, wr[w * R + r]);
+            alpha[r] = __expf(m_run[r] - m);   // 0 on the first pass (m_run = -inf, m finite)
+            m_run[r] = m;
+            l_loc[r] *= alpha[r];
+#pragma unroll
+            for (int d = 0; d < D; ++d) o[r][d] *= alpha[r];
+        }
+#pragma unroll
+        for (int j = 0; j < kTpt; ++j) {
+            const int t = tid + j * kKvThreads;
+            if (t < n) {
+                float p[R];
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    p[r] = __expf(s[j][r] - m_run[r]);
+                    l_loc[r] += p[r];
+                }
+                st_heads<R>(scb + (size_t)t * R, p);
+            }
+        }
+        __syncthreads();
+
+        // (3) values
+        if (vg < G) {
+            const uint8_t* codes = vt + (size_t)vg * vrow;
+            for (int t = vst; t < n; t += stripes) {
+                const int c = codes[t];
                 float v[D], p[R];
 #pragma unroll
-                for (int d = 0; d < D; ++d) v[d] = cv[d];
-#pragma unroll
-                for (int r = 0; r < R; ++r) p[r] = sc[(size_t)t * R + r];
+                for (int q = 0; q < kPieces; ++q) {
+                    const float4 f = *reinterpret_cast<const float4*>(vcb + ((size_t)q * 256 + c) * 4);
+                    v[q * 4 + 0] = f.x; v[q * 4 + 1] = f.y; v[q * 4 + 2] = f.z; v[q * 4 + 3] = f.w;
+                }
+                ld_heads<R>(scb + (size_t)t * R, p);
 #pragma unroll
                 for (int r = 0; r < R; ++r)
 #pragma unroll
                     for (int d = 0; d < D; ++d) o[r][d] = fmaf(p[r], v[d], o[r][d]);
             }
         }
-        __syncthreads();                                      // the query table is dead: reuse it for the stripe partials
-        float* stripe_out = lut;                              // [stripes][R][hd]
-        if (g < G) {
-#pragma unroll
-            for (int r = 0; r < R; ++r)
-#pragma unroll
-                for (int d = 0; d < D; ++d) stripe_out[((size_t)st * R + r) * hd + g * D + d] = o[r][d];
-        }
-        __syncthreads();
-        for (int i = tid; i < R * hd; i += blockDim.x) {
-            float acc = 0.0f;
-            for (int s2 = 0; s2 < stripes; ++s2) acc += stripe_out[(size_t)s2 * R * hd + i];
-            osum[i] = acc;
-        }
-        __syncthreads();
+        // no barrier here: the next pass writes the other buffers, and the pass after that cannot reach
+        // its writes before every thread has passed the next pass's first barrier
     }
+
+    // normaliser: fixed-shape reduction (shuffle tree, then the warps in order)
+    __syncthreads();
+    float* lred = wred;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        float l = l_loc[r];
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+        if (lane == 0) lred[warp * R + r] = l;
+    }
+    // stripes of one group are added in a fixed order; the query table is dead, its area holds them
+    float* stripe_out = lut;                              // [stripes][R][hd]
+    if (vg < G) {
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int d = 0; d < D; ++d) stripe_out[((size_t)vst * R + r) * hd + vg * D + d] = o[r][d];
+    }
+    __syncthreads();
     for (int i = tid; i < R * hd; i += blockDim.x) {
+        float acc = 0.0f;
+        for (int s2 = 0; s2 < stripes; ++s2) acc += stripe_out[(size_t)s2 * R * hd + i];
         const int r = i / hd, c = i - r * hd;
-        part[(size_t)r * (hd + 2) + 2 + c] = osum[i];
+        part[(size_t)r * (hd + 2) + 2 + c] = acc;
     }
-    if (tid < R) {
-        part[(size_t)tid * (hd + 2) + 0] = mch[tid];
-        part[(size_t)tid * (hd + 2) + 1] = lch[tid];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        if (tid == r) {
+            float l = 0.0f;
+            for (int w = 0; w < kWarps; ++w) l += lred[w * R + r];
+            part[(size_t)r * (hd + 2) + 0] = m_run[r];
+            part[(size_t)r * (hd + 2) + 1] = l;
+        }
     }
 }
 
@@ -286,8 +365,30 @@ __global__ void kvq_combine_kernel(const __grid_constant__ KvqProblem P, int R) 
 }
 
 size_t kvq_decode_smem(const KvqProblem& P, int R) {
-    return sizeof(float) * ((size_t)P.G * 256 * R + 256 * (size_t)P.D + 2 * (size_t)R * P.head_dim + (size_t)P.chunk * R +
-                            kKvThreads) + 2 * (size_t)P.chunk * P.G;
+    return sizeof(float) * ((size_t)P.G * 256 * R + 256 * (size_t)P.D + (size_t)R * P.head_dim + 2 * (size_t)kKvSub * R +
+                            2 * (kKvThreads / 32) * (size_t)R) + 2 * (size_t)P.G * (kKvSub + kKvVctPad);
+}
+
+// Splits of the context: a CTA's range is a multiple of 256 tokens; among the split counts the one with
+// the least (waves of CTAs) x (range + the query-table build, worth about 160 tokens) wins.
+void plan_kvq_decode(KvqProblem& P, int T, int sms) {
+    const int R = P.Hq / P.Hkv, heads = P.B * P.Hkv;
+    const int slots = sms * (2 * (kvq_decode_smem(P, R) + 1024) <= 228 * 1024 ? 2 : 1);
+    const int max_s = std::min(kKvMaxSplits, (T + 255) / 256);
+    long best = -1;
+    P.chunk = round_up(std::max(T, 1), 256);
+    P.n_chunks = 1;
+    for (int s = 1; s <= max_s; ++s) {
+        const int span = round_up((T + s - 1) / s, 256);
+        const int n = (T + span - 1) / span;
+        const long waves = ((long)heads * n + slots - 1) / slots;
+        const long cost = waves * (span + 160);
+        if (best < 0 || cost < best) {
+            best = cost;
+            P.chunk = span;
+            P.n_chunks = n;
+        }
+    }
 }
 
 template <int D>
@@ -342,7 +443,7 @@ static int launch_decode_r(const KvqProblem& P, cudaStream_t s) {
 int launch_kvq_decode(const KvqProblem& P, cudaStream_t s) {
     if (!P.q || !P.out || !P.partials || !P.seq_lens) return OJX_ERR_ARG;
     if (P.G > kKvMaxGroups || P.Hq % P.Hkv != 0) return OJX_ERR_UNSUPPORTED;
-    if (P.head_dim > kKvThreads || kKvThreads % P.head_dim != 0) return OJX_ERR_UNSUPPORTED;
+    if (P.head_dim > 2 * kKvThreads || P.head_dim % 4 != 0) return OJX_ERR_UNSUPPORTED;
     switch (P.Hq / P.Hkv) {
         case 1: return launch_decode_r<1>(P, s);
         case 2: return launch_decode_r<2>(P, s);

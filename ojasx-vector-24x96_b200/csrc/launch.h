@@ -30,7 +30,10 @@ int launch_moe_router(const float* Wr, const void* x, int io_dtype, int n_tokens
                       float* logits, float* probs, int* idx_out, float* w_out, cudaStream_t stream);
 
 // --- kv.cu
+constexpr int kKvMaxSplits = 256;   // context splits of one (sequence, KV head) in kvq decode
 size_t kvq_decode_smem(const KvqProblem& P, int R);
+// Fills P.chunk (tokens per CTA) and P.n_chunks (<= kKvMaxSplits) for a context of T tokens.
+void plan_kvq_decode(KvqProblem& P, int T, int sms);
 int launch_kvq_append(const KvqProblem& P, cudaStream_t stream);
 int launch_kvq_decode(const KvqProblem& P, cudaStream_t stream);
 int launch_legacy_append(const float* k, const float* v, int head_dim, int block_dim, uint8_t* k_row, uint8_t* v_row,

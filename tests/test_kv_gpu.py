@@ -44,6 +44,27 @@ def test_kvq_append_then_decode(cuda, oracle, B, ctx):
     assert np.allclose(got_b, want_b, rtol=2e-2, atol=2e-3), np.abs(got_b - want_b).max()
 
 
+@pytest.mark.parametrize("B,ctx,kv_heads,q_heads,head_dim,block_dim,q_gain", [
+    (4, 8192, 8, 32, 128, 8, 6.0),     # ranges of 1024 tokens: two passes per CTA, peaked softmax (running-max rescale)
+    (8, 20000, 8, 32, 128, 8, 1.0),    # ranges of several thousand tokens with a ragged tail
+    (2, 1500, 4, 4, 64, 4, 3.0),       # one query head per KV head, block_dim 4
+    (3, 900, 2, 16, 128, 16, 3.0),     # eight query heads per KV head, block_dim 16 (8 groups: byte code loads)
+    (2, 700, 4, 8, 96, 8, 2.0),        # head_dim 96: 12 groups
+])
+def test_kvq_decode_shapes_and_long_ranges(cuda, oracle, B, ctx, kv_heads, q_heads, head_dim, block_dim, q_gain):
+    kv = synth.make_vq_kv(ctx + head_dim, B, ctx, kv_heads=kv_heads, q_heads=q_heads, head_dim=head_dim, block_dim=block_dim)
+    q = (kv.q * q_gain).astype(np.float32)
+    cache = ops.VQKVCache(B, kv_heads, q_heads, head_dim, block_dim, ctx + 300, kv.k_codebook, kv.v_codebook)
+    cache.load(kv.k_codes, kv.v_codes)
+    want = _oracle_decode(oracle, kv, kv.k_codes, kv.v_codes, q)
+    got = cache.decode(torch.from_numpy(q).to(cuda)).cpu().numpy()
+    assert np.allclose(got, want, rtol=1e-4, atol=2e-6), np.abs(got - want).max()
+    # planned for the capacity (the CUDA-graph mode): other splits, same tolerance
+    cache.set_static_plan(True)
+    again = cache.decode(torch.from_numpy(q).to(cuda)).cpu().numpy()
+    assert np.allclose(again, want, rtol=1e-4, atol=2e-6), np.abs(again - want).max()
+
+
 def test_kvq_full_and_errors(cuda):
     kv = synth.make_vq_kv(1, 1, 4)
     cache = ops.VQKVCache(1, 8, 32, 128, 8, 4, kv.k_codebook, kv.v_codebook)
