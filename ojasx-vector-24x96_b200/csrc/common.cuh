@@ -94,6 +94,7 @@ struct KvqProblem {
     float* partials;        // scratch [B, Hkv, n_chunks, R, head_dim + 2]
     int B, Hkv, Hq, head_dim, D, G, Kcb, max_seq;
     int chunk, n_chunks;
+    int v_copies;           // copies of the value codebook in the decode kernel's shared memory (1 or 8)
     int io_dtype;
     float scale;
 };

@@ -97,12 +97,17 @@ __global__ void kvq_bump_kernel(int* seq_lens, int B, int max_seq, int* error_fl
 // query table [G,256,R], R heads per 128-bit gather; its V codes are stored transposed, [g][token], for
 // the value phase; warp maxima go to shared memory.  (2) after a barrier every thread knows the new
 // running maximum, turns its own scores into probabilities, and rescales its accumulators.  (3) after
-// a second barrier thread = (group, token stripe) gathers whole centroids of the value codebook (stored
-// as D/4 arrays of float4 so that a gather's bank depends on all low code bits) and keeps the R x D
-// partial outputs of its group in registers.  Score, probability and code buffers are double-buffered,
-// so a pass costs two barriers.
-constexpr int kKvSub = 2 * kKvThreads;   // tokens per pass
-constexpr int kKvVctPad = 16;            // bytes of padding per transposed code row (bank spread)
+// a second barrier thread = (group, token stripe) gathers whole centroids of the value codebook and keeps
+// the R x D partial outputs of its group in registers.  Score, probability and code buffers are
+// double-buffered, so a pass costs two barriers.
+//
+// The kernel is bound by shared-memory wavefronts: a 128-bit gather is served eight lanes at a time, and
+// eight random addresses over eight 16-byte bank groups collide (10.8 wavefronts per warp instead of 4,
+// measured).  The value codebook is small, so when it fits it is stored eight times, copy q confined to
+// bank group q, and lane l reads copy l % 8: those gathers are conflict-free.
+// Threads per CTA: 512, or 256 where the R x D accumulators of a thread need more than 128 registers.
+constexpr int kvq_decode_threads(int R, int D) { return R * D > 64 ? 256 : 512; }
+constexpr int kKvVctPad = 16;               // bytes of padding per transposed code row (bank spread)
 
 // R consecutive floats at a 4*R-byte aligned shared-memory address, as 128-bit (R % 4 == 0) or 64-bit (R == 2) accesses
 template <int R>
@@ -135,13 +140,15 @@ __device__ __forceinline__ void st_heads(float* p, const float (&o)[R]) {
 }
 
 template <int R, int D>
-__global__ void __launch_bounds__(kKvThreads, (R * 4 <= 16 ? 2 : 1)) kvq_decode_kernel(const __grid_constant__ KvqProblem P) {
+__global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel(const __grid_constant__ KvqProblem P) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    constexpr int kWarps = kKvThreads / 32, kPieces = D / 4, kTpt = kKvSub / kKvThreads;
+    constexpr int kKvDecThreads = kvq_decode_threads(R, D), kKvSub = 2 * kKvDecThreads;   // tokens per pass
+    constexpr int kWarps = kKvDecThreads / 32, kPieces = D / 4, kTpt = kKvSub / kKvDecThreads;
     const int G = P.G, hd = P.head_dim, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     float* lut = reinterpret_cast<float*>(smem_raw);               // [G][256][R]
-    float* vcb = lut + (size_t)G * 256 * R;                        // [D/4][256] float4
-    float* qs = vcb + 256 * D;                                     // [R*hd]; the summed output at the end
+    const int vrep = P.v_copies;                                   // 1 or 8 copies of the value codebook
+    float* vcb = lut + (size_t)G * 256 * R;                        // [D/4][256][vrep] float4
+    float* qs = vcb + 256 * D * vrep;                              // [R*hd]
     float* sc = qs + R * hd;                                       // [2][kKvSub*R]
     float* wred = sc + 2 * (size_t)kKvSub * R;                     // [2][warps][R]
     uint8_t* vct = reinterpret_cast<uint8_t*>(wred + 2 * kWarps * R);  // [2][G][kKvSub + pad]
@@ -162,15 +169,17 @@ __global__ void __launch_bounds__(kKvThreads, (R * 4 <= 16 ? 2 : 1)) kvq_decode_
     for (int i = tid; i < R * hd; i += blockDim.x) qs[i] = load_io(P.q, ((size_t)b * P.Hq + (size_t)h * R) * hd + i, P.io_dtype);
     for (int i = tid; i < 256 * D; i += blockDim.x) {
         const int c = i / D, d = i - c * D;
-        vcb[((d >> 2) * 256 + c) * 4 + (d & 3)] = c < P.Kcb ? P.v_cb[((size_t)h * P.Kcb + c) * D + d] : 0.0f;
+        const float val = c < P.Kcb ? P.v_cb[((size_t)h * P.Kcb + c) * D + d] : 0.0f;
+        for (int q = 0; q < vrep; ++q) vcb[(((d >> 2) * 256 + c) * vrep + q) * 4 + (d & 3)] = val;
     }
     __syncthreads();
-    // query table: thread c owns centroid c
+    // query table: two threads per centroid, groups interleaved between them
     {
+        const int cen = tid & 255;
         float c[D];
 #pragma unroll
-        for (int d = 0; d < D; ++d) c[d] = tid < P.Kcb ? P.k_cb[((size_t)h * P.Kcb + tid) * D + d] : 0.0f;
-        for (int g = 0; g < G; ++g) {
+        for (int d = 0; d < D; ++d) c[d] = cen < P.Kcb ? P.k_cb[((size_t)h * P.Kcb + cen) * D + d] : 0.0f;
+        for (int g = tid >> 8; g < G; g += kKvDecThreads / 256) {
             float e[R];
 #pragma unroll
             for (int r = 0; r < R; ++r) {
@@ -179,7 +188,7 @@ __global__ void __launch_bounds__(kKvThreads, (R * 4 <= 16 ? 2 : 1)) kvq_decode_
                 for (int d = 0; d < D; ++d) dot = fmaf(qs[r * hd + g * D + d], c[d], dot);
                 e[r] = dot;
             }
-            st_heads<R>(lut + ((size_t)g * 256 + tid) * R, e);
+            st_heads<R>(lut + ((size_t)g * 256 + cen) * R, e);
         }
     }
     __syncthreads();
@@ -209,7 +218,7 @@ __global__ void __launch_bounds__(kKvThreads, (R * 4 <= 16 ? 2 : 1)) kvq_decode_
         for (int r = 0; r < R; ++r) mloc[r] = -INFINITY;
 #pragma unroll
         for (int j = 0; j < kTpt; ++j) {
-            const int t = tid + j * kKvThreads;
+            const int t = tid + j * kKvDecThreads;
             float acc[R];
 #pragma unroll
             for (int r = 0; r < R; ++r) acc[r] = 0.0f;
@@ -267,7 +276,7 @@ __global__ void __launch_bounds__(kKvThreads, (R * 4 <= 16 ? 2 : 1)) kvq_decode_
         }
 #pragma unroll
         for (int j = 0; j < kTpt; ++j) {
-            const int t = tid + j * kKvThreads;
+            const int t = tid + j * kKvDecThreads;
             if (t < n) {
                 float p[R];
 #pragma unroll
@@ -283,12 +292,13 @@ __global__ void __launch_bounds__(kKvThreads, (R * 4 <= 16 ? 2 : 1)) kvq_decode_
         // (3) values
         if (vg < G) {
             const uint8_t* codes = vt + (size_t)vg * vrow;
+            const float* vmine = vcb + (lane & (vrep - 1)) * 4;   // this lane's copy
             for (int t = vst; t < n; t += stripes) {
                 const int c = codes[t];
                 float v[D], p[R];
 #pragma unroll
                 for (int q = 0; q < kPieces; ++q) {
-                    const float4 f = *reinterpret_cast<const float4*>(vcb + ((size_t)q * 256 + c) * 4);
+                    const float4 f = *reinterpret_cast<const float4*>(vmine + ((size_t)q * 256 + c) * vrep * 4);
                     v[q * 4 + 0] = f.x; v[q * 4 + 1] = f.y; v[q * 4 + 2] = f.z; v[q * 4 + 3] = f.w;
                 }
                 ld_heads<R>(scb + (size_t)t * R, p);
@@ -364,16 +374,22 @@ __global__ void kvq_combine_kernel(const __grid_constant__ KvqProblem P, int R) 
     }
 }
 
-size_t kvq_decode_smem(const KvqProblem& P, int R) {
-    return sizeof(float) * ((size_t)P.G * 256 * R + 256 * (size_t)P.D + (size_t)R * P.head_dim + 2 * (size_t)kKvSub * R +
-                            2 * (kKvThreads / 32) * (size_t)R) + 2 * (size_t)P.G * (kKvSub + kKvVctPad);
+static size_t kvq_decode_smem_copies(const KvqProblem& P, int R, int copies) {
+    const int threads = kvq_decode_threads(R, P.D), sub = 2 * threads;
+    return sizeof(float) * ((size_t)P.G * 256 * R + 256 * (size_t)P.D * copies + (size_t)R * P.head_dim +
+                            2 * (size_t)sub * R + 2 * (threads / 32) * (size_t)R) +
+           2 * (size_t)P.G * (sub + kKvVctPad);
 }
 
+// Copies of the value codebook the decode kernel keeps in shared memory: 8 when that fits, else 1.
+int kvq_decode_v_copies(const KvqProblem& P, int R) { return kvq_decode_smem_copies(P, R, 8) <= 227 * 1024 ? 8 : 1; }
+
+size_t kvq_decode_smem(const KvqProblem& P, int R) { return kvq_decode_smem_copies(P, R, kvq_decode_v_copies(P, R)); }
+
 // Splits of the context: a CTA's range is a multiple of 256 tokens; among the split counts the one with
-// the least (waves of CTAs) x (range + the query-table build, worth about 160 tokens) wins.
+// the least (waves of CTAs, one per SM) x (range + the table set-up, worth about 200 tokens) wins.
 void plan_kvq_decode(KvqProblem& P, int T, int sms) {
-    const int R = P.Hq / P.Hkv, heads = P.B * P.Hkv;
-    const int slots = sms * (2 * (kvq_decode_smem(P, R) + 1024) <= 228 * 1024 ? 2 : 1);
+    const int heads = P.B * P.Hkv, slots = sms;
     const int max_s = std::min(kKvMaxSplits, (T + 255) / 256);
     long best = -1;
     P.chunk = round_up(std::max(T, 1), 256);
@@ -382,7 +398,7 @@ void plan_kvq_decode(KvqProblem& P, int T, int sms) {
         const int span = round_up((T + s - 1) / s, 256);
         const int n = (T + span - 1) / span;
         const long waves = ((long)heads * n + slots - 1) / slots;
-        const long cost = waves * (span + 160);
+        const long cost = waves * (span + 200);
         if (best < 0 || cost < best) {
             best = cost;
             P.chunk = span;
@@ -417,12 +433,14 @@ template <int R, int D>
 static int launch_decode_t(const KvqProblem& P, cudaStream_t s) {
     const size_t smem = kvq_decode_smem(P, R);
     if (smem > 227 * 1024) return OJX_ERR_TOO_LARGE;
+    KvqProblem Q = P;
+    Q.v_copies = kvq_decode_v_copies(P, R);
     static thread_local size_t configured = 0;  // largest opt-in made for this instantiation
     if (smem > configured) {
         OJX_CUDA_TRY(cudaFuncSetAttribute(kvq_decode_kernel<R, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = smem;
     }
-    kvq_decode_kernel<R, D><<<dim3(P.n_chunks, P.Hkv, P.B), kKvThreads, smem, s>>>(P);
+    kvq_decode_kernel<R, D><<<dim3(P.n_chunks, P.Hkv, P.B), kvq_decode_threads(R, D), smem, s>>>(Q);
     OJX_CUDA_TRY(cudaGetLastError());
     kvq_combine_kernel<<<dim3(P.Hq, P.B), 128, 0, s>>>(P, R);
     OJX_CUDA_TRY(cudaGetLastError());
