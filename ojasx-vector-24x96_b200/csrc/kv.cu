@@ -90,24 +90,48 @@ __global__ void kvq_bump_kernel(int* seq_lens, int B, int max_seq, int* error_fl
 
 // ------------------------------------------------------------------------------ kvq decode
 // grid = (splits, Hkv, B); a CTA owns tokens [split*chunk, (split+1)*chunk) of one (sequence, KV head)
-// and walks them in passes of kKvSub tokens with a running maximum (online softmax), so the query
-// table is built once per CTA however long its range is.
+// and walks them in passes of kSub tokens with a running maximum (online softmax), so the query table
+// [G,256,R] is built once per CTA however long its range is.
 //
-// One pass: (1) thread per token: its K codes (one 16-byte load when G is a multiple of 16) index the
-// query table [G,256,R], R heads per 128-bit gather; its V codes are stored transposed, [g][token], for
-// the value phase; warp maxima go to shared memory.  (2) after a barrier every thread knows the new
-// running maximum, turns its own scores into probabilities, and rescales its accumulators.  (3) after
-// a second barrier thread = (group, token stripe) gathers whole centroids of the value codebook and keeps
-// the R x D partial outputs of its group in registers.  Score, probability and code buffers are
-// double-buffered, so a pass costs two barriers.
+// The CTA's warps are split in two groups that work on consecutive passes at the same time:
+//  * score warps: thread per token; its K codes (one 16-byte load when G is a multiple of 16) index the
+//    query table, R heads per 128-bit gather; its V codes are stored as words of four groups,
+//    [g / 4][token] (byte stores of different lanes into one word would be serialised); after a
+//    barrier among the score warps every one of them knows the pass maximum, turns its scores into
+//    probabilities exp(s - running max), and publishes the running maximum of the pass;
+//  * value warps: thread = (group, token stripe); it gathers whole centroids of the value codebook and
+//    keeps the R x D partial outputs of its group in registers, rescaled when the running maximum moves.
+// Probabilities, transposed codes and the published maxima are double-buffered; the groups hand the
+// buffers over with named barriers (full: score warps arrive, value warps wait; empty: the reverse).
 //
 // The kernel is bound by shared-memory wavefronts: a 128-bit gather is served eight lanes at a time, and
 // eight random addresses over eight 16-byte bank groups collide (10.8 wavefronts per warp instead of 4,
 // measured).  The value codebook is small, so when it fits it is stored eight times, copy q confined to
-// bank group q, and lane l reads copy l % 8: those gathers are conflict-free.
+// bank group q, and lane l reads copy l % 8: those gathers are conflict-free.  While the score warps wait
+// for their codes from global memory the value warps keep the shared-memory pipe busy.
+//
 // Threads per CTA: 512, or 256 where the R x D accumulators of a thread need more than 128 registers.
 constexpr int kvq_decode_threads(int R, int D) { return R * D > 64 ? 256 : 512; }
-constexpr int kKvVctPad = 16;               // bytes of padding per transposed code row (bank spread)
+constexpr int kKvVctPad = 4;                // words of padding per transposed code row (bank spread)
+// named barriers (0 is __syncthreads)
+constexpr int kBarScore = 1, kBarFull = 2 /* +buf */, kBarEmpty = 4 /* +buf */;
+
+// Per-phase cycle counters of CTA (0,0,0) for tuning; compiled out unless OJX_PHASE_TIMING is defined.
+#ifdef OJX_PHASE_TIMING
+__device__ unsigned long long g_kv_phase[16];
+#define KV_TICK(i, who) do { if (threadIdx.x == (who) && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) { long long n_ = clock64(); atomicAdd(&g_kv_phase[i], (unsigned long long)(n_ - t_)); t_ = n_; } } while (0)
+#define KV_TICK_INIT long long t_ = clock64()
+#else
+#define KV_TICK(i, who) do { } while (0)
+#define KV_TICK_INIT do { } while (0)
+#endif
+
+__device__ __forceinline__ void named_bar_sync(int id, int count) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+__device__ __forceinline__ void named_bar_arrive(int id, int count) {
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
 
 // R consecutive floats at a 4*R-byte aligned shared-memory address, as 128-bit (R % 4 == 0) or 64-bit (R == 2) accesses
 template <int R>
@@ -142,17 +166,20 @@ __device__ __forceinline__ void st_heads(float* p, const float (&o)[R]) {
 template <int R, int D>
 __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel(const __grid_constant__ KvqProblem P) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    constexpr int kKvDecThreads = kvq_decode_threads(R, D), kKvSub = 2 * kKvDecThreads;   // tokens per pass
-    constexpr int kWarps = kKvDecThreads / 32, kPieces = D / 4, kTpt = kKvSub / kKvDecThreads;
+    constexpr int kThreads = kvq_decode_threads(R, D), kHalf = kThreads / 2;   // score threads = value threads
+    constexpr int kTpt = 2, kSub = kTpt * kHalf;                               // tokens per pass
+    constexpr int kWarpsHalf = kHalf / 32, kPieces = D / 4;
+    constexpr int kVu = R * D <= 32 ? 4 : 2;                                    // tokens per step of a value thread
     const int G = P.G, hd = P.head_dim, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     float* lut = reinterpret_cast<float*>(smem_raw);               // [G][256][R]
     const int vrep = P.v_copies;                                   // 1 or 8 copies of the value codebook
     float* vcb = lut + (size_t)G * 256 * R;                        // [D/4][256][vrep] float4
     float* qs = vcb + 256 * D * vrep;                              // [R*hd]
-    float* sc = qs + R * hd;                                       // [2][kKvSub*R]
-    float* wred = sc + 2 * (size_t)kKvSub * R;                     // [2][warps][R]
-    uint8_t* vct = reinterpret_cast<uint8_t*>(wred + 2 * kWarps * R);  // [2][G][kKvSub + pad]
-    const int vrow = kKvSub + kKvVctPad;
+    float* sc = qs + R * hd;                                       // [2][kSub*R] probabilities
+    float* wred = sc + 2 * (size_t)kSub * R;                       // [2][score warps][R] warp maxima / normalisers
+    float* mpub = wred + 2 * kWarpsHalf * R;                       // [2][R] running maximum after each pass
+    uint32_t* vct = reinterpret_cast<uint32_t*>(mpub + 2 * R);     // [2][ceil(G/4)][kSub + pad] words of four codes
+    const int vrow = kSub + kKvVctPad, Gq = (G + 3) >> 2;
 
     const int b = blockIdx.z, h = blockIdx.y, split = blockIdx.x;
     const int T = P.seq_lens[b];
@@ -160,32 +187,45 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
     const int t_end = min(T, t_begin + P.chunk);
     float* part = P.partials + ((((size_t)b * P.Hkv + h) * P.n_chunks + split) * R) * (hd + 2);
     if (t_begin >= t_end) {  // range beyond this sequence: neutral partial
-        for (int i = tid; i < R * (hd + 2); i += blockDim.x) part[i] = (i % (hd + 2)) == 0 ? -INFINITY : 0.0f;
+        for (int i = tid; i < R * (hd + 2); i += kThreads) part[i] = (i % (hd + 2)) == 0 ? -INFINITY : 0.0f;
         return;
     }
+    const int n_passes = (t_end - t_begin + kSub - 1) / kSub;
     const uint8_t* kc = P.k_codes + (((size_t)b * P.Hkv + h) * P.max_seq) * G;
     const uint8_t* vc = P.v_codes + (((size_t)b * P.Hkv + h) * P.max_seq) * G;
 
-    for (int i = tid; i < R * hd; i += blockDim.x) qs[i] = load_io(P.q, ((size_t)b * P.Hq + (size_t)h * R) * hd + i, P.io_dtype);
-    for (int i = tid; i < 256 * D; i += blockDim.x) {
-        const int c = i / D, d = i - c * D;
-        const float val = c < P.Kcb ? P.v_cb[((size_t)h * P.Kcb + c) * D + d] : 0.0f;
-        for (int q = 0; q < vrep; ++q) vcb[(((d >> 2) * 256 + c) * vrep + q) * 4 + (d & 3)] = val;
+    KV_TICK_INIT;
+    for (int i = tid; i < R * hd; i += kThreads) qs[i] = load_io(P.q, ((size_t)b * P.Hq + (size_t)h * R) * hd + i, P.io_dtype);
+    for (int i0 = tid; i0 < 256 * kPieces * vrep; i0 += 4 * kThreads) {   // consecutive threads, consecutive 16-byte slots
+        float4 val[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {   // loads first, then stores
+            const int i = i0 + u * kThreads, slot = i / vrep, piece = slot >> 8, c = slot & 255;
+            val[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (i < 256 * kPieces * vrep && c < P.Kcb)
+                val[u] = *reinterpret_cast<const float4*>(P.v_cb + ((size_t)h * P.Kcb + c) * D + piece * 4);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (i0 + u * kThreads < 256 * kPieces * vrep) reinterpret_cast<float4*>(vcb)[i0 + u * kThreads] = val[u];
     }
     __syncthreads();
-    // query table: two threads per centroid, groups interleaved between them
+    KV_TICK(12, 0);
+    // query table: kThreads / 256 threads per centroid, groups interleaved between them
     {
         const int cen = tid & 255;
         float c[D];
 #pragma unroll
         for (int d = 0; d < D; ++d) c[d] = cen < P.Kcb ? P.k_cb[((size_t)h * P.Kcb + cen) * D + d] : 0.0f;
-        for (int g = tid >> 8; g < G; g += kKvDecThreads / 256) {
+        for (int g = tid >> 8; g < G; g += kThreads / 256) {
             float e[R];
 #pragma unroll
             for (int r = 0; r < R; ++r) {
+                float qv[D];   // D consecutive query values, 128-bit broadcast reads (D % 4 == 0, hd % 4 == 0)
+                ld_heads<D>(qs + r * hd + g * D, qv);
                 float dot = 0.0f;
 #pragma unroll
-                for (int d = 0; d < D; ++d) dot = fmaf(qs[r * hd + g * D + d], c[d], dot);
+                for (int d = 0; d < D; ++d) dot = fmaf(qv[d], c[d], dot);
                 e[r] = dot;
             }
             st_heads<R>(lut + ((size_t)g * 256 + cen) * R, e);
@@ -193,10 +233,11 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
     }
     __syncthreads();
 
-    // value phase mapping: threads per group capped so that the stripe partials fit in the query-table area
-    const int stripes = min((int)blockDim.x / G, 256 / D);
-    const int vg = tid / stripes, vst = tid - vg * stripes;
-    float o[R][D], m_run[R], l_loc[R];
+    KV_TICK(13, 0);
+    // value mapping: threads per group capped so that the stripe partials ([stripes][R][hd + 4]) fit in the
+    // query-table area (G*256*R floats)
+    const int stripes = min(kHalf / G, (256 * G) / (hd + 4));
+    float m_run[R], l_loc[R], o[R][D];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         m_run[r] = -INFINITY;
@@ -204,144 +245,246 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
 #pragma unroll
         for (int d = 0; d < D; ++d) o[r][d] = 0.0f;
     }
+    const bool score_warp = warp < kWarpsHalf;
+    const int vt_id = tid - kHalf;                 // value thread index (value warps only)
+    const int vg = vt_id / stripes, vst = vt_id - vg * stripes;
 
-    int buf = 0;
-    for (int base = t_begin; base < t_end; base += kKvSub, buf ^= 1) {
-        const int n = min(kKvSub, t_end - base);
-        float* scb = sc + (size_t)buf * kKvSub * R;
-        float* wr = wred + buf * kWarps * R;
-        uint8_t* vt = vct + (size_t)buf * G * vrow;
+    if (score_warp) {
+        // G == 16 (one 16-byte row per token): the rows of the next pass are fetched a pass ahead, so the
+        // latency of global memory is off the score warps' critical path
+        const bool ahead = G == 16;
+        uint4 k_next[kTpt], v_next[kTpt];
+        auto fetch = [&](int pass_base) {
+#pragma unroll
+            for (int j = 0; j < kTpt; ++j) {
+                const int t = pass_base + tid + j * kHalf;
+                const size_t row = (size_t)(t < t_end ? t : pass_base) * 16;
+                k_next[j] = *reinterpret_cast<const uint4*>(kc + row);
+                v_next[j] = *reinterpret_cast<const uint4*>(vc + row);
+            }
+        };
+        if (ahead) fetch(t_begin);
+        for (int it = 0; it < n_passes; ++it) {
+            const int buf = it & 1, base = t_begin + it * kSub;
+            const int n = min(kSub, t_end - base);
+            float* scb = sc + (size_t)buf * kSub * R;
+            float* wr = wred + buf * kWarpsHalf * R;
+            uint32_t* vt = vct + (size_t)buf * Gq * vrow;
+            if (it >= 2) named_bar_sync(kBarEmpty + buf, kThreads);   // the value warps are done with this buffer
+            KV_TICK(0, 0);
 
-        // (1) scores of this thread's tokens
-        float s[kTpt][R], mloc[R];
+            // both tokens of a thread go through the groups together, so that their gathers overlap; a token
+            // beyond the pass reads row 0 of the pass and is discarded
+            float s[kTpt][R], mloc[R];
+            const uint8_t* krow[kTpt];
+            const uint8_t* vrow_g[kTpt];
 #pragma unroll
-        for (int r = 0; r < R; ++r) mloc[r] = -INFINITY;
+            for (int j = 0; j < kTpt; ++j) {
+                const int t = tid + j * kHalf;
+                const size_t row = (size_t)(base + (t < n ? t : 0)) * G;
+                krow[j] = kc + row;
+                vrow_g[j] = vc + row;
 #pragma unroll
-        for (int j = 0; j < kTpt; ++j) {
-            const int t = tid + j * kKvDecThreads;
-            float acc[R];
+                for (int r = 0; r < R; ++r) s[j][r] = 0.0f;
+            }
+            // four groups: four gathers per token and one word of V codes
+            auto quad = [&](int gq, const unsigned (&kword)[kTpt], const unsigned (&vword)[kTpt]) {
 #pragma unroll
-            for (int r = 0; r < R; ++r) acc[r] = 0.0f;
-            if (t < n) {
-                const uint8_t* krow = kc + (size_t)(base + t) * G;
-                const uint8_t* vrow_g = vc + (size_t)(base + t) * G;
-                auto one = [&](int g, unsigned kcode, unsigned vcode) {
-                    float e[R];
-                    ld_heads<R>(lut + ((size_t)g * 256 + kcode) * R, e);
+                for (int q = 0; q < 4; ++q) {
+                    if (gq * 4 + q < G) {
 #pragma unroll
-                    for (int r = 0; r < R; ++r) acc[r] += e[r];
-                    vt[(size_t)g * vrow + t] = (uint8_t)vcode;
-                };
-                int g = 0;
-                if ((G & 15) == 0) {
-                    for (; g < G; g += 16) {
-                        const uint4 kw = *reinterpret_cast<const uint4*>(krow + g);
-                        const uint4 vw = *reinterpret_cast<const uint4*>(vrow_g + g);
-                        const unsigned ka[4] = {kw.x, kw.y, kw.z, kw.w}, va[4] = {vw.x, vw.y, vw.z, vw.w};
+                        for (int j = 0; j < kTpt; ++j) {
+                            float e[R];
+                            ld_heads<R>(lut + ((size_t)(gq * 4 + q) * 256 + ((kword[j] >> (8 * q)) & 255u)) * R, e);
 #pragma unroll
-                        for (int w = 0; w < 4; ++w)
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) one(g + w * 4 + q, (ka[w] >> (8 * q)) & 255u, (va[w] >> (8 * q)) & 255u);
+                            for (int r = 0; r < R; ++r) s[j][r] += e[r];
+                        }
                     }
-                } else {
-                    for (; g < G; ++g) one(g, krow[g], vrow_g[g]);
+                }
+#pragma unroll
+                for (int j = 0; j < kTpt; ++j) vt[(size_t)gq * vrow + tid + j * kHalf] = vword[j];
+            };
+            if (ahead) {
+                uint4 kw[kTpt], vw[kTpt];
+#pragma unroll
+                for (int j = 0; j < kTpt; ++j) {
+                    kw[j] = k_next[j];
+                    vw[j] = v_next[j];
+                }
+                if (it + 1 < n_passes) fetch(base + kSub);
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    unsigned ka[kTpt], va[kTpt];
+#pragma unroll
+                    for (int j = 0; j < kTpt; ++j) {
+                        ka[j] = w == 0 ? kw[j].x : w == 1 ? kw[j].y : w == 2 ? kw[j].z : kw[j].w;
+                        va[j] = w == 0 ? vw[j].x : w == 1 ? vw[j].y : w == 2 ? vw[j].z : vw[j].w;
+                    }
+                    quad(w, ka, va);
+                }
+            } else if ((G & 15) == 0) {
+                for (int g = 0; g < G; g += 16) {
+                    uint4 kw[kTpt], vw[kTpt];
+#pragma unroll
+                    for (int j = 0; j < kTpt; ++j) {
+                        kw[j] = *reinterpret_cast<const uint4*>(krow[j] + g);
+                        vw[j] = *reinterpret_cast<const uint4*>(vrow_g[j] + g);
+                    }
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        unsigned ka[kTpt], va[kTpt];
+#pragma unroll
+                        for (int j = 0; j < kTpt; ++j) {
+                            ka[j] = w == 0 ? kw[j].x : w == 1 ? kw[j].y : w == 2 ? kw[j].z : kw[j].w;
+                            va[j] = w == 0 ? vw[j].x : w == 1 ? vw[j].y : w == 2 ? vw[j].z : vw[j].w;
+                        }
+                        quad((g >> 2) + w, ka, va);
+                    }
+                }
+            } else {
+                for (int gq = 0; gq < Gq; ++gq) {
+                    unsigned ka[kTpt], va[kTpt];
+#pragma unroll
+                    for (int j = 0; j < kTpt; ++j) {
+                        ka[j] = va[j] = 0u;
+                        for (int q = 0; q < 4 && gq * 4 + q < G; ++q) {
+                            ka[j] |= (unsigned)krow[j][gq * 4 + q] << (8 * q);
+                            va[j] |= (unsigned)vrow_g[j][gq * 4 + q] << (8 * q);
+                        }
+                    }
+                    quad(gq, ka, va);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) mloc[r] = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < kTpt; ++j) {
+                const bool live = tid + j * kHalf < n;
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    s[j][r] = live ? s[j][r] * P.scale : -INFINITY;
+                    mloc[r] = fmaxf(mloc[r], s[j][r]);
                 }
             }
 #pragma unroll
             for (int r = 0; r < R; ++r) {
-                s[j][r] = t < n ? acc[r] * P.scale : -INFINITY;
-                mloc[r] = fmaxf(mloc[r], s[j][r]);
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) mloc[r] = fmaxf(mloc[r], __shfl_xor_sync(0xffffffffu, mloc[r], off));
+                if (lane == 0) wr[warp * R + r] = mloc[r];
             }
-        }
+            KV_TICK(1, 0);
+            named_bar_sync(kBarScore, kHalf);
+            KV_TICK(2, 0);
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
+            for (int r = 0; r < R; ++r) {
+                float m = m_run[r];
 #pragma unroll
-            for (int off = 16; off >= 1; off >>= 1) mloc[r] = fmaxf(mloc[r], __shfl_xor_sync(0xffffffffu, mloc[r], off));
-            if (lane == 0) wr[warp * R + r] = mloc[r];
-        }
-        __syncthreads();
-
-        // (2) new running maximum, probabilities, rescale
-        float alpha[R];
+                for (int w = 0; w < kWarpsHalf; ++w) m = fmaxf(m, wr[w * R + r]);
+                l_loc[r] *= __expf(m_run[r] - m);   // factor 0 on the first pass (m_run = -inf, m finite)
+                m_run[r] = m;
+            }
+            if (tid == 0) {
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-            float m = m_run[r];
+                for (int r = 0; r < R; ++r) mpub[buf * R + r] = m_run[r];
+            }
 #pragma unroll
-            for (int w = 0; w < kWarps; ++w) m = fmaxf(m, wr[w * R + r]);
-            alpha[r] = __expf(m_run[r] - m);   // 0 on the first pass (m_run = -inf, m finite)
-            m_run[r] = m;
-            l_loc[r] *= alpha[r];
+            for (int j = 0; j < kTpt; ++j) {
+                const int t = tid + j * kHalf;
+                if (t < n) {
+                    float p[R];
 #pragma unroll
-            for (int d = 0; d < D; ++d) o[r][d] *= alpha[r];
-        }
-#pragma unroll
-        for (int j = 0; j < kTpt; ++j) {
-            const int t = tid + j * kKvDecThreads;
-            if (t < n) {
-                float p[R];
-#pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    p[r] = __expf(s[j][r] - m_run[r]);
-                    l_loc[r] += p[r];
+                    for (int r = 0; r < R; ++r) {
+                        p[r] = __expf(s[j][r] - m_run[r]);
+                        l_loc[r] += p[r];
+                    }
+                    st_heads<R>(scb + (size_t)t * R, p);
                 }
-                st_heads<R>(scb + (size_t)t * R, p);
             }
+            named_bar_arrive(kBarFull + buf, kThreads);
+            KV_TICK(3, 0);
         }
-        __syncthreads();
-
-        // (3) values
-        if (vg < G) {
-            const uint8_t* codes = vt + (size_t)vg * vrow;
-            const float* vmine = vcb + (lane & (vrep - 1)) * 4;   // this lane's copy
-            for (int t = vst; t < n; t += stripes) {
-                const int c = codes[t];
-                float v[D], p[R];
+    } else {
+        const float* vmine = vcb + (lane & (vrep - 1)) * 4;   // this lane's copy of the value codebook
+        for (int it = 0; it < n_passes; ++it) {
+            const int buf = it & 1, base = t_begin + it * kSub;
+            const int n = min(kSub, t_end - base);
+            const float* scb = sc + (size_t)buf * kSub * R;
+            const uint8_t* codes = reinterpret_cast<const uint8_t*>(vct + (size_t)buf * Gq * vrow + (size_t)(vg >> 2) * vrow) + (vg & 3);
+            named_bar_sync(kBarFull + buf, kThreads);
+            KV_TICK(8, kHalf);
 #pragma unroll
-                for (int q = 0; q < kPieces; ++q) {
-                    const float4 f = *reinterpret_cast<const float4*>(vmine + ((size_t)q * 256 + c) * vrep * 4);
-                    v[q * 4 + 0] = f.x; v[q * 4 + 1] = f.y; v[q * 4 + 2] = f.z; v[q * 4 + 3] = f.w;
+            for (int r = 0; r < R; ++r) {
+                const float m = mpub[buf * R + r];
+                const float alpha = __expf(m_run[r] - m);
+                m_run[r] = m;
+#pragma unroll
+                for (int d = 0; d < D; ++d) o[r][d] *= alpha;
+            }
+            if (vg < G) {
+                // kVu tokens per step, loads first: a token beyond the pass re-reads this thread's first
+                // token with probability 0
+                for (int t = vst; t < n; t += kVu * stripes) {
+                    float v[kVu][D], p[kVu][R];
+#pragma unroll
+                    for (int u = 0; u < kVu; ++u) {
+                        const int tu = t + u * stripes;
+                        const bool live = tu < n;
+                        const int tt = live ? tu : t;
+                        const int c = codes[(size_t)tt * 4];
+#pragma unroll
+                        for (int q = 0; q < kPieces; ++q) {
+                            const float4 f = *reinterpret_cast<const float4*>(vmine + ((size_t)q * 256 + c) * vrep * 4);
+                            v[u][q * 4 + 0] = f.x; v[u][q * 4 + 1] = f.y; v[u][q * 4 + 2] = f.z; v[u][q * 4 + 3] = f.w;
+                        }
+                        ld_heads<R>(scb + (size_t)tt * R, p[u]);
+                        if (!live) {
+#pragma unroll
+                            for (int r = 0; r < R; ++r) p[u][r] = 0.0f;
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < kVu; ++u)
+#pragma unroll
+                        for (int r = 0; r < R; ++r)
+#pragma unroll
+                            for (int d = 0; d < D; ++d) o[r][d] = fmaf(p[u][r], v[u][d], o[r][d]);
                 }
-                ld_heads<R>(scb + (size_t)t * R, p);
-#pragma unroll
-                for (int r = 0; r < R; ++r)
-#pragma unroll
-                    for (int d = 0; d < D; ++d) o[r][d] = fmaf(p[r], v[d], o[r][d]);
             }
+            if (it + 2 < n_passes) named_bar_arrive(kBarEmpty + buf, kThreads);   // only if a score pass will wait for it
+            KV_TICK(9, kHalf);
         }
-        // no barrier here: the next pass writes the other buffers, and the pass after that cannot reach
-        // its writes before every thread has passed the next pass's first barrier
     }
 
-    // normaliser: fixed-shape reduction (shuffle tree, then the warps in order)
+    // both groups are past their last pass: the query table is dead, its area takes the stripe partials
     __syncthreads();
+    KV_TICK(14, 0);
     float* lred = wred;
+    float* stripe_out = lut;                              // [stripes][R][hd + 4]: padded so that stripes spread over the banks
+    const int srow = hd + 4;
+    if (score_warp) {   // normaliser: fixed-shape reduction (shuffle tree, then the warps in order)
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-        float l = l_loc[r];
+        for (int r = 0; r < R; ++r) {
+            float l = l_loc[r];
 #pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
-        if (lane == 0) lred[warp * R + r] = l;
-    }
-    // stripes of one group are added in a fixed order; the query table is dead, its area holds them
-    float* stripe_out = lut;                              // [stripes][R][hd]
-    if (vg < G) {
+            for (int off = 16; off >= 1; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+            if (lane == 0) lred[warp * R + r] = l;
+        }
+    } else if (vg < G) {
 #pragma unroll
-        for (int r = 0; r < R; ++r)
-#pragma unroll
-            for (int d = 0; d < D; ++d) stripe_out[((size_t)vst * R + r) * hd + vg * D + d] = o[r][d];
+        for (int r = 0; r < R; ++r) st_heads<D>(stripe_out + ((size_t)vst * R + r) * srow + vg * D, o[r]);
     }
     __syncthreads();
-    for (int i = tid; i < R * hd; i += blockDim.x) {
-        float acc = 0.0f;
-        for (int s2 = 0; s2 < stripes; ++s2) acc += stripe_out[(size_t)s2 * R * hd + i];
+    for (int i = tid; i < R * hd; i += kThreads) {   // stripes of one group are added in a fixed order
         const int r = i / hd, c = i - r * hd;
+        float acc = 0.0f;
+        for (int s2 = 0; s2 < stripes; ++s2) acc += stripe_out[((size_t)s2 * R + r) * srow + c];
         part[(size_t)r * (hd + 2) + 2 + c] = acc;
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        if (tid == r) {
+        if (tid == r) {   // a score thread: its m_run is the final running maximum
             float l = 0.0f;
-            for (int w = 0; w < kWarps; ++w) l += lred[w * R + r];
+            for (int w = 0; w < kWarpsHalf; ++w) l += lred[w * R + r];
             part[(size_t)r * (hd + 2) + 0] = m_run[r];
             part[(size_t)r * (hd + 2) + 1] = l;
         }
@@ -375,10 +518,10 @@ __global__ void kvq_combine_kernel(const __grid_constant__ KvqProblem P, int R) 
 }
 
 static size_t kvq_decode_smem_copies(const KvqProblem& P, int R, int copies) {
-    const int threads = kvq_decode_threads(R, P.D), sub = 2 * threads;
+    const int threads = kvq_decode_threads(R, P.D), sub = threads;   // two tokens per score thread, half the threads score
     return sizeof(float) * ((size_t)P.G * 256 * R + 256 * (size_t)P.D * copies + (size_t)R * P.head_dim +
-                            2 * (size_t)sub * R + 2 * (threads / 32) * (size_t)R) +
-           2 * (size_t)P.G * (sub + kKvVctPad);
+                            2 * (size_t)sub * R + 2 * (threads / 64) * (size_t)R + 2 * (size_t)R) +
+           2 * sizeof(uint32_t) * (size_t)((P.G + 3) / 4) * (sub + kKvVctPad);
 }
 
 // Copies of the value codebook the decode kernel keeps in shared memory: 8 when that fits, else 1.
@@ -386,19 +529,20 @@ int kvq_decode_v_copies(const KvqProblem& P, int R) { return kvq_decode_smem_cop
 
 size_t kvq_decode_smem(const KvqProblem& P, int R) { return kvq_decode_smem_copies(P, R, kvq_decode_v_copies(P, R)); }
 
-// Splits of the context: a CTA's range is a multiple of 256 tokens; among the split counts the one with
-// the least (waves of CTAs, one per SM) x (range + the table set-up, worth about 200 tokens) wins.
+// Splits of the context: a CTA's range is a multiple of 64 tokens; among the split counts the one with
+// the least (waves of CTAs, one per SM) x (range + the table set-up and the fill and drain of the
+// score/value pipeline, together worth about 1000 tokens) wins.
 void plan_kvq_decode(KvqProblem& P, int T, int sms) {
     const int heads = P.B * P.Hkv, slots = sms;
     const int max_s = std::min(kKvMaxSplits, (T + 255) / 256);
     long best = -1;
-    P.chunk = round_up(std::max(T, 1), 256);
+    P.chunk = round_up(std::max(T, 1), 64);
     P.n_chunks = 1;
     for (int s = 1; s <= max_s; ++s) {
-        const int span = round_up((T + s - 1) / s, 256);
+        const int span = round_up((T + s - 1) / s, 64);
         const int n = (T + span - 1) / span;
         const long waves = ((long)heads * n + slots - 1) / slots;
-        const long cost = waves * (span + 200);
+        const long cost = waves * (span + 1000);
         if (best < 0 || cost < best) {
             best = cost;
             P.chunk = span;
@@ -583,3 +727,11 @@ int launch_legacy_attention(const float* q, int head_dim, int block_dim, int T, 
 }
 
 }  // namespace ojx
+
+#ifdef OJX_PHASE_TIMING
+extern "C" __attribute__((visibility("default"))) int ojx_read_kv_phases(unsigned long long* out, int reset) {
+    cudaMemcpyFromSymbol(out, ojx::g_kv_phase, sizeof(unsigned long long) * 16);
+    if (reset) { unsigned long long z[16] = {}; cudaMemcpyToSymbol(ojx::g_kv_phase, z, sizeof(z)); }
+    return 0;
+}
+#endif
