@@ -99,8 +99,10 @@ __global__ void kvq_bump_kernel(int* seq_lens, int B, int max_seq, int* error_fl
 //    [g / 4][token] (byte stores of different lanes into one word would be serialised); after a
 //    barrier among the score warps every one of them knows the pass maximum, turns its scores into
 //    probabilities exp(s - running max), and publishes the running maximum of the pass;
-//  * value warps: thread = (group, token stripe); it gathers whole centroids of the value codebook and
-//    keeps the R x D partial outputs of its group in registers, rescaled when the running maximum moves.
+//  * value warps: thread = (group or pair of groups, token stripe); it gathers whole centroids of the
+//    value codebook and keeps the R x D partial outputs of its groups in registers, rescaled when the
+//    running maximum moves.  Two groups per thread (when the registers allow) halve the reads of the
+//    probabilities and of the codes.
 // Probabilities, transposed codes and the published maxima are double-buffered; the groups hand the
 // buffers over with named barriers (full: score warps arrive, value warps wait; empty: the reverse).
 //
@@ -114,7 +116,7 @@ __global__ void kvq_bump_kernel(int* seq_lens, int B, int max_seq, int* error_fl
 constexpr int kvq_decode_threads(int R, int D) { return R * D > 64 ? 256 : 512; }
 constexpr int kKvVctPad = 4;                // words of padding per transposed code row (bank spread)
 // named barriers (0 is __syncthreads)
-constexpr int kBarScore = 1, kBarFull = 2 /* +buf */, kBarEmpty = 4 /* +buf */;
+constexpr int kBarScore = 1, kBarFull = 2 /* +buf */, kBarEmpty = 4 /* +buf */, kBarValue = 6;
 
 // Per-phase cycle counters of CTA (0,0,0) for tuning; compiled out unless OJX_PHASE_TIMING is defined.
 #ifdef OJX_PHASE_TIMING
@@ -169,7 +171,8 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
     constexpr int kThreads = kvq_decode_threads(R, D), kHalf = kThreads / 2;   // score threads = value threads
     constexpr int kTpt = 2, kSub = kTpt * kHalf;                               // tokens per pass
     constexpr int kWarpsHalf = kHalf / 32, kPieces = D / 4;
-    constexpr int kVu = R * D <= 32 ? 4 : 2;                                    // tokens per step of a value thread
+    constexpr int kGp = R * D <= 32 ? 2 : 1;                                    // groups per value thread
+    constexpr int kVu = 2;                                                      // tokens per step of a value thread
     const int G = P.G, hd = P.head_dim, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     float* lut = reinterpret_cast<float*>(smem_raw);               // [G][256][R]
     const int vrep = P.v_copies;                                   // 1 or 8 copies of the value codebook
@@ -178,7 +181,9 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
     float* sc = qs + R * hd;                                       // [2][kSub*R] probabilities
     float* wred = sc + 2 * (size_t)kSub * R;                       // [2][score warps][R] warp maxima / normalisers
     float* mpub = wred + 2 * kWarpsHalf * R;                       // [2][R] running maximum after each pass
-    uint32_t* vct = reinterpret_cast<uint32_t*>(mpub + 2 * R);     // [2][ceil(G/4)][kSub + pad] words of four codes
+    float* lred = mpub + 2 * R;                                    // [score warps][R] normaliser partials, [R] final maximum
+    float* mfin = lred + kWarpsHalf * R;
+    uint32_t* vct = reinterpret_cast<uint32_t*>(mfin + R);         // [2][ceil(G/4)][kSub + pad] words of four codes
     const int vrow = kSub + kKvVctPad, Gq = (G + 3) >> 2;
 
     const int b = blockIdx.z, h = blockIdx.y, split = blockIdx.x;
@@ -234,22 +239,24 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
     __syncthreads();
 
     KV_TICK(13, 0);
-    // value mapping: threads per group capped so that the stripe partials ([stripes][R][hd + 4]) fit in the
-    // query-table area (G*256*R floats)
-    const int stripes = min(kHalf / G, (256 * G) / (hd + 4));
-    float m_run[R], l_loc[R], o[R][D];
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-        m_run[r] = -INFINITY;
-        l_loc[r] = 0.0f;
-#pragma unroll
-        for (int d = 0; d < D; ++d) o[r][d] = 0.0f;
-    }
+    // value mapping: threads per unit (kGp groups) capped so that the stripe partials ([stripes][R][hd + 4])
+    // fit in the area of the query table and the value codebook, both dead by then
+    const int units = (G + kGp - 1) / kGp;
+    const int stripes = min(kHalf / units, (int)((((size_t)G * R + (size_t)D * vrep) * 256) / ((size_t)R * (hd + 4))));
+    float* stripe_out = lut;                       // [stripes][R][hd + 4]: padded so that stripes spread over the banks
+    const int srow = hd + 4;
     const bool score_warp = warp < kWarpsHalf;
     const int vt_id = tid - kHalf;                 // value thread index (value warps only)
-    const int vg = vt_id / stripes, vst = vt_id - vg * stripes;
+    const int vu = vt_id / stripes, vst = vt_id - vu * stripes;   // unit, stripe
+    const int vg = vu * kGp;                                      // first group of the unit
 
     if (score_warp) {
+        float m_run[R], l_loc[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            m_run[r] = -INFINITY;
+            l_loc[r] = 0.0f;
+        }
         // G == 16 (one 16-byte row per token): the rows of the next pass are fetched a pass ahead, so the
         // latency of global memory is off the score warps' critical path
         const bool ahead = G == 16;
@@ -403,12 +410,31 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
             named_bar_arrive(kBarFull + buf, kThreads);
             KV_TICK(3, 0);
         }
+        // normaliser: fixed-shape reduction (shuffle tree here, then the warps in order after the join)
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            float l = l_loc[r];
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+            if (lane == 0) lred[warp * R + r] = l;
+            if (tid == 0) mfin[r] = m_run[r];
+        }
     } else {
+        float m_run[R], o[kGp][R][D];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            m_run[r] = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < kGp; ++i)
+#pragma unroll
+                for (int d = 0; d < D; ++d) o[i][r][d] = 0.0f;
+        }
         const float* vmine = vcb + (lane & (vrep - 1)) * 4;   // this lane's copy of the value codebook
         for (int it = 0; it < n_passes; ++it) {
             const int buf = it & 1, base = t_begin + it * kSub;
             const int n = min(kSub, t_end - base);
             const float* scb = sc + (size_t)buf * kSub * R;
+            // the unit's codes of one token sit in one word (kGp divides 4)
             const uint8_t* codes = reinterpret_cast<const uint8_t*>(vct + (size_t)buf * Gq * vrow + (size_t)(vg >> 2) * vrow) + (vg & 3);
             named_bar_sync(kBarFull + buf, kThreads);
             KV_TICK(8, kHalf);
@@ -418,23 +444,31 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
                 const float alpha = __expf(m_run[r] - m);
                 m_run[r] = m;
 #pragma unroll
-                for (int d = 0; d < D; ++d) o[r][d] *= alpha;
+                for (int i = 0; i < kGp; ++i)
+#pragma unroll
+                    for (int d = 0; d < D; ++d) o[i][r][d] *= alpha;
             }
             if (vg < G) {
                 // kVu tokens per step, loads first: a token beyond the pass re-reads this thread's first
                 // token with probability 0
                 for (int t = vst; t < n; t += kVu * stripes) {
-                    float v[kVu][D], p[kVu][R];
+                    float v[kVu][kGp][D], p[kVu][R];
 #pragma unroll
                     for (int u = 0; u < kVu; ++u) {
                         const int tu = t + u * stripes;
                         const bool live = tu < n;
                         const int tt = live ? tu : t;
-                        const int c = codes[(size_t)tt * 4];
+                        unsigned cc;   // kGp codes, one per byte (a group beyond G reads the zero padding of the word)
+                        if constexpr (kGp == 2) cc = *reinterpret_cast<const uint16_t*>(codes + (size_t)tt * 4);
+                        else cc = codes[(size_t)tt * 4];
 #pragma unroll
-                        for (int q = 0; q < kPieces; ++q) {
-                            const float4 f = *reinterpret_cast<const float4*>(vmine + ((size_t)q * 256 + c) * vrep * 4);
-                            v[u][q * 4 + 0] = f.x; v[u][q * 4 + 1] = f.y; v[u][q * 4 + 2] = f.z; v[u][q * 4 + 3] = f.w;
+                        for (int i = 0; i < kGp; ++i) {
+                            const int c = (cc >> (8 * i)) & 255u;
+#pragma unroll
+                            for (int q = 0; q < kPieces; ++q) {
+                                const float4 f = *reinterpret_cast<const float4*>(vmine + ((size_t)q * 256 + c) * vrep * 4);
+                                v[u][i][q * 4 + 0] = f.x; v[u][i][q * 4 + 1] = f.y; v[u][i][q * 4 + 2] = f.z; v[u][i][q * 4 + 3] = f.w;
+                            }
                         }
                         ld_heads<R>(scb + (size_t)tt * R, p[u]);
                         if (!live) {
@@ -445,35 +479,32 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
 #pragma unroll
                     for (int u = 0; u < kVu; ++u)
 #pragma unroll
-                        for (int r = 0; r < R; ++r)
+                        for (int i = 0; i < kGp; ++i)
 #pragma unroll
-                            for (int d = 0; d < D; ++d) o[r][d] = fmaf(p[u][r], v[u][d], o[r][d]);
+                            for (int r = 0; r < R; ++r)
+#pragma unroll
+                                for (int d = 0; d < D; ++d) o[i][r][d] = fmaf(p[u][r], v[u][i][d], o[i][r][d]);
                 }
             }
             if (it + 2 < n_passes) named_bar_arrive(kBarEmpty + buf, kThreads);   // only if a score pass will wait for it
             KV_TICK(9, kHalf);
         }
+        // Every value warp is past its last pass, and so are the score warps (that pass was handed over by
+        // all of them): the query table and the value codebook are dead, their area takes the stripe partials.
+        named_bar_sync(kBarValue, kHalf);
+        if (vg < G) {
+#pragma unroll
+            for (int i = 0; i < kGp; ++i) {
+                if (vg + i < G) {
+#pragma unroll
+                    for (int r = 0; r < R; ++r) st_heads<D>(stripe_out + ((size_t)vst * R + r) * srow + (vg + i) * D, o[i][r]);
+                }
+            }
+        }
     }
 
-    // both groups are past their last pass: the query table is dead, its area takes the stripe partials
     __syncthreads();
     KV_TICK(14, 0);
-    float* lred = wred;
-    float* stripe_out = lut;                              // [stripes][R][hd + 4]: padded so that stripes spread over the banks
-    const int srow = hd + 4;
-    if (score_warp) {   // normaliser: fixed-shape reduction (shuffle tree, then the warps in order)
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            float l = l_loc[r];
-#pragma unroll
-            for (int off = 16; off >= 1; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
-            if (lane == 0) lred[warp * R + r] = l;
-        }
-    } else if (vg < G) {
-#pragma unroll
-        for (int r = 0; r < R; ++r) st_heads<D>(stripe_out + ((size_t)vst * R + r) * srow + vg * D, o[r]);
-    }
-    __syncthreads();
     for (int i = tid; i < R * hd; i += kThreads) {   // stripes of one group are added in a fixed order
         const int r = i / hd, c = i - r * hd;
         float acc = 0.0f;
@@ -482,10 +513,10 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        if (tid == r) {   // a score thread: its m_run is the final running maximum
+        if (tid == r) {
             float l = 0.0f;
             for (int w = 0; w < kWarpsHalf; ++w) l += lred[w * R + r];
-            part[(size_t)r * (hd + 2) + 0] = m_run[r];
+            part[(size_t)r * (hd + 2) + 0] = mfin[r];
             part[(size_t)r * (hd + 2) + 1] = l;
         }
     }
@@ -520,7 +551,7 @@ __global__ void kvq_combine_kernel(const __grid_constant__ KvqProblem P, int R) 
 static size_t kvq_decode_smem_copies(const KvqProblem& P, int R, int copies) {
     const int threads = kvq_decode_threads(R, P.D), sub = threads;   // two tokens per score thread, half the threads score
     return sizeof(float) * ((size_t)P.G * 256 * R + 256 * (size_t)P.D * copies + (size_t)R * P.head_dim +
-                            2 * (size_t)sub * R + 2 * (threads / 64) * (size_t)R + 2 * (size_t)R) +
+                            2 * (size_t)sub * R + 3 * (threads / 64) * (size_t)R + 3 * (size_t)R) +
            2 * sizeof(uint32_t) * (size_t)((P.G + 3) / 4) * (sub + kKvVctPad);
 }
 
