@@ -195,9 +195,12 @@ int ojasx_b200_moe_forward_routed(OjasxMoEHandle handle, const void* d_x, void* 
     int* idx = reinterpret_cast<int*>(probs + (size_t)n_tokens * h->E_total);
     float* w = reinterpret_cast<float*>(idx + (size_t)n_tokens * top_k);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    rc = launch_moe_router(h->router, d_x, io_dtype, n_tokens, h->H, h->E_total, top_k, logits, probs, idx, w, s);
+    MoeProblem P = h->problem(d_x, d_y, idx, w, n_tokens, top_k, io_dtype);
+    rc = launch_moe_router(h->router, d_x, io_dtype, n_tokens, h->H, h->E_total, top_k, logits, probs, idx, w, s,
+                           P.cb_in, P.Kcb, P.D, const_cast<float*>(P.lut_in));
     if (rc != OJX_OK) return rc;
-    return launch_moe_experts(h->problem(d_x, d_y, idx, w, n_tokens, top_k, io_dtype), s);
+    P.lut_ready = P.lut_in != nullptr;
+    return launch_moe_experts(P, s);
 }
 
 int ojasx_b200_silu_mul(const void* d_gate, const void* d_up, void* d_out, size_t count, int io_dtype, void* stream) {

@@ -66,6 +66,7 @@ struct MoeProblem {
     CsrView gu_csr;           // rows of the flattened [E*2I, H] matrix
     CsrView dn_csr;           // rows of the flattened [E*H, I] matrix
     const float* lut_in;      // optional scratch [n_tokens, G, 256]: tables of the tokens, built once per token
+    int lut_ready;            // lut_in was filled by the router launch: the expert launch does not rebuild it
     const int* pair_list;     // optional scratch [pairs + 1]: [0] = number of pairs this handle evaluates, then
                               // their ids grouped by expert; null = every pair is visited and skipped if not local
     float* inter;             // scratch [pairs, I]

@@ -26,8 +26,11 @@ int take_dequant_gemm_error(int* out);
 // --- moe.cu
 int launch_moe_experts(MoeProblem P, cudaStream_t stream);
 int launch_silu_mul(const void* gate, const void* up, void* out, size_t n, int io_dtype, cudaStream_t stream);
+// codebook .. lut_out: when lut_out is not null the gate/up tables of the tokens ([n_tokens, H/D, 256]) are
+// built by the same launch as the logits.
 int launch_moe_router(const float* Wr, const void* x, int io_dtype, int n_tokens, int H, int E, int k,
-                      float* logits, float* probs, int* idx_out, float* w_out, cudaStream_t stream);
+                      float* logits, float* probs, int* idx_out, float* w_out, cudaStream_t stream,
+                      const float* codebook = nullptr, int Kcb = 0, int D = 0, float* lut_out = nullptr);
 
 // --- kv.cu
 constexpr int kKvMaxSplits = 256;   // context splits of one (sequence, KV head) in kvq decode

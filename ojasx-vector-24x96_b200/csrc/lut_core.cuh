@@ -281,11 +281,10 @@ struct RowWalker {
 // vector (the routed experts of a token): out[t, g, k] with the arithmetic of build_slice.
 // grid = (ceil(G / 16), n_vectors), 256 threads (thread = centroid).
 template <int D>
-__global__ void __launch_bounds__(256) lut_prebuild_kernel(const void* __restrict__ x, int io_dtype, int K, int G,
-                                                           const float* __restrict__ codebook, int Kcb,
-                                                           float* __restrict__ out) {
-    __shared__ float xs[16 * D];
-    const int t = blockIdx.y, g0 = blockIdx.x * 16, ng = min(16, G - g0), kc = threadIdx.x;
+__device__ __forceinline__ void lut_prebuild_block(const void* __restrict__ x, int io_dtype, int K, int G,
+                                                   const float* __restrict__ codebook, int Kcb, float* __restrict__ out,
+                                                   int gx, int t, float* xs /* shared, 16 * D floats */) {
+    const int g0 = gx * 16, ng = min(16, G - g0), kc = threadIdx.x;
     const size_t esz = io_dtype == OJX_BF16 ? 2 : 4;
     const XLoad xl{static_cast<const char*>(x) + (size_t)t * K * esz, K, io_dtype};
     for (int i = threadIdx.x; i < ng * D; i += 256) xs[i] = xl(g0 * D + i);
@@ -301,6 +300,14 @@ __global__ void __launch_bounds__(256) lut_prebuild_kernel(const void* __restric
         for (int d = 1; d < D; ++d) dot = __fadd_rn(dot, __fmul_rn(xg[d], c[d]));
         o[(size_t)gl * 256] = kc < Kcb ? dot : 0.0f;
     }
+}
+
+template <int D>
+__global__ void __launch_bounds__(256) lut_prebuild_kernel(const void* __restrict__ x, int io_dtype, int K, int G,
+                                                           const float* __restrict__ codebook, int Kcb,
+                                                           float* __restrict__ out) {
+    __shared__ float xs[16 * D];
+    lut_prebuild_block<D>(x, io_dtype, K, G, codebook, Kcb, out, blockIdx.x, blockIdx.y, xs);
 }
 
 // CSR outlier row sums for the rows [row0, row0+n) of a work item, reference order

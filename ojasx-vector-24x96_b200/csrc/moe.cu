@@ -212,14 +212,14 @@ __global__ void moe_combine_kernel(const __grid_constant__ MoeProblem P) {
 // off = 16..1.  One warp per expert (its row of W stays hot in L1 while the warp loops over the
 // tokens of its blockIdx.y stripe).
 
-__global__ void __launch_bounds__(256) moe_router_logits_kernel(const float* __restrict__ Wr, const void* __restrict__ x,
-                                                                int io_dtype, int n_tokens, int H, int E,
-                                                                float* __restrict__ logits) {
-    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+__device__ __forceinline__ void router_logits_block(const float* __restrict__ Wr, const void* __restrict__ x, int io_dtype,
+                                                    int n_tokens, int H, int E, float* __restrict__ logits, int bx, int by,
+                                                    int nby) {
+    const int warp = (bx * 256 + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= E) return;
     const float* w = Wr + (size_t)warp * H;
     const size_t esz = io_dtype == OJX_BF16 ? 2 : 4;
-    for (int t = blockIdx.y; t < n_tokens; t += gridDim.y) {
+    for (int t = by; t < n_tokens; t += nby) {
         const XLoad xl{static_cast<const char*>(x) + (size_t)t * H * esz, H, io_dtype};
         float part = 0.0f;
         int c = lane;
@@ -234,6 +234,31 @@ __global__ void __launch_bounds__(256) moe_router_logits_kernel(const float* __r
 #pragma unroll
         for (int off = 16; off >= 1; off >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, off));
         if (lane == 0) logits[(size_t)t * E + warp] = part;
+    }
+}
+
+__global__ void __launch_bounds__(256) moe_router_logits_kernel(const float* __restrict__ Wr, const void* __restrict__ x,
+                                                                int io_dtype, int n_tokens, int H, int E,
+                                                                float* __restrict__ logits) {
+    router_logits_block(Wr, x, io_dtype, n_tokens, H, E, logits, blockIdx.x, blockIdx.y, gridDim.y);
+}
+
+// Router logits and the per-token gate/up tables in one launch: neither depends on the other, both
+// depend only on x.  Blocks [0, lx*ly) are logits blocks (bx = b % lx, by = b / lx), the rest build
+// tables (16 groups of one token each).
+template <int D>
+__global__ void __launch_bounds__(256) moe_logits_prebuild_kernel(const float* __restrict__ Wr, const void* __restrict__ x,
+                                                                  int io_dtype, int n_tokens, int H, int E,
+                                                                  float* __restrict__ logits, int lx, int ly, int G,
+                                                                  const float* __restrict__ codebook, int Kcb,
+                                                                  float* __restrict__ lut_out) {
+    __shared__ float xs[16 * D];
+    const int b = blockIdx.x;
+    if (b < lx * ly) {
+        router_logits_block(Wr, x, io_dtype, n_tokens, H, E, logits, b % lx, b / lx, ly);
+    } else {
+        const int j = b - lx * ly, px = (G + 15) / 16;
+        lut_prebuild_block<D>(x, io_dtype, H, G, codebook, Kcb, lut_out, j % px, j / px, xs);
     }
 }
 
@@ -294,6 +319,92 @@ __global__ void __launch_bounds__(kTopkWarps * 32) moe_router_topk_kernel(const 
     for (int r = lane; r < k; r += 32) w_out[(size_t)t * k + r] = __fdiv_rn(w_out[(size_t)t * k + r], ws);
 }
 
+// Same rule for E <= 32 * EPL: a lane keeps its EPL probabilities (experts lane, lane + 32, ...) in
+// registers, so the k arg-max rounds touch no memory; only the sequential normaliser goes through
+// shared memory.
+template <int EPL>
+__global__ void __launch_bounds__(kTopkWarps * 32) moe_router_topk_reg_kernel(const float* __restrict__ logits, int n_tokens,
+                                                                             int E, int k, int* __restrict__ idx_out,
+                                                                             float* __restrict__ w_out,
+                                                                             float* __restrict__ probs) {
+    extern __shared__ float topk_smem[];  // [kTopkWarps][E]
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int t = blockIdx.x * kTopkWarps + wid;
+    if (t >= n_tokens) return;
+    float* p = topk_smem + (size_t)wid * E;
+    const float* l = logits + (size_t)t * E;
+    float v[EPL];
+    float m = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+        const int e = lane + 32 * j;
+        v[j] = e < E ? l[e] : -INFINITY;
+        m = fmaxf(m, v[j]);
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+        const int e = lane + 32 * j;
+        if (e < E) {
+            v[j] = (float)exp((double)__fsub_rn(v[j], m));
+            p[e] = v[j];
+        }
+    }
+    __syncwarp();
+    float s = 0.0f;
+    if (lane == 0) {
+        int e = 0;
+        for (; e + 8 <= E; e += 8) {   // loads ahead, additions in index order
+            float q[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) q[u] = p[e + u];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) s = __fadd_rn(s, q[u]);
+        }
+        for (; e < E; ++e) s = __fadd_rn(s, p[e]);
+    }
+    s = __shfl_sync(0xffffffffu, s, 0);
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+        const int e = lane + 32 * j;
+        if (e < E) {
+            v[j] = __fdiv_rn(v[j], s);
+            probs[(size_t)t * E + e] = v[j];
+        } else {
+            v[j] = -1.0f;   // never selected (probabilities are >= 0)
+        }
+    }
+    float ws = 0.0f, mine = 0.0f;   // lane r keeps the r-th selected weight
+    for (int r = 0; r < k; ++r) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+#pragma unroll
+        for (int j = 0; j < EPL; ++j)
+            if (v[j] > bv) { bv = v[j]; bi = lane + 32 * j; }   // ascending index per lane keeps the lowest index on ties
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if ((bi & 31) == lane) {
+#pragma unroll
+            for (int j = 0; j < EPL; ++j)
+                if (j == (bi >> 5)) v[j] = -1.0f;   // taken
+        }
+        if (lane == 0) idx_out[(size_t)t * k + r] = bi;
+        if ((r & 31) == lane) mine = bv;
+        ws = __fadd_rn(ws, bv);  // same value in every lane, selection order
+        if ((r & 31) == 31 || r == k - 1) {   // every 32 rounds the lanes write their weights (each lane only ever
+            const int r0 = r & ~31;            // touches indices = lane mod 32); normalised below
+            if (r0 + lane <= r) w_out[(size_t)t * k + r0 + lane] = mine;
+        }
+    }
+    __syncwarp();
+    for (int r = lane; r < k; r += 32) w_out[(size_t)t * k + r] = __fdiv_rn(w_out[(size_t)t * k + r], ws);
+}
+
 // out = silu(gate) * up, elementwise, computed in fp32 with the expert kernels' silu and rounded once
 // to the io dtype (the SwiGLU step of a dense VQ MLP block: gate and up are separate VQ linears).
 __global__ void silu_mul_kernel(const void* __restrict__ gate, const void* __restrict__ up, void* __restrict__ out,
@@ -326,6 +437,8 @@ static int set_smem(K kern) {
     return OJX_OK;
 }
 
+constexpr int kMoePlanMinPairs = 64;
+
 template <int D>
 static int launch_moe_experts_t(const MoeProblem& P, cudaStream_t s) {
     int rc;
@@ -341,7 +454,7 @@ static int launch_moe_experts_t(const MoeProblem& P, cudaStream_t s) {
         OJX_CUDA_TRY(cudaGetLastError());
         ++extra;
     }
-    if (P.lut_in) {
+    if (P.lut_in && !P.lut_ready) {
         lut_prebuild_kernel<D><<<dim3((P.G + 15) / 16, P.n_tokens), 256, 0, s>>>(P.x, P.io_dtype, P.H, P.G, P.cb_in, P.Kcb,
                                                                                 const_cast<float*>(P.lut_in));
         OJX_CUDA_TRY(cudaGetLastError());
@@ -365,6 +478,9 @@ int launch_moe_experts(MoeProblem P, cudaStream_t s) {
     // Tiles: spread few pairs over the SMs, keep tiles whole when there are many pairs.  An
     // expert-parallel shard expects only its share of the routed pairs.
     const int expect = P.E_total > P.E ? (int)(((long long)pairs * P.E + P.E_total - 1) / P.E_total) : pairs;
+    // A handful of pairs on an unsharded expert table: the work list (grouping by expert, dropping the
+    // pairs of other shards) buys nothing, so its kernel is left out and the pairs are visited in order.
+    if (pairs <= kMoePlanMinPairs && P.E_total <= P.E) P.pair_list = nullptr;
     int want = (sms + expect - 1) / (expect > 0 ? expect : 1);
     P.gu_tile = round_up((P.I + want - 1) / want, 16);
     if (P.gu_tile > kAccRows / 2) P.gu_tile = kAccRows / 2;
@@ -382,17 +498,32 @@ int launch_moe_experts(MoeProblem P, cudaStream_t s) {
 }
 
 int launch_moe_router(const float* Wr, const void* x, int io_dtype, int n_tokens, int H, int E, int k,
-                      float* logits, float* probs, int* idx_out, float* w_out, cudaStream_t s) {
+                      float* logits, float* probs, int* idx_out, float* w_out, cudaStream_t s,
+                      const float* codebook, int Kcb, int D, float* lut_out) {
     if (!Wr || !x || !logits || !probs || !idx_out || !w_out) return OJX_ERR_ARG;
     if (n_tokens <= 0 || k <= 0 || k > E) return OJX_ERR_ARG;
     const int warps_per_block = 8;
-    const dim3 lgrid((E + warps_per_block - 1) / warps_per_block, n_tokens < 32 ? n_tokens : 32);
-    moe_router_logits_kernel<<<lgrid, 256, 0, s>>>(Wr, x, io_dtype, n_tokens, H, E, logits);
+    const int lx = (E + warps_per_block - 1) / warps_per_block, ly = n_tokens < 32 ? n_tokens : 32;
+    if (lut_out) {   // the gate/up tables ride along (one launch less)
+        if (!codebook || H % D != 0) return OJX_ERR_ARG;
+        const int G = H / D, grid = lx * ly + (G + 15) / 16 * n_tokens;
+        switch (D) {
+            case 4: moe_logits_prebuild_kernel<4><<<grid, 256, 0, s>>>(Wr, x, io_dtype, n_tokens, H, E, logits, lx, ly, G, codebook, Kcb, lut_out); break;
+            case 8: moe_logits_prebuild_kernel<8><<<grid, 256, 0, s>>>(Wr, x, io_dtype, n_tokens, H, E, logits, lx, ly, G, codebook, Kcb, lut_out); break;
+            case 16: moe_logits_prebuild_kernel<16><<<grid, 256, 0, s>>>(Wr, x, io_dtype, n_tokens, H, E, logits, lx, ly, G, codebook, Kcb, lut_out); break;
+            case 32: moe_logits_prebuild_kernel<32><<<grid, 256, 0, s>>>(Wr, x, io_dtype, n_tokens, H, E, logits, lx, ly, G, codebook, Kcb, lut_out); break;
+            default: return OJX_ERR_UNSUPPORTED;
+        }
+    } else {
+        moe_router_logits_kernel<<<dim3(lx, ly), 256, 0, s>>>(Wr, x, io_dtype, n_tokens, H, E, logits);
+    }
     OJX_CUDA_TRY(cudaGetLastError());
     const size_t tsm = sizeof(float) * kTopkWarps * (size_t)E;
     if (tsm > 200 * 1024) return OJX_ERR_TOO_LARGE;
     if (tsm > 48 * 1024) OJX_CUDA_TRY(cudaFuncSetAttribute(moe_router_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tsm));
-    moe_router_topk_kernel<<<(n_tokens + kTopkWarps - 1) / kTopkWarps, kTopkWarps * 32, tsm, s>>>(logits, n_tokens, E, k, idx_out, w_out, probs);
+    const int tgrid = (n_tokens + kTopkWarps - 1) / kTopkWarps;
+    if (E <= 512) moe_router_topk_reg_kernel<16><<<tgrid, kTopkWarps * 32, tsm, s>>>(logits, n_tokens, E, k, idx_out, w_out, probs);
+    else moe_router_topk_kernel<<<tgrid, kTopkWarps * 32, tsm, s>>>(logits, n_tokens, E, k, idx_out, w_out, probs);
     OJX_CUDA_TRY(cudaGetLastError());
     count_launch(2);
     return OJX_OK;
