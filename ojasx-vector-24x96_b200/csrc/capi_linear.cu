@@ -324,6 +324,19 @@ int ojasx_b200_linear_group_forward(OjasxLinearGroupHandle group, const void* d_
     if (io_dtype != OJX_F32 && io_dtype != OJX_BF16) return OJX_ERR_ARG;
     auto* g = static_cast<LinearGroup*>(group);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // A few problems of one shape (q/k/v, gate/up): one cluster launch, the problems travel as kernel
+    // arguments, so nothing is copied or synchronised (safe inside a stream capture).
+    if (g->host.size() <= 8 && !linear_cluster_disabled()) {
+        LinearProblem tmp[8];
+        for (size_t i = 0; i < g->host.size(); ++i) {
+            tmp[i] = g->host[i];
+            tmp[i].x = static_cast<const char*>(d_x) + i * x_stride_bytes;
+            tmp[i].y = static_cast<char*>(d_y) + i * y_stride_bytes;
+            tmp[i].io_dtype = io_dtype;
+        }
+        const int rc = try_launch_linear_cluster_group(tmp, (int)g->host.size(), s);
+        if (rc != OJX_ERR_UNSUPPORTED) return rc;
+    }
     // The problem table is rewritten only when the I/O binding changes, so steady-state calls
     // enqueue exactly one kernel.
     if (g->bound_x != d_x || g->bound_y != d_y || g->bound_xs != x_stride_bytes || g->bound_ys != y_stride_bytes ||

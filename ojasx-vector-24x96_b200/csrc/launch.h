@@ -12,6 +12,10 @@ int launch_linear_group(const LinearProblem* d_probs, int nprobs, int total_item
 
 // --- linear_cluster.cu: OJX_ERR_UNSUPPORTED means "use the persistent kernel"
 int try_launch_linear_cluster(const LinearProblem& P, cudaStream_t stream);
+// Up to 8 host-side problems with the same K, G, block_dim, batch and io dtype in one cluster launch.
+int try_launch_linear_cluster_group(const LinearProblem* probs, int count, cudaStream_t stream);
+// True when OJASX_B200_LINEAR_KERNEL=persistent asks for the streaming kernel only.
+bool linear_cluster_disabled();
 
 // --- rvq_generic.cu
 int launch_rvq_generic(const uint8_t* packed, const float* codebooks, const float* row_scales, const float* bias,

@@ -112,6 +112,7 @@ static bool force_persistent() {
     const char* e = getenv("OJASX_B200_LINEAR_KERNEL");
     return e && e[0] == 'p';
 }
+bool linear_cluster_disabled() { return force_persistent(); }
 
 int validate_linear(const LinearProblem& P) {
     if (!P.codes || !P.codebook || !P.x || !P.y) return OJX_ERR_ARG;

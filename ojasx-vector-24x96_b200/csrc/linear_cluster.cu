@@ -32,12 +32,23 @@ constexpr int kClProd = 2048;   // CSR products staged per pass
 struct ClusterPlan {
     int C;        // CTAs per cluster
     int cpc;      // 16-group chunks per CTA
-    int R;        // rows per tile (multiple of 32)
-    int RO;       // rows of a tile owned by one CTA for the ordered sum
+    int R;        // rows per tile (multiple of 32); the largest of the problems' tiles in a grouped launch
+    int RO;       // rows of a tile owned by one CTA for the ordered sum (of the largest tile)
     int stride;   // bytes per staged code row (odd multiple of 16: conflict-free 128-bit reads)
     int n_tiles;
     int n_clusters;
     size_t smem;
+};
+
+// Up to kClMaxGroup problems with the same K, G, block_dim and batch in one launch (q/k/v of an attention
+// block, gate/up of an MLP): every cluster works on one problem, clusters [first[p], first[p+1]) on
+// problem p with that problem's own tile size.  Passed by value, so a launch needs no device-side table.
+constexpr int kClMaxGroup = 8;
+struct ClusterGroup {
+    LinearProblem P[kClMaxGroup];
+    int first[kClMaxGroup + 1];
+    int R[kClMaxGroup], RO[kClMaxGroup], n_tiles[kClMaxGroup];
+    int count;
 };
 
 __device__ __forceinline__ unsigned cluster_ctarank() {
@@ -59,22 +70,28 @@ __device__ __forceinline__ void cluster_sync_all() {
 
 template <int D>
 __global__ void __launch_bounds__(kClThreads, 1)
-lut_linear_cluster_kernel(const __grid_constant__ LinearProblem P, const __grid_constant__ ClusterPlan plan) {
+lut_linear_cluster_kernel(const __grid_constant__ ClusterGroup grp, const __grid_constant__ ClusterPlan plan) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int G = P.G, C = plan.C, RO = plan.RO;
+    const int C = plan.C;
+    const int cid_all = blockIdx.x / C;
+    int pi = 0;
+    while (pi + 1 < grp.count && cid_all >= grp.first[pi + 1]) ++pi;   // same for every CTA of a cluster
+    const LinearProblem& P = grp.P[pi];
+    const int G = P.G, RO = grp.RO[pi], R = grp.R[pi], n_tiles = grp.n_tiles[pi];
+    const int n_clusters = grp.first[pi + 1] - grp.first[pi];
     const int ngp = plan.cpc * 16;                                       // groups of a full slice
     float* lut = reinterpret_cast<float*>(smem_raw);                     // [ngp][256]
     const int Gp = G + 4;                                                // padded row of gathered values
-    float* recv = lut + (size_t)ngp * 256;                               // [RO][Gp]
-    uint8_t* codes_s = reinterpret_cast<uint8_t*>(recv + (size_t)Gp * RO);  // [R][stride]
+    float* recv = lut + (size_t)ngp * 256;                               // [plan.RO][Gp]
+    uint8_t* codes_s = reinterpret_cast<uint8_t*>(recv + (size_t)Gp * plan.RO);  // [plan.R][stride]
     float* xs = reinterpret_cast<float*>(codes_s + (size_t)plan.R * plan.stride);  // [ngp*D]
-    float* oacc_s = xs + (size_t)ngp * D;                                          // [RO]
-    int* rp_s = reinterpret_cast<int*>(oacc_s + RO);                               // [RO + 1]
-    float* prod_s = reinterpret_cast<float*>(rp_s + RO + 1);                       // [kClProd]
+    float* oacc_s = xs + (size_t)ngp * D;                                          // [plan.RO]
+    int* rp_s = reinterpret_cast<int*>(oacc_s + plan.RO);                          // [plan.RO + 1]
+    float* prod_s = reinterpret_cast<float*>(rp_s + plan.RO + 1);                  // [kClProd]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int rank = (int)cluster_ctarank();
-    const int cid = blockIdx.x / C;
+    const int cid = cid_all - grp.first[pi];
     const int b = blockIdx.y;
     const int g0 = rank * ngp;
     const int ng = max(0, min(G, g0 + ngp) - g0);
@@ -84,8 +101,8 @@ lut_linear_cluster_kernel(const __grid_constant__ LinearProblem P, const __grid_
     const unsigned recv_addr = static_cast<unsigned>(__cvta_generic_to_shared(recv));
 
     auto stage_codes = [&](int tile) {
-        const int r0 = P.row_start + tile * plan.R;
-        const int nR = min(plan.R, P.row_stop - r0);
+        const int r0 = P.row_start + tile * R;
+        const int nR = min(R, P.row_stop - r0);
         const int ppr = ng >> 4;  // 16-byte pieces per row
         for (int i = tid; i < nR * ppr; i += kClThreads) {
             const int row = i / ppr, c = i - row * ppr;
@@ -101,8 +118,8 @@ lut_linear_cluster_kernel(const __grid_constant__ LinearProblem P, const __grid_
     // depends only on x, so it runs while the tile's code bytes are still in flight.
     auto outlier_sums = [&](int tile) {
         if (P.csr.nnz <= 0) return;
-        const int r0 = P.row_start + tile * plan.R;
-        const int nR = min(plan.R, P.row_stop - r0);
+        const int r0 = P.row_start + tile * R;
+        const int nR = min(R, P.row_stop - r0);
         const int first = rank * RO;
         const int mine = max(0, min(RO, nR - first));
         for (int i = tid; i <= mine; i += kClThreads) rp_s[i] = mine > 0 ? P.csr.row_ptrs[r0 + first + i] : 0;
@@ -124,7 +141,7 @@ lut_linear_cluster_kernel(const __grid_constant__ LinearProblem P, const __grid_
 
     OJX_TICK_INIT;
     int tile = cid;
-    if (tile < plan.n_tiles) {
+    if (tile < n_tiles) {
         stage_codes(tile);
         OJX_TICK(0);
         outlier_sums(tile);
@@ -149,9 +166,9 @@ lut_linear_cluster_kernel(const __grid_constant__ LinearProblem P, const __grid_
         }
     }
 
-    for (; tile < plan.n_tiles; tile += plan.n_clusters) {
-        const int r0 = P.row_start + tile * plan.R;
-        const int nR = min(plan.R, P.row_stop - r0);
+    for (; tile < n_tiles; tile += n_clusters) {
+        const int r0 = P.row_start + tile * R;
+        const int nR = min(R, P.row_stop - r0);
         OJX_TICK(3);
         cp_async_wait<0>();
         __syncthreads();  // codes landed, table built
@@ -186,7 +203,7 @@ lut_linear_cluster_kernel(const __grid_constant__ LinearProblem P, const __grid_
         OJX_TICK(6);
 
         // next tile's codes can stream in while this one is summed (codes_s is no longer read)
-        if (tile + plan.n_clusters < plan.n_tiles) stage_codes(tile + plan.n_clusters);
+        if (tile + n_clusters < n_tiles) stage_codes(tile + n_clusters);
 
         // ordered sums for my rows of the tile
         const int first = rank * RO;
@@ -220,14 +237,14 @@ lut_linear_cluster_kernel(const __grid_constant__ LinearProblem P, const __grid_
         }
         OJX_TICK(7);
         __syncthreads();     // oacc_s of this tile has been consumed
-        if (tile + plan.n_clusters < plan.n_tiles) outlier_sums(tile + plan.n_clusters);
+        if (tile + n_clusters < n_tiles) outlier_sums(tile + n_clusters);
         cluster_sync_all();  // recv may be overwritten by the next tile; nobody exits while peers may still write
         OJX_TICK(8);
     }
 }
 
 template <int D>
-static int launch_cluster_t(const LinearProblem& P, ClusterPlan plan, cudaStream_t stream, bool dry_run) {
+static int launch_cluster_t(const ClusterGroup& grp, ClusterPlan plan, cudaStream_t stream, bool dry_run) {
     auto kern = lut_linear_cluster_kernel<D>;
     // query_max_clusters<D> already opted this kernel in to kClSmemCap bytes of dynamic shared memory on
     // this device (plans never exceed it), so nothing has to be set per launch.
@@ -242,9 +259,9 @@ static int launch_cluster_t(const LinearProblem& P, ClusterPlan plan, cudaStream
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cfg.gridDim = dim3(plan.C * plan.n_clusters, P.batch);
+    cfg.gridDim = dim3(plan.C * plan.n_clusters, grp.P[0].batch);
     if (dry_run) return OJX_OK;
-    OJX_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, P, plan));
+    OJX_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, grp, plan));
     count_launch(1);
     return OJX_OK;
 }
@@ -287,53 +304,100 @@ static int max_active_clusters(int D, int C) {
     return slot > 0 ? slot : 0;
 }
 
-// Picks cluster size, group slice and row tile; returns false when the problem does not suit
-// this kernel (unaligned code rows, too large a table slice, too many rows).
-bool plan_linear_cluster(const LinearProblem& P, ClusterPlan* out) {
-    const int rows = P.row_stop - P.row_start;
-    if ((P.G & 15) || (reinterpret_cast<uintptr_t>(P.codes) & 15) || P.G == 0) return false;
-    if (P.D != 4 && P.D != 8 && P.D != 16 && P.D != 32) return false;
+// Picks cluster size, group slice and row tiles for `count` problems that share K, G, block_dim, batch and
+// io dtype; returns false when they do not suit this kernel (unaligned code rows, too large a table
+// slice, too many rows or problems).  The resident clusters are shared out in proportion to the rows.
+static bool plan_cluster_group(const LinearProblem* Ps, int count, ClusterPlan* out, ClusterGroup* grp) {
+    if (count <= 0 || count > kClMaxGroup) return false;
+    const LinearProblem& P0 = Ps[0];
+    long long rows_total = 0;
+    for (int p = 0; p < count; ++p) {
+        const LinearProblem& P = Ps[p];
+        if (P.G != P0.G || P.K != P0.K || P.D != P0.D || P.batch != P0.batch || P.io_dtype != P0.io_dtype || P.Kcb != P0.Kcb) return false;
+        if ((P.G & 15) || (reinterpret_cast<uintptr_t>(P.codes) & 15) || P.G == 0 || P.row_stop <= P.row_start) return false;
+        rows_total += P.row_stop - P.row_start;
+    }
+    if (P0.D != 4 && P0.D != 8 && P0.D != 16 && P0.D != 32) return false;
     // Measured on B200 (2560->6912): 12.5 us against 22.7 us for the persistent kernel at batch 1,
     // but 33 us against 24.7 us at batch 4, where the persistent kernel's larger tiles win.
-    if (P.batch > 2 || (long long)rows * P.batch > 32768) return false;
-    const int TC = P.G / 16, sms = num_sms();
+    if (P0.batch > 2 || rows_total * P0.batch > 32768) return false;
+    const int TC = P0.G / 16, sms = num_sms();
     double best = 1e30;
     bool found = false;
     for (int C = 1; C <= 8; ++C) {
         ClusterPlan pl{};
+        ClusterGroup g{};
         pl.C = C;
         pl.cpc = (TC + C - 1) / C;
         if ((C - 1) * pl.cpc >= TC && C > 1) continue;  // would leave the last CTA without groups
-        int resident = max_active_clusters(P.D, C);
+        int resident = max_active_clusters(P0.D, C);
         if (resident <= 0) continue;
         if (resident > sms / C) resident = sms / C;
-        const int ncl_max = resident / P.batch > 0 ? resident / P.batch : 1;
-        pl.R = round_up((rows + ncl_max - 1) / ncl_max, 32);
+        const int ncl_max = resident / P0.batch > 0 ? resident / P0.batch : 1;
+        if (ncl_max < count) continue;
         pl.stride = pl.cpc * 16 + ((pl.cpc & 1) ? 0 : 16);
-        for (;;) {
+        // clusters per problem: proportional to its rows, at least one, at most ncl_max in all
+        int ncl[kClMaxGroup], used = 0;
+        for (int p = 0; p < count; ++p) {
+            const long long rows = Ps[p].row_stop - Ps[p].row_start;
+            ncl[p] = (int)std::max<long long>(1, rows * (ncl_max - count) / rows_total + 1);
+            used += ncl[p];
+        }
+        while (used > ncl_max) {   // rounding: take from the problem with the fewest rows per cluster
+            int w = -1;
+            double least = 1e30;
+            for (int p = 0; p < count; ++p) {
+                const double per = double(Ps[p].row_stop - Ps[p].row_start) / ncl[p];
+                if (ncl[p] > 1 && per < least) { least = per; w = p; }
+            }
+            if (w < 0) break;
+            --ncl[w]; --used;
+        }
+        if (used > ncl_max) continue;
+        int Rmax = 0;
+        for (int p = 0; p < count; ++p) {
+            const int rows = Ps[p].row_stop - Ps[p].row_start;
+            g.R[p] = round_up((rows + ncl[p] - 1) / ncl[p], 32);
+            Rmax = std::max(Rmax, g.R[p]);
+        }
+        for (;;) {   // shrink the largest tiles until the shared memory fits
+            pl.R = Rmax;
             pl.RO = (pl.R + C - 1) / C;
-            pl.smem = sizeof(float) * ((size_t)pl.cpc * 16 * 256 + (size_t)(P.G + 4) * pl.RO + (size_t)pl.cpc * 16 * P.D + 2 * pl.RO + 1 + kClProd) +
+            pl.smem = sizeof(float) * ((size_t)pl.cpc * 16 * 256 + (size_t)(P0.G + 4) * pl.RO + (size_t)pl.cpc * 16 * P0.D + 2 * pl.RO + 1 + kClProd) +
                       (size_t)pl.R * pl.stride;
-            if (pl.smem <= kClSmemCap || pl.R <= 32) break;
-            pl.R -= 32;
+            if (pl.smem <= kClSmemCap || Rmax <= 32) break;
+            Rmax -= 32;
         }
         if (pl.smem > kClSmemCap) continue;
-        pl.n_tiles = (rows + pl.R - 1) / pl.R;
-        pl.n_clusters = pl.n_tiles < ncl_max ? pl.n_tiles : ncl_max;
-        const int waves = (pl.n_tiles + pl.n_clusters - 1) / pl.n_clusters;
+        int waves = 1, first = 0;
+        for (int p = 0; p < count; ++p) {
+            const int rows = Ps[p].row_stop - Ps[p].row_start;
+            g.P[p] = Ps[p];
+            g.R[p] = std::min(g.R[p], Rmax);
+            g.RO[p] = (g.R[p] + C - 1) / C;
+            g.n_tiles[p] = (rows + g.R[p] - 1) / g.R[p];
+            const int n = std::min(ncl[p], g.n_tiles[p]);
+            g.first[p] = first;
+            first += n;
+            waves = std::max(waves, (g.n_tiles[p] + n - 1) / n);
+        }
+        g.first[count] = first;
+        g.count = count;
+        pl.n_clusters = first;
+        pl.n_tiles = 0;
         // crude cost in clocks: table slice build + per-tile gather and ordered sum
-        const double cost = pl.cpc * 16 * 75.0 + waves * (pl.R * pl.cpc * 16 / 6.0 + P.G * 6.0 + 1500.0);
-        if (cost < best) { best = cost; *out = pl; found = true; }
+        const double cost = pl.cpc * 16 * 75.0 + waves * (pl.R * pl.cpc * 16 / 6.0 + P0.G * 6.0 + 1500.0);
+        if (cost < best) { best = cost; *out = pl; *grp = g; found = true; }
     }
     return found;
 }
 
-int launch_linear_cluster(const LinearProblem& P, const ClusterPlan& plan, cudaStream_t stream) {
-    switch (P.D) {
-        case 4: return launch_cluster_t<4>(P, plan, stream, false);
-        case 8: return launch_cluster_t<8>(P, plan, stream, false);
-        case 16: return launch_cluster_t<16>(P, plan, stream, false);
-        case 32: return launch_cluster_t<32>(P, plan, stream, false);
+static int launch_cluster_group(const ClusterGroup& grp, const ClusterPlan& plan, cudaStream_t stream) {
+    switch (grp.P[0].D) {
+        case 4: return launch_cluster_t<4>(grp, plan, stream, false);
+        case 8: return launch_cluster_t<8>(grp, plan, stream, false);
+        case 16: return launch_cluster_t<16>(grp, plan, stream, false);
+        case 32: return launch_cluster_t<32>(grp, plan, stream, false);
         default: return OJX_ERR_UNSUPPORTED;
     }
 }
@@ -342,8 +406,18 @@ int launch_linear_cluster(const LinearProblem& P, const ClusterPlan& plan, cudaS
 // to the persistent kernel.
 int try_launch_linear_cluster(const LinearProblem& P, cudaStream_t stream) {
     ClusterPlan plan;
-    if (!plan_linear_cluster(P, &plan)) return OJX_ERR_UNSUPPORTED;
-    return launch_linear_cluster(P, plan, stream);
+    ClusterGroup grp;
+    if (!plan_cluster_group(&P, 1, &plan, &grp)) return OJX_ERR_UNSUPPORTED;
+    return launch_cluster_group(grp, plan, stream);
+}
+
+// Same for a few problems at once (host copies of the problems; nothing is read from them after
+// the call returns).  OJX_ERR_UNSUPPORTED: use the persistent grouped kernel.
+int try_launch_linear_cluster_group(const LinearProblem* probs, int count, cudaStream_t stream) {
+    ClusterPlan plan;
+    ClusterGroup grp;
+    if (!plan_cluster_group(probs, count, &plan, &grp)) return OJX_ERR_UNSUPPORTED;
+    return launch_cluster_group(grp, plan, stream);
 }
 
 }  // namespace ojx

@@ -19,7 +19,7 @@ import numpy as np
 import torch
 
 from . import synth
-from .ops import VQKVCache, VQLinear, VQMoE, add_int_, rmsnorm, rope_qk_
+from .ops import VQKVCache, VQLinear, VQLinearGroup, VQMoE, add_int_, rmsnorm, rope_qk_
 
 
 @dataclass
@@ -92,6 +92,9 @@ def make_stack_weights(seed: int, cfg: StackConfig) -> StackWeights:
 class _Layer:
     def __init__(self, w: LayerWeights, cfg: StackConfig, batch: int, device):
         self.q, self.k, self.v, self.o = (VQLinear.from_weights(a) for a in (w.q, w.k, w.v, w.o))
+        # one sequence: q, k and v read the same vector and run as one grouped launch into a fixed buffer
+        self.qkv = VQLinearGroup([self.q, self.k, self.v]) if batch == 1 else None
+        self.qkv_out = None
         self.moe = VQMoE(w.moe)
         self.moe.reserve(batch, cfg.top_k)
         self.norm1 = torch.from_numpy(w.norm1).to(device)
@@ -138,9 +141,17 @@ class VQDecoderStack:
         pending = None                       # residual branch not yet added to h (added inside the next norm)
         for l in self.layers:
             a = rmsnorm(h, l.norm1, cfg.rms_eps, add=pending)
-            q = l.q(a).view(B, cfg.q_heads, cfg.head_dim)
-            k = l.k(a).view(B, cfg.kv_heads, cfg.head_dim)
-            v = l.v(a).view(B, cfg.kv_heads, cfg.head_dim)
+            if l.qkv is not None:
+                if l.qkv_out is None or l.qkv_out.dtype != a.dtype:
+                    l.qkv_out = torch.empty((3, cfg.q_heads * cfg.head_dim), dtype=a.dtype, device=self.device)
+                l.qkv.forward(a.view(-1), l.qkv_out, shared_x=True)
+                q = l.qkv_out[0].view(B, cfg.q_heads, cfg.head_dim)
+                k = l.qkv_out[1, : cfg.kv_heads * cfg.head_dim].view(B, cfg.kv_heads, cfg.head_dim)
+                v = l.qkv_out[2, : cfg.kv_heads * cfg.head_dim].view(B, cfg.kv_heads, cfg.head_dim)
+            else:
+                q = l.q(a).view(B, cfg.q_heads, cfg.head_dim)
+                k = l.k(a).view(B, cfg.kv_heads, cfg.head_dim)
+                v = l.v(a).view(B, cfg.kv_heads, cfg.head_dim)
             rope_qk_(q, k, self.pos, cfg.rope_theta)
             l.cache.append(k, v)
             att = l.cache.decode(q)

@@ -188,8 +188,14 @@ class VQMLP:
     def __init__(self, gate: VQLinear, up: VQLinear, down: VQLinear):
         assert gate.in_features == up.in_features and gate.out_features == up.out_features == down.in_features
         self.gate, self.up, self.down = gate, up, down
+        self._pair = VQLinearGroup([gate, up])   # one launch for gate and up when there is a single token
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.numel() == self.gate.in_features:   # one token: gate and up share x and run as one grouped launch
+            gu = torch.empty((2, self.gate.out_features), dtype=x.dtype, device=x.device)
+            self._pair.forward(x.reshape(-1), gu, shared_x=True)
+            h = silu_mul(gu[0], gu[1], out=gu[0])
+            return self.down(h.view(*x.shape[:-1], -1))
         g = self.gate(x)
         u = self.up(x)
         return self.down(silu_mul(g, u, out=g))
