@@ -57,7 +57,7 @@ MoeProblem MoeHandle::problem(const void* x, void* y, const int* idx, const floa
 
 KvqHandle::~KvqHandle() {
     DeviceGuard g(dev);
-    cudaFree(k_codes); cudaFree(v_codes); cudaFree(k_cb); cudaFree(v_cb); cudaFree(seq_lens); cudaFree(error_flag);
+    cudaFree(k_codes); cudaFree(v_codes); cudaFree(k_cb); cudaFree(v_cb); cudaFree(seq_lens); cudaFree(error_flag); cudaFree(counters);
     cudaFree(partials);
 }
 
@@ -272,6 +272,7 @@ OjasxKvqHandle ojasx_b200_kvq_create(int batch, int kv_heads, int q_heads, int h
     if (rc == OJX_OK) rc = upload((void**)&h->v_cb, v_codebook, cbb);
     if (rc == OJX_OK) rc = upload((void**)&h->seq_lens, nullptr, sizeof(int) * (size_t)batch);
     if (rc == OJX_OK) rc = upload((void**)&h->error_flag, nullptr, sizeof(int));
+    if (rc == OJX_OK) rc = upload((void**)&h->counters, nullptr, sizeof(int) * ((size_t)batch + (size_t)batch * kv_heads));
     if (rc != OJX_OK) { delete h; return nullptr; }
     return h;
 }
@@ -322,6 +323,7 @@ static KvqProblem kvq_problem(const KvqHandle* h, int io) {
     KvqProblem P{};
     P.k_codes = h->k_codes; P.v_codes = h->v_codes; P.k_cb = h->k_cb; P.v_cb = h->v_cb;
     P.seq_lens = h->seq_lens; P.error_flag = h->error_flag; P.partials = static_cast<float*>(h->partials);
+    P.append_done = h->counters; P.split_done = h->counters + h->B;
     P.B = h->B; P.Hkv = h->Hkv; P.Hq = h->Hq; P.head_dim = h->head_dim; P.D = h->D; P.G = h->G; P.Kcb = 256;
     P.max_seq = h->max_seq; P.io_dtype = io;
     return P;

@@ -93,6 +93,8 @@ struct KvqProblem {
     int* seq_lens;          // [B] tokens cached per sequence
     int* error_flag;        // set to 1 when an append found the cache full
     float* partials;        // scratch [B, Hkv, n_chunks, R, head_dim + 2]
+    int* append_done;       // [B] CTAs of the running append that have finished (returns to 0)
+    int* split_done;        // [B, Hkv] decode CTAs of a (sequence, head) that have written their partial (returns to 0)
     int B, Hkv, Hq, head_dim, D, G, Kcb, max_seq;
     int chunk, n_chunks;
     int v_copies;           // copies of the value codebook in the decode kernel's shared memory (1 or 8)

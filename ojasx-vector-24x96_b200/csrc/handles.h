@@ -103,6 +103,7 @@ struct KvqHandle {
     float* v_cb = nullptr;
     int* seq_lens = nullptr;
     int* error_flag = nullptr;
+    int* counters = nullptr;                 // [B] append + [B*Hkv] decode completion counters (zero between launches)
     void* partials = nullptr;
     size_t partials_cap = 0;
     ~KvqHandle();

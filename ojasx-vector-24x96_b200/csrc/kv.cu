@@ -31,18 +31,22 @@ __device__ __forceinline__ float load_io(const void* p, size_t i, int dtype) {
 // ------------------------------------------------------------------------------ kvq append
 // grid = (ceil(tasks / warps per CTA), B).  Task = (k|v, kv head, group); one warp per task scans
 // the 256 centroids.  dist = (|v|^2 - 2 v.c) + |c|^2 with every dot product a sequential fp32 sum
-// (separate multiply and add); arg-min takes the first minimum.  The sequence length is bumped
-// by kvq_bump_kernel once every task has written its code.
+// (separate multiply and add); arg-min takes the first minimum.  Every CTA counts itself done when
+// its codes are written; the last one of a sequence advances that sequence's length (the others read
+// the length before they count), so an append is one launch.
 template <int D>
 __global__ void __launch_bounds__(kKvThreads) kvq_append_kernel(const __grid_constant__ KvqProblem P) {
     const int b = blockIdx.y;
     const int T = P.seq_lens[b];
-    if (T >= P.max_seq) return;  // reported by kvq_bump_kernel
+    if (T >= P.max_seq) {   // cache full: nothing is written, the error flag reports it
+        if (blockIdx.x == 0 && threadIdx.x == 0) atomicExch(P.error_flag, 1);
+        return;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const int G = P.G, hd = P.head_dim;
     const int tasks = 2 * P.Hkv * G;
     const int task = blockIdx.x * nwarps + warp;
-    if (task >= tasks) return;
+    if (task < tasks) {
     const int which = task / (P.Hkv * G);
     const int rem = task - which * P.Hkv * G;
     const int h = rem / G, g = rem - h * G;
@@ -79,13 +83,15 @@ __global__ void __launch_bounds__(kKvThreads) kvq_append_kernel(const __grid_con
         uint8_t* codes = which ? P.v_codes : P.k_codes;
         codes[(((size_t)b * P.Hkv + h) * P.max_seq + T) * G + g] = (uint8_t)bi;
     }
-}
-
-__global__ void kvq_bump_kernel(int* seq_lens, int B, int max_seq, int* error_flag) {
-    const int b = blockIdx.x * blockDim.x + threadIdx.x;
-    if (b >= B) return;
-    if (seq_lens[b] >= max_seq) atomicExch(error_flag, 1);
-    else seq_lens[b] += 1;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(&P.append_done[b], 1) == (int)gridDim.x - 1) {
+            P.append_done[b] = 0;
+            P.seq_lens[b] = T + 1;
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------ kvq decode
@@ -165,6 +171,46 @@ __device__ __forceinline__ void st_heads(float* p, const float (&o)[R]) {
     }
 }
 
+// Every CTA of a (sequence, KV head) calls this once its partial is written (all threads of the CTA).
+// The CTA that arrives last merges the partials of the R query heads: M = max m_c, weights
+// exp(m_c - M), splits in index order -- so a decode is one launch.  The counter returns to zero.
+template <int R>
+__device__ __forceinline__ void kvq_merge_if_last(const KvqProblem& P, int b, int h) {
+    __shared__ int s_last;
+    __threadfence();   // this thread's partial is visible device-wide before the CTA is counted
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* cnt = P.split_done + (size_t)b * P.Hkv + h;
+        const int last = atomicAdd(cnt, 1) == P.n_chunks - 1;
+        if (last) *cnt = 0;
+        s_last = last;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const int hd = P.head_dim;
+    const float* base = P.partials + (((size_t)b * P.Hkv + h) * P.n_chunks) * R * (hd + 2);
+    for (int i = threadIdx.x; i < R * hd; i += blockDim.x) {
+        const int r = i / hd, col = i - r * hd;
+        float M = -INFINITY;
+        for (int c = 0; c < P.n_chunks; ++c) M = fmaxf(M, __ldcg(base + ((size_t)c * R + r) * (hd + 2)));
+        float L = 0.0f, o = 0.0f;
+        for (int c = 0; c < P.n_chunks; ++c) {
+            const float* p = base + ((size_t)c * R + r) * (hd + 2);
+            const float m = __ldcg(p);
+            if (m != -INFINITY) {
+                const float wgt = __expf(m - M);
+                L += __ldcg(p + 1) * wgt;
+                o = fmaf(__ldcg(p + 2 + col), wgt, o);
+            }
+        }
+        o *= L > 0.0f ? 1.0f / L : 0.0f;
+        const size_t oi = ((size_t)b * P.Hq + (size_t)h * R + r) * hd + col;
+        if (P.io_dtype == OJX_BF16) reinterpret_cast<__nv_bfloat16*>(P.out)[oi] = __float2bfloat16_rn(o);
+        else reinterpret_cast<float*>(P.out)[oi] = o;
+    }
+}
+
 template <int R, int D>
 __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel(const __grid_constant__ KvqProblem P) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -193,6 +239,7 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
     float* part = P.partials + ((((size_t)b * P.Hkv + h) * P.n_chunks + split) * R) * (hd + 2);
     if (t_begin >= t_end) {  // range beyond this sequence: neutral partial
         for (int i = tid; i < R * (hd + 2); i += kThreads) part[i] = (i % (hd + 2)) == 0 ? -INFINITY : 0.0f;
+        kvq_merge_if_last<R>(P, b, h);
         return;
     }
     const int n_passes = (t_end - t_begin + kSub - 1) / kSub;
@@ -520,32 +567,7 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
             part[(size_t)r * (hd + 2) + 1] = l;
         }
     }
-}
-
-// Merge the chunk partials of one (sequence, query head): M = max m_c, weights exp(m_c - M).
-__global__ void kvq_combine_kernel(const __grid_constant__ KvqProblem P, int R) {
-    const int b = blockIdx.y, qh = blockIdx.x, hd = P.head_dim;
-    const int h = qh / R, r = qh - h * R;
-    const float* base = P.partials + (((size_t)b * P.Hkv + h) * P.n_chunks) * R * (hd + 2);
-    float M = -INFINITY;
-    for (int c = 0; c < P.n_chunks; ++c) M = fmaxf(M, base[((size_t)c * R + r) * (hd + 2)]);
-    float L = 0.0f;
-    for (int c = 0; c < P.n_chunks; ++c) {
-        const float* p = base + ((size_t)c * R + r) * (hd + 2);
-        if (p[0] != -INFINITY) L += p[1] * __expf(p[0] - M);
-    }
-    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
-    for (int col = threadIdx.x; col < hd; col += blockDim.x) {
-        float o = 0.0f;
-        for (int c = 0; c < P.n_chunks; ++c) {
-            const float* p = base + ((size_t)c * R + r) * (hd + 2);
-            if (p[0] != -INFINITY) o = fmaf(p[2 + col], __expf(p[0] - M), o);
-        }
-        o *= inv;
-        const size_t oi = ((size_t)b * P.Hq + qh) * hd + col;
-        if (P.io_dtype == OJX_BF16) reinterpret_cast<__nv_bfloat16*>(P.out)[oi] = __float2bfloat16_rn(o);
-        else reinterpret_cast<float*>(P.out)[oi] = o;
-    }
+    kvq_merge_if_last<R>(P, b, h);
 }
 
 static size_t kvq_decode_smem_copies(const KvqProblem& P, int R, int copies) {
@@ -556,7 +578,7 @@ static size_t kvq_decode_smem_copies(const KvqProblem& P, int R, int copies) {
 }
 
 // Copies of the value codebook the decode kernel keeps in shared memory: 8 when that fits, else 1.
-int kvq_decode_v_copies(const KvqProblem& P, int R) { return kvq_decode_smem_copies(P, R, 8) <= 227 * 1024 ? 8 : 1; }
+int kvq_decode_v_copies(const KvqProblem& P, int R) { return kvq_decode_smem_copies(P, R, 8) + 64 <= 227 * 1024 ? 8 : 1; }
 
 size_t kvq_decode_smem(const KvqProblem& P, int R) { return kvq_decode_smem_copies(P, R, kvq_decode_v_copies(P, R)); }
 
@@ -587,9 +609,7 @@ static int launch_append_t(const KvqProblem& P, cudaStream_t s) {
     const int tasks = 2 * P.Hkv * P.G, wpb = kKvThreads / 32;
     kvq_append_kernel<D><<<dim3((tasks + wpb - 1) / wpb, P.B), kKvThreads, 0, s>>>(P);
     OJX_CUDA_TRY(cudaGetLastError());
-    kvq_bump_kernel<<<(P.B + 127) / 128, 128, 0, s>>>(P.seq_lens, P.B, P.max_seq, P.error_flag);
-    OJX_CUDA_TRY(cudaGetLastError());
-    count_launch(2);
+    count_launch(1);
     return OJX_OK;
 }
 
@@ -607,7 +627,7 @@ int launch_kvq_append(const KvqProblem& P, cudaStream_t s) {
 template <int R, int D>
 static int launch_decode_t(const KvqProblem& P, cudaStream_t s) {
     const size_t smem = kvq_decode_smem(P, R);
-    if (smem > 227 * 1024) return OJX_ERR_TOO_LARGE;
+    if (smem + 64 > 227 * 1024) return OJX_ERR_TOO_LARGE;   // 64: the kernel's few static bytes
     KvqProblem Q = P;
     Q.v_copies = kvq_decode_v_copies(P, R);
     static thread_local size_t configured = 0;  // largest opt-in made for this instantiation
@@ -617,9 +637,7 @@ static int launch_decode_t(const KvqProblem& P, cudaStream_t s) {
     }
     kvq_decode_kernel<R, D><<<dim3(P.n_chunks, P.Hkv, P.B), kvq_decode_threads(R, D), smem, s>>>(Q);
     OJX_CUDA_TRY(cudaGetLastError());
-    kvq_combine_kernel<<<dim3(P.Hq, P.B), 128, 0, s>>>(P, R);
-    OJX_CUDA_TRY(cudaGetLastError());
-    count_launch(2);
+    count_launch(1);
     return OJX_OK;
 }
 
