@@ -88,7 +88,7 @@ DeviceGuard::~DeviceGuard() { if (prev_ >= 0) cudaSetDevice(prev_); }
 LinearHandle::~LinearHandle() {
     DeviceGuard g(dev);
     cudaFree(codes); cudaFree(codebook); cudaFree(scales); cudaFree(bias);
-    cudaFree(row_ptrs); cudaFree(cols); cudaFree(vals); cudaFree(d_x); cudaFree(d_y);
+    cudaFree(row_ptrs); cudaFree(cols); cudaFree(vals); cudaFree(d_x); cudaFree(d_y); cudaFree(dq_scratch);
     if (pin_x) cudaFreeHost(pin_x);
     if (pin_y) cudaFreeHost(pin_y);
     if (stream) cudaStreamDestroy(stream);
@@ -175,7 +175,7 @@ int ojasx_b200_linear_forward(OjasxLinearHandle handle, const void* d_x, void* d
     // OJASX_B200_TENSOR_MIN_BATCH overrides the threshold (0 = never).
     if (io_dtype == OJX_BF16 && dequant_gemm_supported(P, h->csr_sorted)) {
         static const int min_batch = [] { const char* e = getenv("OJASX_B200_TENSOR_MIN_BATCH"); return e ? atoi(e) : kTensorMinBatch; }();
-        if (min_batch > 0 && batch_size >= min_batch) return launch_dequant_gemm(P, static_cast<cudaStream_t>(stream));
+        if (min_batch > 0 && batch_size >= min_batch) return launch_dequant_gemm(P, static_cast<cudaStream_t>(stream), &h->dq_scratch, &h->dq_scratch_cap);
     }
     return launch_linear(P, static_cast<cudaStream_t>(stream));
 }
@@ -229,7 +229,7 @@ int ojasx_b200_linear_forward_tensor(OjasxLinearHandle handle, const void* d_x, 
     if (batch_size <= 0 || row_start < 0 || row_stop > h->out || row_start >= row_stop) return OJX_ERR_ARG;
     LinearProblem P = h->problem(d_x, d_y, batch_size, OJX_BF16, row_start, row_stop);
     if (!dequant_gemm_supported(P, h->csr_sorted)) return OJX_ERR_UNSUPPORTED;
-    return launch_dequant_gemm(P, static_cast<cudaStream_t>(stream));
+    return launch_dequant_gemm(P, static_cast<cudaStream_t>(stream), &h->dq_scratch, &h->dq_scratch_cap);
 }
 
 int ojasx_b200_take_device_error(void) {

@@ -10,9 +10,16 @@
 // tcgen05.commit.  After the last K tile the producer warps become the epilogue: tcgen05.ld the
 // accumulator rows, scale, bias, store bf16.
 //
+// A layer has few 128-row tiles (54 for 6912 rows), so the K axis is split over up to four CTAs per
+// tile until the GPU is full: each writes its raw fp32 partial sums to scratch, and the CTA that
+// finishes last (an atomic count after a device-wide fence) adds the partials in split order and
+// applies scale and bias -- no CTA waits for another.
+//
 // This path trades the bit-exactness of the table kernels for throughput (weights are rounded to
 // bf16), so it is used only for bf16 I/O, inside the rel 2e-2 tolerance of the bf16 activation path.
 // Every wait on an mbarrier is bounded; on a timeout the kernel raises a flag that the host reads.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "launch.h"
 #include "handles.h"
@@ -93,6 +100,10 @@ struct DequantGemmProblem {
     int tmem_cols;              // power of two >= n_pad, >= 32
     int stages;                 // 3 or 4 stage buffers
     int csr_cap;                // outlier entries of the CTA's rows that fit in shared memory
+    int ksplit;                 // CTAs per tile along K (gridDim.z)
+    int tiles_per_split;        // K tiles per split (even, so that a split's code bytes start 16-byte aligned)
+    float* partial;             // ksplit > 1: [tile][split][n_pad][128] raw fp32 partial sums
+    int* tile_done;             // ksplit > 1: [tile] splits that have written their partial (returns to 0)
 };
 
 __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __grid_constant__ DequantGemmProblem P) {
@@ -115,7 +126,11 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
     const int b0 = blockIdx.y * 256;
     const int nb = min(256, P.batch - b0);
     const int rows_out = P.row_stop - P.row_start;
-    const int KT = P.K / kDqBlockK;
+    const int KT_all = P.K / kDqBlockK;
+    const int kt0 = blockIdx.z * P.tiles_per_split;                  // this CTA's K tiles: [kt0, kt0 + KT)
+    const int KT = min(P.tiles_per_split, KT_all - kt0);
+    const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+    const bool split = P.ksplit > 1;
 
     // codebook -> bf16, one 16-byte entry per centroid
     for (int c = tid; c < 256; c += kDqThreads) {
@@ -171,13 +186,13 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
         const int total_x = N * 8;
         unsigned char* my_codes = code_stage + tid * kDqCodeStride;           // [2][64 B] per thread
         auto issue_codes = [&](int blk) {   // K tiles [8*blk, 8*blk+8) -> buffer blk & 1
-            const int k0 = blk * 8;
+            const int k0 = blk * 8;   // local tile index
             if (k0 >= KT) return;
             unsigned char* dst = my_codes + (blk & 1) * 64;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int bytes = min(16, max(0, (KT - k0) * 8 - c * 16));
-                if (bytes > 0) cp_async16_zfill(dst + c * 16, crow + (size_t)k0 * 8 + c * 16, bytes);
+                if (bytes > 0) cp_async16_zfill(dst + c * 16, crow + (size_t)(kt0 + k0) * 8 + c * 16, bytes);
             }
         };
         auto issue_x = [&](int kt) {       // requires the stage of tile kt to be free
@@ -187,7 +202,7 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
                 const int r = i >> 3, c = i & 7;
                 const bool in = r < nb;
                 cp_async16_zfill(B + (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4),
-                                 P.x + (size_t)(b0 + (in ? r : 0)) * P.K + kt * kDqBlockK + c * 8, in ? 16 : 0);
+                                 P.x + (size_t)(b0 + (in ? r : 0)) * P.K + (kt0 + kt) * kDqBlockK + c * 8, in ? 16 : 0);
             }
         };
         issue_codes(0);
@@ -201,6 +216,10 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
             else { col_next = P.csr.cols[cur]; val_next = P.csr.vals[cur] * inv_scale; }
         };
         fetch_outlier();
+        while (col_next < kt0 * kDqBlockK) {   // outliers of the splits before this one
+            ++cur;
+            fetch_outlier();
+        }
         DQ_TICK_INIT;
         for (int kt = 0; kt < KT && ok; ++kt) {
             const int s = kt % S;
@@ -227,9 +246,9 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
 #pragma unroll
             for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(arow + (((half * 4 + q) ^ r7) << 4)) = wv[q];
             // CSR outliers of this row inside this thread's half of the tile (columns ascending): w += value / scale
-            const int kend = (kt + 1) * kDqBlockK;
+            const int kend = (kt0 + kt + 1) * kDqBlockK;
             while (col_next < kend) {
-                const int kk = col_next - kt * kDqBlockK;
+                const int kk = col_next - (kt0 + kt) * kDqBlockK;
                 if (kk >= 0 && (kk >> 5) == half) {
                     __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(arow + (((kk >> 3) ^ r7) << 4)) + (kk & 7);
                     *e = __float2bfloat16_rn(__bfloat162float(*e) + val_next);
@@ -258,7 +277,12 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
                     : "r"(taddr));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (row_ok) {
+                if (split) {   // raw partial sums, rows contiguous
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if (c0 + j < nb)
+                            P.partial[(((size_t)tile_id * P.ksplit + blockIdx.z) * N + c0 + j) * kDqBlockM + trow] = __uint_as_float(v[j]);
+                } else if (row_ok) {
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         const int b = c0 + j;
@@ -307,7 +331,51 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)P.tmem_cols) : "memory");
     }
+    if (split) {
+        __shared__ int s_last;
+        __threadfence();   // this thread's partial sums are visible device-wide before the CTA is counted
+        __syncthreads();
+        if (tid == 0) {
+            const int last = atomicAdd(P.tile_done + tile_id, 1) == P.ksplit - 1;
+            if (last) P.tile_done[tile_id] = 0;
+            s_last = last;
+        }
+        __syncthreads();
+        if (s_last && warp < kDqProducers / 32) {
+            __threadfence();
+            const int trow = tid & 127, half = tid >> 7, m = m0 + trow;
+            if (m < P.row_stop) {
+                const float sc = P.scales ? P.scales[m] : 1.0f, bi = P.bias ? P.bias[m] : 0.0f;
+                const int cbeg = half * (N >> 1), cstop = min(cbeg + (N >> 1), nb);
+                for (int bb = cbeg; bb < cstop; bb += 8) {   // eight columns at a time: all loads first
+                    float acc[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+                    for (int z = 0; z < P.ksplit; ++z) {   // split order: the result does not depend on which CTA came last
+                        float pv[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            pv[j] = bb + j < cstop ? __ldcg(P.partial + (((size_t)tile_id * P.ksplit + z) * N + bb + j) * kDqBlockM + trow) : 0.0f;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) acc[j] += pv[j];
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int b = bb + j;
+                        if (b >= cstop) break;
+                        float r = fmaf(acc[j], sc, bi);
+                        if (sc == 0.0f && P.csr.nnz > 0)  // a zero row scale cannot carry the folded outliers: add them here
+                            for (int q = P.csr.row_ptrs[m]; q < P.csr.row_ptrs[m + 1]; ++q)
+                                r += P.csr.vals[q] * __bfloat162float(P.x[(size_t)(b0 + b) * P.K + P.csr.cols[q]]);
+                        P.y[(size_t)(b0 + b) * rows_out + (m - P.row_start)] = __float2bfloat16_rn(r);
+                    }
+                }
+            }
+        }
+    }
 }
+
+constexpr size_t kDqSmemBudget = 226 * 1024;   // dynamic shared memory; the kernel also has a few static bytes
 
 size_t dequant_gemm_smem(int n_pad, int stages, int csr_cap) {
     return (size_t)stages * (kDqBlockM * 128 + (size_t)n_pad * 128) + 256 * 16 + (2 * kDqStages + 1) * 8 + 16 +
@@ -333,7 +401,19 @@ bool dequant_gemm_supported(const LinearProblem& P, bool csr_sorted) {
            (reinterpret_cast<uintptr_t>(P.x) & 15) == 0;
 }
 
-int launch_dequant_gemm(const LinearProblem& L, cudaStream_t stream) {
+// Splits along K for `ctas` (row tile, batch tile) pairs and KT tiles of 64 columns: fill the SMs, at most
+// four splits, at least eight tiles per split, an even number of tiles per split.
+static void plan_ksplit(int ctas, int KT, int sms, int* ksplit, int* per) {
+    int z = sms / (ctas > 0 ? ctas : 1);
+    z = z < 1 ? 1 : z > 4 ? 4 : z;
+    while (z > 1 && KT / z < 8) --z;
+    int p = (KT + z - 1) / z;
+    p += p & 1;
+    *per = z > 1 ? p : KT;
+    *ksplit = z > 1 ? (KT + p - 1) / p : 1;
+}
+
+int launch_dequant_gemm(const LinearProblem& L, cudaStream_t stream, void** scratch, size_t* scratch_cap) {
     DequantGemmProblem P{};
     int* error_flag = nullptr;
     OJX_CUDA_TRY(cudaGetSymbolAddress((void**)&error_flag, g_dq_error));
@@ -346,12 +426,12 @@ int launch_dequant_gemm(const LinearProblem& L, cudaStream_t stream) {
     int cols = 32;
     while (cols < P.n_pad) cols <<= 1;
     P.tmem_cols = cols;
-    P.stages = dequant_gemm_smem(P.n_pad, kDqStages, 4096) <= 227 * 1024 ? kDqStages : 3;
+    P.stages = dequant_gemm_smem(P.n_pad, kDqStages, 4096) <= kDqSmemBudget ? kDqStages : 3;
     // shared-memory room for the outliers of 128 rows: whatever is left, up to 8192 entries; the
     // kernel reads entries beyond that from global memory
     P.csr_cap = 0;
     if (L.csr.nnz > 0) {
-        const size_t left = 227 * 1024 - dequant_gemm_smem(P.n_pad, P.stages, 0);
+        const size_t left = kDqSmemBudget - dequant_gemm_smem(P.n_pad, P.stages, 0);
         P.csr_cap = (int)(left / 8 < 8192 ? left / 8 : 8192);
     }
     const size_t smem = dequant_gemm_smem(P.n_pad, P.stages, P.csr_cap);
@@ -361,7 +441,28 @@ int launch_dequant_gemm(const LinearProblem& L, cudaStream_t stream) {
         configured = smem;
     }
     const int rows = L.row_stop - L.row_start;
-    const dim3 grid((rows + kDqBlockM - 1) / kDqBlockM, (L.batch + 255) / 256);
+    dim3 grid((rows + kDqBlockM - 1) / kDqBlockM, (L.batch + 255) / 256, 1);
+    P.ksplit = 1;
+    P.tiles_per_split = L.K / kDqBlockK;
+    if (scratch && scratch_cap && !getenv("OJASX_B200_TENSOR_NO_KSPLIT")) {
+        int z = 1, per = P.tiles_per_split;
+        plan_ksplit((int)(grid.x * grid.y), L.K / kDqBlockK, num_sms(), &z, &per);
+        if (z > 1) {
+            // [tiles] counters (zeroed once; they return to zero) followed by the partial sums
+            const size_t tiles = (size_t)grid.x * grid.y, cnt_bytes = round_up((int)(tiles * sizeof(int)), 256);
+            const size_t need = cnt_bytes + sizeof(float) * tiles * z * P.n_pad * kDqBlockM;
+            if (*scratch_cap < need || !*scratch) {
+                int rc = ensure_capacity(scratch, scratch_cap, need);
+                if (rc != OJX_OK) return rc;
+                OJX_CUDA_TRY(cudaMemsetAsync(*scratch, 0, *scratch_cap, stream));
+            }
+            P.tile_done = static_cast<int*>(*scratch);
+            P.partial = reinterpret_cast<float*>(static_cast<char*>(*scratch) + cnt_bytes);
+            P.ksplit = z;
+            P.tiles_per_split = per;
+            grid.z = z;
+        }
+    }
     vq_dequant_gemm_kernel<<<grid, kDqThreads, smem, stream>>>(P);
     OJX_CUDA_TRY(cudaGetLastError());
     count_launch(1);

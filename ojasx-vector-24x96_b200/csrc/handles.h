@@ -43,6 +43,8 @@ struct LinearHandle {
     void* pin_y_dev = nullptr;     // device alias of pin_y (cached)
     void* pin_y_dev_of = nullptr;  // the pin_y it was taken from
     cudaStream_t stream = nullptr;
+    void* dq_scratch = nullptr;    // tensor-core path: tile counters and split-K partial sums
+    size_t dq_scratch_cap = 0;
 
     ~LinearHandle();
     LinearProblem problem(const void* x, void* y, int batch, int io_dtype, int row_start, int row_stop) const;

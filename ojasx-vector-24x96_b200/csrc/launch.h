@@ -24,7 +24,9 @@ int launch_rvq_generic(const uint8_t* packed, const float* codebooks, const floa
 
 // --- dequant_gemm.cu (tcgen05 path for bf16 batches)
 bool dequant_gemm_supported(const LinearProblem& P, bool csr_sorted);
-int launch_dequant_gemm(const LinearProblem& P, cudaStream_t stream);
+// scratch / scratch_cap: a grow-only device buffer of the caller (per layer handle) for the split-K partial
+// sums and tile counters; null = never split.  Calls that share the buffer must not overlap in time.
+int launch_dequant_gemm(const LinearProblem& P, cudaStream_t stream, void** scratch = nullptr, size_t* scratch_cap = nullptr);
 int take_dequant_gemm_error(int* out);
 
 // --- moe.cu
