@@ -18,6 +18,7 @@
 // This path trades the bit-exactness of the table kernels for throughput (weights are rounded to
 // bf16), so it is used only for bf16 I/O, inside the rel 2e-2 tolerance of the bf16 activation path.
 // Every wait on an mbarrier is bounded; on a timeout the kernel raises a flag that the host reads.
+#include <algorithm>
 #include <cstdlib>
 
 #include "common.cuh"
@@ -30,7 +31,7 @@ constexpr int kDqProducers = 256;    // 8 producer/epilogue warps: two threads p
 constexpr int kDqThreads = kDqProducers + 32;   // + 1 MMA warp
 constexpr int kDqBlockM = 128;
 constexpr int kDqBlockK = 64;        // bf16 elements per K tile = one 128-byte swizzle row
-constexpr int kDqStages = 4;        // most stages; wide batch tiles use 3 to fit shared memory
+constexpr int kDqStages = 8;        // most stage buffers; as many as fit next to the batch tile are used (3 at N = 256)
 constexpr int kDqSpin = 1 << 22;     // bounded mbarrier polling
 
 // Per-phase cycle counters for tuning; compiled out unless OJX_PHASE_TIMING is defined.
@@ -98,7 +99,8 @@ struct DequantGemmProblem {
     int K, G, row_start, row_stop, batch;
     int n_pad;                  // MMA N: batch tile rounded up to 16 (<= 256)
     int tmem_cols;              // power of two >= n_pad, >= 32
-    int stages;                 // 3 or 4 stage buffers
+    int stages;                 // stage buffers (3..8)
+    int prefetch;               // K tiles the X copies run ahead (1..6, < stages)
     int csr_cap;                // outlier entries of the CTA's rows that fit in shared memory
     int ksplit;                 // CTAs per tile along K (gridDim.z)
     int tiles_per_split;        // K tiles per split (even, so that a split's code bytes start 16-byte aligned)
@@ -182,7 +184,7 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
         //  * this thread's share of the X tile (N/32 chunks of 16 bytes) is copied straight into its
         //    swizzled place in the stage buffer two K tiles ahead of use;
         //  * the next outlier of the row is held in registers (outliers are staged in shared memory).
-        constexpr int kPF = 2;
+        const int kPF = P.prefetch;   // X copies run this many K tiles ahead of the tile being filled (<= stages - 1)
         const int total_x = N * 8;
         unsigned char* my_codes = code_stage + tid * kDqCodeStride;           // [2][64 B] per thread
         auto issue_codes = [&](int blk) {   // K tiles [8*blk, 8*blk+8) -> buffer blk & 1
@@ -231,7 +233,14 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
             issue_x(kn);
             if ((kt & 7) == 0) issue_codes((kt >> 3) + 1);   // next code block rides in this tile's group
             asm volatile("cp.async.commit_group;" ::: "memory");
-            asm volatile("cp.async.wait_group %0;" ::"n"(kPF) : "memory");   // copies of tile kt (and its code block) have landed
+            switch (kPF) {   // copies of tile kt (and its code block) have landed; wait_group takes an immediate
+                case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+                case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+                case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+                case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+                case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+                default: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+            }
             if (tid == 0) DQ_TICK(1);
             unsigned char* A = tiles + s * stage_bytes;
             const unsigned cw = *reinterpret_cast<const unsigned*>(my_codes + ((kt >> 3) & 1) * 64 + (kt & 7) * 8 + half * 4);
@@ -426,7 +435,10 @@ int launch_dequant_gemm(const LinearProblem& L, cudaStream_t stream, void** scra
     int cols = 32;
     while (cols < P.n_pad) cols <<= 1;
     P.tmem_cols = cols;
-    P.stages = dequant_gemm_smem(P.n_pad, kDqStages, 4096) <= kDqSmemBudget ? kDqStages : 3;
+    P.stages = 3;
+    while (P.stages < kDqStages && dequant_gemm_smem(P.n_pad, P.stages + 1, 4096) <= kDqSmemBudget) ++P.stages;
+    P.prefetch = P.stages - 2 < 1 ? 1 : P.stages - 2 > 6 ? 6 : P.stages - 2;
+    if (const char* e = getenv("OJASX_B200_TENSOR_PREFETCH")) P.prefetch = std::max(1, std::min(atoi(e), std::min(6, P.stages - 1)));
     // shared-memory room for the outliers of 128 rows: whatever is left, up to 8192 entries; the
     // kernel reads entries beyond that from global memory
     P.csr_cap = 0;
