@@ -1,11 +1,12 @@
 // Batched VQ linear on the 5th-generation tensor cores (tcgen05 + TMEM), for bf16 activations and
 // batches large enough that the operation is a dense contraction:
 //     Y[b, m] = scale[m] * sum_k X[b, k] * W[m, k] (+ bias[m]),   W[m, 8g + d] = codebook[code[m, g]][d] (+ outlier)
-// The weights are never materialised in global memory: per 128-row x 64-column tile the four
-// producer warps turn code bytes into bf16 (one 16-byte shared-memory gather from a bf16 copy of
-// the codebook per code byte), add the row's CSR outliers that fall in the tile, and store the
+// The weights are never materialised in global memory: per 128-row x 64-column tile a group of
+// two producer warps turns code bytes into bf16 (one 16-byte shared-memory gather from a bf16 copy
+// of the codebook per code byte), adds the rows' CSR outliers that fall in the tile, and stores the
 // tile in the 128-byte-swizzled K-major layout that tcgen05.mma reads; the same threads stage the
-// matching X tile.  One thread of a fifth warp issues the MMAs (M = 128, N = padded batch, K = 16
+// matching X tile.  Four such groups work on four consecutive K tiles at the same time, so the
+// latencies of one tile's hand-over overlap with the others.  One thread of a ninth warp issues the MMAs (M = 128, N = padded batch, K = 16
 // per instruction, fp32 accumulation in tensor memory) and signals stage reuse with
 // tcgen05.commit.  After the last K tile the producer warps become the epilogue: tcgen05.ld the
 // accumulator rows, scale, bias, store bf16.
@@ -27,7 +28,9 @@
 
 namespace ojx {
 
-constexpr int kDqProducers = 256;    // 8 producer/epilogue warps: two threads per tile row, four code bytes each
+constexpr int kDqProducers = 256;    // 8 producer/epilogue warps
+constexpr int kDqGroups = 4;         // producer groups; each builds every fourth K tile
+constexpr int kDqGroupThreads = kDqProducers / kDqGroups;
 constexpr int kDqThreads = kDqProducers + 32;   // + 1 MMA warp
 constexpr int kDqBlockM = 128;
 constexpr int kDqBlockK = 64;        // bf16 elements per K tile = one 128-byte swizzle row
@@ -39,12 +42,16 @@ constexpr int kDqSpin = 1 << 22;     // bounded mbarrier polling
 __device__ unsigned long long g_dq_phase[16];
 #define DQ_TICK(i) do { if (blockIdx.x == 0 && blockIdx.y == 0) { long long n_ = clock64(); atomicAdd(&g_dq_phase[i], (unsigned long long)(n_ - t_)); t_ = n_; } } while (0)
 #define DQ_TICK_INIT long long t_ = clock64()
+// absolute time since kernel start, thread 0 of CTA (0,0,0)
+#define DQ_MARK_INIT const long long t0_ = clock64()
+#define DQ_MARK(i) do { if (threadIdx.x == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) atomicAdd(&g_dq_phase[i], (unsigned long long)(clock64() - t0_)); } while (0)
 #else
+#define DQ_MARK_INIT do { } while (0)
+#define DQ_MARK(i) do { } while (0)
 #define DQ_TICK(i) do { } while (0)
 #define DQ_TICK_INIT do { } while (0)
 #endif
 
-constexpr int kDqCodeStride = 144;   // bytes between the code slots of neighbouring threads (2 x 64 + 16: fewer bank conflicts)
 
 __device__ __forceinline__ void cp_async16_zfill(void* smem_dst, const void* gsrc, int src_bytes) {
     unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
@@ -100,7 +107,6 @@ struct DequantGemmProblem {
     int n_pad;                  // MMA N: batch tile rounded up to 16 (<= 256)
     int tmem_cols;              // power of two >= n_pad, >= 32
     int stages;                 // stage buffers (3..8)
-    int prefetch;               // K tiles the X copies run ahead (1..6, < stages)
     int csr_cap;                // outlier entries of the CTA's rows that fit in shared memory
     int ksplit;                 // CTAs per tile along K (gridDim.z)
     int tiles_per_split;        // K tiles per split (even, so that a split's code bytes start 16-byte aligned)
@@ -110,6 +116,7 @@ struct DequantGemmProblem {
 
 __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __grid_constant__ DequantGemmProblem P) {
     extern __shared__ unsigned char dq_smem_raw[];
+    DQ_MARK_INIT;
     // swizzled tiles need 1024-byte alignment; the dynamic segment only promises 16
     unsigned char* dq_smem = dq_smem_raw + ((1024u - (smem_u32(dq_smem_raw) & 1023u)) & 1023u);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -118,8 +125,7 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
     const int a_bytes = kDqBlockM * 128, b_bytes = N * 128, stage_bytes = a_bytes + b_bytes;
     unsigned char* tiles = dq_smem;                                   // [stages][A | B], 1024-byte aligned
     uint4* cb16 = reinterpret_cast<uint4*>(tiles + S * stage_bytes);   // [256] centroids as 8 bf16
-    unsigned char* code_stage = reinterpret_cast<unsigned char*>(cb16 + 256);   // [256 threads][kDqCodeStride], 16-byte aligned
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(code_stage + kDqProducers * kDqCodeStride);
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(cb16 + 256);
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * kDqStages + 1);
     int2* csr_s = reinterpret_cast<int2*>(tmem_slot + 2);                     // [csr_cap] (col, value bits), 8-byte aligned
     const unsigned full0 = smem_u32(bars), empty0 = full0 + 8 * kDqStages, accum = empty0 + 8 * kDqStages;
@@ -150,7 +156,7 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
             csr_s[i] = make_int2(P.csr.cols[csr_base + i], __float_as_int(P.csr.vals[csr_base + i]));
     }
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) { mbar_init(full0 + 8 * s, kDqProducers); mbar_init(empty0 + 8 * s, 1); }
+        for (int s = 0; s < S; ++s) { mbar_init(full0 + 8 * s, kDqGroupThreads); mbar_init(empty0 + 8 * s, 1); }
         mbar_init(accum, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -163,116 +169,113 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem_base = *tmem_slot;
     bool ok = true;
+    DQ_MARK(10);
 
     if (warp < kDqProducers / 32) {
-        // ---------------- producers: tile row = tid & 127, this thread owns code bytes [4*half, 4*half+4) of each K tile
-        const int trow = tid & 127, half = tid >> 7;
-        const int m = m0 + trow;
-        const bool row_ok = m < P.row_stop;
-        const uint8_t* crow = P.codes + (size_t)(row_ok ? m : P.row_start) * P.G;
-        int cur = 0, cend = 0;
-        if (row_ok && P.csr.nnz > 0) { cur = P.csr.row_ptrs[m]; cend = P.csr.row_ptrs[m + 1]; }
-        // The reference adds the outlier row sum AFTER the row scale (ojasx_lut_cpu.cpp:178-182, 127), so an
-        // outlier folded into the weight tile is pre-divided by the scale that the epilogue applies.
-        const float row_scale = (row_ok && P.scales) ? P.scales[m] : 1.0f;
-        const float inv_scale = row_scale != 0.0f ? 1.0f / row_scale : 0.0f;
-        const int csr_begin = cur;
-        const int r7 = trow & 7;
-        // Global-memory latency is kept off the per-tile critical path by asynchronous copies:
-        //  * the row's code bytes arrive in blocks of 8 K tiles (64 bytes) into a private,
-        //    double-buffered slot of shared memory, one block ahead of use;
-        //  * this thread's share of the X tile (N/32 chunks of 16 bytes) is copied straight into its
-        //    swizzled place in the stage buffer two K tiles ahead of use;
-        //  * the next outlier of the row is held in registers (outliers are staged in shared memory).
-        const int kPF = P.prefetch;   // X copies run this many K tiles ahead of the tile being filled (<= stages - 1)
+        // ---------------- producers: kDqGroups groups of 64 threads; group q builds K tiles q, q + 4, ... on its
+        // own, so four tiles are in production at any time and the round trips of one tile (stage free ->
+        // copies -> gathers -> arrival -> MMA) overlap with those of the others.  Thread t of a group owns
+        // tile rows t and t + 64 (all eight code bytes of the tile each).
+        const int gq = tid / kDqGroupThreads, gt = tid - gq * kDqGroupThreads;
         const int total_x = N * 8;
-        unsigned char* my_codes = code_stage + tid * kDqCodeStride;           // [2][64 B] per thread
-        auto issue_codes = [&](int blk) {   // K tiles [8*blk, 8*blk+8) -> buffer blk & 1
-            const int k0 = blk * 8;   // local tile index
-            if (k0 >= KT) return;
-            unsigned char* dst = my_codes + (blk & 1) * 64;
+        int rm[2], cur[2], cend[2], col_next[2];
+        float inv_scale[2], val_next[2];
+        bool rok[2];
+        const uint8_t* crow[2];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int bytes = min(16, max(0, (KT - k0) * 8 - c * 16));
-                if (bytes > 0) cp_async16_zfill(dst + c * 16, crow + (size_t)(kt0 + k0) * 8 + c * 16, bytes);
-            }
+        for (int u = 0; u < 2; ++u) {
+            rm[u] = m0 + gt + u * kDqGroupThreads;
+            rok[u] = rm[u] < P.row_stop;
+            crow[u] = P.codes + (size_t)(rok[u] ? rm[u] : P.row_start) * P.G;
+            cur[u] = cend[u] = 0;
+            if (rok[u] && P.csr.nnz > 0) { cur[u] = P.csr.row_ptrs[rm[u]]; cend[u] = P.csr.row_ptrs[rm[u] + 1]; }
+            // The reference adds the outlier row sum AFTER the row scale (ojasx_lut_cpu.cpp:178-182, 127), so an
+            // outlier folded into the weight tile is pre-divided by the scale that the epilogue applies.
+            const float sc = (rok[u] && P.scales) ? P.scales[rm[u]] : 1.0f;
+            inv_scale[u] = sc != 0.0f ? 1.0f / sc : 0.0f;
+            col_next[u] = 0x7fffffff;
+            val_next[u] = 0.0f;
+        }
+        auto fetch_outlier = [&](int u) {   // entry cur[u] of row u: from shared memory when it was staged
+            if (cur[u] >= cend[u]) { col_next[u] = 0x7fffffff; return; }
+            const int i = cur[u] - csr_base;
+            if (i < csr_staged) { const int2 e = csr_s[i]; col_next[u] = e.x; val_next[u] = __int_as_float(e.y) * inv_scale[u]; }
+            else { col_next[u] = P.csr.cols[cur[u]]; val_next[u] = P.csr.vals[cur[u]] * inv_scale[u]; }
         };
-        auto issue_x = [&](int kt) {       // requires the stage of tile kt to be free
-            if (kt >= KT) return;
-            unsigned char* B = tiles + (kt % S) * stage_bytes + a_bytes;
-            for (int i = tid; i < total_x; i += kDqProducers) {
+        fetch_outlier(0);
+        fetch_outlier(1);
+        auto load_codes = [&](int kt, uint2 (&c)[2]) {   // the eight code bytes of both rows for K tile kt (8-byte aligned)
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+                c[u] = kt < KT ? *reinterpret_cast<const uint2*>(crow[u] + (size_t)(kt0 + kt) * 8) : make_uint2(0u, 0u);
+        };
+        uint2 codes_now[2], codes_next[2];
+        load_codes(gq, codes_now);
+        DQ_TICK_INIT;
+        for (int kt = gq; kt < KT && ok; kt += kDqGroups) {
+            const int s = kt % S;
+            load_codes(kt + kDqGroups, codes_next);   // in flight while this tile is built
+            // the MMAs that read this stage's previous contents must be done
+            if (kt >= S) ok = mbar_wait(empty0 + 8 * s, ((kt / S) - 1) & 1);
+            if (!ok) break;
+            if (tid == 0) DQ_TICK(0);
+            unsigned char* A = tiles + s * stage_bytes;
+            unsigned char* B = A + a_bytes;
+            for (int i = gt; i < total_x; i += kDqGroupThreads) {   // X tile: 16-byte chunks straight into their swizzled place
                 const int r = i >> 3, c = i & 7;
                 const bool in = r < nb;
                 cp_async16_zfill(B + (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4),
                                  P.x + (size_t)(b0 + (in ? r : 0)) * P.K + (kt0 + kt) * kDqBlockK + c * 8, in ? 16 : 0);
             }
-        };
-        issue_codes(0);
-        for (int t = 0; t < kPF; ++t) { issue_x(t); asm volatile("cp.async.commit_group;" ::: "memory"); }
-        int col_next = 0x7fffffff;
-        float val_next = 0.0f;
-        auto fetch_outlier = [&]() {   // entry `cur` of this row: from shared memory when it was staged
-            if (cur >= cend) { col_next = 0x7fffffff; return; }
-            const int i = cur - csr_base;
-            if (i < csr_staged) { const int2 e = csr_s[i]; col_next = e.x; val_next = __int_as_float(e.y) * inv_scale; }
-            else { col_next = P.csr.cols[cur]; val_next = P.csr.vals[cur] * inv_scale; }
-        };
-        fetch_outlier();
-        while (col_next < kt0 * kDqBlockK) {   // outliers of the splits before this one
-            ++cur;
-            fetch_outlier();
-        }
-        DQ_TICK_INIT;
-        for (int kt = 0; kt < KT && ok; ++kt) {
-            const int s = kt % S;
-            // stage of tile kt+kPF: wait until the MMAs that read its previous contents are done, then start its X copy
-            const int kn = kt + kPF;
-            if (kn < KT && kn >= S) ok = mbar_wait(empty0 + 8 * (kn % S), ((kn / S) - 1) & 1);
-            if (!ok) break;
-            if (tid == 0) DQ_TICK(0);
-            issue_x(kn);
-            if ((kt & 7) == 0) issue_codes((kt >> 3) + 1);   // next code block rides in this tile's group
             asm volatile("cp.async.commit_group;" ::: "memory");
-            switch (kPF) {   // copies of tile kt (and its code block) have landed; wait_group takes an immediate
-                case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
-                case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
-                case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
-                case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
-                case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
-                default: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
-            }
-            if (tid == 0) DQ_TICK(1);
-            unsigned char* A = tiles + s * stage_bytes;
-            const unsigned cw = *reinterpret_cast<const unsigned*>(my_codes + ((kt >> 3) & 1) * 64 + (kt & 7) * 8 + half * 4);
-            // A: four codes of this row -> four 16-byte chunks, chunk index XOR (row % 8)
-            unsigned char* arow = A + (trow >> 3) * 1024 + r7 * 128;
-            uint4 wv[4];   // all gathers first, then the stores (the compiler cannot reorder them itself)
+            const int kbeg = (kt0 + kt) * kDqBlockK, kend = kbeg + kDqBlockK;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const unsigned code = (cw >> (q * 8)) & 0xffu;
-                wv[q] = row_ok ? cb16[code] : make_uint4(0, 0, 0, 0);
-            }
+            for (int u = 0; u < 2; ++u) {
+                // A: eight codes of the row -> eight 16-byte chunks, chunk index XOR (row % 8)
+                const int trow = gt + u * kDqGroupThreads, r7 = trow & 7;
+                unsigned char* arow = A + (trow >> 3) * 1024 + r7 * 128;
+                const unsigned cw[2] = {codes_now[u].x, codes_now[u].y};
+                uint4 wv[8];   // all gathers first, then the stores
 #pragma unroll
-            for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(arow + (((half * 4 + q) ^ r7) << 4)) = wv[q];
-            // CSR outliers of this row inside this thread's half of the tile (columns ascending): w += value / scale
-            const int kend = (kt0 + kt + 1) * kDqBlockK;
-            while (col_next < kend) {
-                const int kk = col_next - (kt0 + kt) * kDqBlockK;
-                if (kk >= 0 && (kk >> 5) == half) {
-                    __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(arow + (((kk >> 3) ^ r7) << 4)) + (kk & 7);
-                    *e = __float2bfloat16_rn(__bfloat162float(*e) + val_next);
+                for (int q = 0; q < 8; ++q) {
+                    const unsigned code = (cw[q >> 2] >> ((q & 3) * 8)) & 0xffu;
+                    wv[q] = rok[u] ? cb16[code] : make_uint4(0, 0, 0, 0);
                 }
-                ++cur;
-                fetch_outlier();
+#pragma unroll
+                for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(arow + ((q ^ r7) << 4)) = wv[q];
+                // CSR outliers of the row inside this tile (columns ascending): w += value / scale; entries of the
+                // tiles that other groups build are passed over
+                while (col_next[u] < kend) {
+                    const int kk = col_next[u] - kbeg;
+                    if (kk >= 0) {
+                        __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(arow + (((kk >> 3) ^ r7) << 4)) + (kk & 7);
+                        *e = __float2bfloat16_rn(__bfloat162float(*e) + val_next[u]);
+                    }
+                    ++cur[u];
+                    fetch_outlier(u);
+                }
             }
             if (tid == 0) DQ_TICK(2);
+            asm volatile("cp.async.wait_group 0;" ::: "memory");   // this thread's share of the X tile has landed
+            if (tid == 0) DQ_TICK(1);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic and cp.async stores -> visible to the tensor core
             mbar_arrive(full0 + 8 * s);
             if (tid == 0) DQ_TICK(3);
+            codes_now[0] = codes_next[0];
+            codes_now[1] = codes_next[1];
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
+        DQ_MARK(11);
+        // the epilogue and the split reduction address rows as (tid & 127, tid >> 7)
+        const int trow = tid & 127, half = tid >> 7;
+        const int m = m0 + trow;
+        const bool row_ok = m < P.row_stop;
+        const float row_scale = (row_ok && P.scales) ? P.scales[m] : 1.0f;
+        int csr_begin = 0, cend_row = 0;
+        if (row_ok && P.csr.nnz > 0) { csr_begin = P.csr.row_ptrs[m]; cend_row = P.csr.row_ptrs[m + 1]; }
         // ---------------- epilogue: accumulator row trow; the two threads of a row split the batch columns
         if (ok) ok = mbar_wait(accum, 0);
+        DQ_MARK(12);
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float sc = row_scale;
@@ -298,7 +301,7 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
                         if (b < nb) {
                             float r = fmaf(__uint_as_float(v[j]), sc, bi);
                             if (sc == 0.0f)  // a zero row scale cannot carry the folded outliers: add them here
-                                for (int q = csr_begin; q < cend; ++q)
+                                for (int q = csr_begin; q < cend_row; ++q)
                                     r += P.csr.vals[q] * __bfloat162float(P.x[(size_t)(b0 + b) * P.K + P.csr.cols[q]]);
                             P.y[(size_t)(b0 + b) * rows_out + (m - P.row_start)] = __float2bfloat16_rn(r);
                         }
@@ -333,6 +336,7 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
         }
         if (ok) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(accum) : "memory");
     }
+    DQ_MARK(13);
     if (!ok && P.error_flag) atomicExch(P.error_flag, 1);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -382,13 +386,14 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
             }
         }
     }
+    DQ_MARK(14);
 }
 
 constexpr size_t kDqSmemBudget = 226 * 1024;   // dynamic shared memory; the kernel also has a few static bytes
 
 size_t dequant_gemm_smem(int n_pad, int stages, int csr_cap) {
     return (size_t)stages * (kDqBlockM * 128 + (size_t)n_pad * 128) + 256 * 16 + (2 * kDqStages + 1) * 8 + 16 +
-           kDqProducers * kDqCodeStride + (size_t)csr_cap * 8 + 1024;
+           (size_t)csr_cap * 8 + 1024;
 }
 
 static __device__ int g_dq_error;  // raised when a bounded wait inside the kernel ran out
@@ -435,10 +440,13 @@ int launch_dequant_gemm(const LinearProblem& L, cudaStream_t stream, void** scra
     int cols = 32;
     while (cols < P.n_pad) cols <<= 1;
     P.tmem_cols = cols;
-    P.stages = 3;
+    // Stage buffers: at least one per producer group.  (A group waits on a stage's "empty" barrier by phase
+    // parity; with fewer stages than groups a group could be two phases ahead of a stage it shares with
+    // another group, and a parity wait cannot tell "two ahead" from "done".)  More stages when the batch
+    // tile is narrow; room for at least 1024 staged outlier entries is kept.
+    P.stages = kDqGroups;
+    if (dequant_gemm_smem(P.n_pad, P.stages, 1024) > kDqSmemBudget) return OJX_ERR_UNSUPPORTED;
     while (P.stages < kDqStages && dequant_gemm_smem(P.n_pad, P.stages + 1, 4096) <= kDqSmemBudget) ++P.stages;
-    P.prefetch = P.stages - 2 < 1 ? 1 : P.stages - 2 > 6 ? 6 : P.stages - 2;
-    if (const char* e = getenv("OJASX_B200_TENSOR_PREFETCH")) P.prefetch = std::max(1, std::min(atoi(e), std::min(6, P.stages - 1)));
     // shared-memory room for the outliers of 128 rows: whatever is left, up to 8192 entries; the
     // kernel reads entries beyond that from global memory
     P.csr_cap = 0;
