@@ -31,6 +31,7 @@ namespace ojx {
 constexpr int kDqProducers = 256;    // 8 producer/epilogue warps
 constexpr int kDqGroups = 4;         // producer groups; each builds every fourth K tile
 constexpr int kDqGroupThreads = kDqProducers / kDqGroups;
+constexpr int kDqMaxTiles = 254;     // K tiles of one CTA whose outliers can be listed per tile (else rows are walked)
 constexpr int kDqThreads = kDqProducers + 32;   // + 1 MMA warp
 constexpr int kDqBlockM = 128;
 constexpr int kDqBlockK = 64;        // bf16 elements per K tile = one 128-byte swizzle row
@@ -127,7 +128,10 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
     uint4* cb16 = reinterpret_cast<uint4*>(tiles + S * stage_bytes);   // [256] centroids as 8 bf16
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(cb16 + 256);
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * kDqStages + 1);
-    int2* csr_s = reinterpret_cast<int2*>(tmem_slot + 2);                     // [csr_cap] (col, value bits), 8-byte aligned
+    int* rp_s = reinterpret_cast<int*>(tmem_slot + 2);                        // [129] row pointers of the CTA's rows
+    int* tstart = rp_s + 130;                                                 // [kDqMaxTiles + 1] first entry of each K tile's outlier list
+    int* tfill = tstart + kDqMaxTiles + 2;                                    // [kDqMaxTiles + 1] fill cursors
+    int2* csr_s = reinterpret_cast<int2*>(tfill + kDqMaxTiles + 2);           // [csr_cap], 8-byte aligned
     const unsigned full0 = smem_u32(bars), empty0 = full0 + 8 * kDqStages, accum = empty0 + 8 * kDqStages;
 
     const int m0 = P.row_start + blockIdx.x * kDqBlockM;
@@ -147,13 +151,53 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
         for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(P.codebook[c * 8 + 2 * q], P.codebook[c * 8 + 2 * q + 1]);
         cb16[c] = *reinterpret_cast<uint4*>(h);
     }
-    // outliers of this CTA's rows: one contiguous CSR range, copied once with coalesced loads
+    // Outliers of this CTA's rows and K range.  Normally they are listed per K tile in shared memory
+    // (counting sort: count, prefix, scatter; entry = row << 8 | column in tile, value / row scale), so
+    // that the group that builds a tile applies that tile's ~30 entries with one thread each.  If the
+    // lists would not fit, the row-ordered entries are staged instead and every thread walks its rows.
     int csr_base = 0, csr_staged = 0;
+    bool listed = false;
     if (P.csr.nnz > 0 && m0 < P.row_stop) {
-        csr_base = P.csr.row_ptrs[m0];
-        csr_staged = min(P.csr_cap, P.csr.row_ptrs[min(m0 + kDqBlockM, P.row_stop)] - csr_base);
-        for (int i = tid; i < csr_staged; i += kDqThreads)
-            csr_s[i] = make_int2(P.csr.cols[csr_base + i], __float_as_int(P.csr.vals[csr_base + i]));
+        const int n_rows = min(kDqBlockM, P.row_stop - m0);
+        for (int i = tid; i <= n_rows; i += kDqThreads) rp_s[i] = P.csr.row_ptrs[m0 + i];
+        for (int i = tid; i <= kDqMaxTiles + 1; i += kDqThreads) tstart[i] = 0;
+        __syncthreads();
+        csr_base = rp_s[0];
+        const int total = rp_s[n_rows] - csr_base;
+        if (KT <= kDqMaxTiles) {
+            for (int j = tid; j < total; j += kDqThreads) {
+                const int t = P.csr.cols[csr_base + j] / kDqBlockK - kt0;
+                if (t >= 0 && t < KT) atomicAdd(&tstart[t + 1], 1);
+            }
+            __syncthreads();
+            if (tid == 0) {
+                int run = 0;
+                for (int t = 0; t <= KT; ++t) { run += tstart[t]; tstart[t] = run; tfill[t] = run; }
+            }
+            __syncthreads();
+            listed = tstart[KT] <= P.csr_cap;
+        }
+        if (listed) {
+            for (int j = tid; j < total; j += kDqThreads) {
+                const int col = P.csr.cols[csr_base + j];
+                const int t = col / kDqBlockK - kt0;
+                if (t < 0 || t >= KT) continue;
+                int lo = 0, hi = n_rows;   // row of entry csr_base + j: last row whose pointer is <= it
+                while (hi - lo > 1) {
+                    const int mid = (lo + hi) >> 1;
+                    if (rp_s[mid] <= csr_base + j) lo = mid; else hi = mid;
+                }
+                // The reference adds the outlier row sum AFTER the row scale (ojasx_lut_cpu.cpp:178-182, 127), so an
+                // outlier folded into the weight tile is pre-divided by the scale that the epilogue applies.
+                const float sc = P.scales ? P.scales[m0 + lo] : 1.0f;
+                const float v = sc != 0.0f ? P.csr.vals[csr_base + j] / sc : 0.0f;
+                csr_s[atomicAdd(&tfill[t], 1)] = make_int2((lo << 8) | (col & (kDqBlockK - 1)), __float_as_int(v));
+            }
+        } else {
+            csr_staged = min(P.csr_cap, total);
+            for (int i = tid; i < csr_staged; i += kDqThreads)
+                csr_s[i] = make_int2(P.csr.cols[csr_base + i], __float_as_int(P.csr.vals[csr_base + i]));
+        }
     }
     if (tid == 0) {
         for (int s = 0; s < S; ++s) { mbar_init(full0 + 8 * s, kDqGroupThreads); mbar_init(empty0 + 8 * s, 1); }
@@ -202,8 +246,12 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
             if (i < csr_staged) { const int2 e = csr_s[i]; col_next[u] = e.x; val_next[u] = __int_as_float(e.y) * inv_scale[u]; }
             else { col_next[u] = P.csr.cols[cur[u]]; val_next[u] = P.csr.vals[cur[u]] * inv_scale[u]; }
         };
-        fetch_outlier(0);
-        fetch_outlier(1);
+        if (!listed) {
+            fetch_outlier(0);
+            fetch_outlier(1);
+            while (col_next[0] < kt0 * kDqBlockK) { ++cur[0]; fetch_outlier(0); }   // outliers of the splits before this one
+            while (col_next[1] < kt0 * kDqBlockK) { ++cur[1]; fetch_outlier(1); }
+        }
         auto load_codes = [&](int kt, uint2 (&c)[2]) {   // the eight code bytes of both rows for K tile kt (8-byte aligned)
 #pragma unroll
             for (int u = 0; u < 2; ++u)
@@ -243,9 +291,9 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
                 }
 #pragma unroll
                 for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(arow + ((q ^ r7) << 4)) = wv[q];
-                // CSR outliers of the row inside this tile (columns ascending): w += value / scale; entries of the
-                // tiles that other groups build are passed over
-                while (col_next[u] < kend) {
+                // row-walk fallback: CSR outliers of the row inside this tile (columns ascending): w += value / scale;
+                // entries of the tiles that other groups build are passed over
+                while (!listed && col_next[u] < kend) {
                     const int kk = col_next[u] - kbeg;
                     if (kk >= 0) {
                         __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(arow + (((kk >> 3) ^ r7) << 4)) + (kk & 7);
@@ -253,6 +301,15 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
                     }
                     ++cur[u];
                     fetch_outlier(u);
+                }
+            }
+            if (listed && tstart[kt + 1] > tstart[kt]) {   // uniform over the group
+                asm volatile("bar.sync %0, %1;" ::"r"(1 + gq), "n"(kDqGroupThreads) : "memory");   // the group's rows are stored
+                for (int i = tstart[kt] + gt; i < tstart[kt + 1]; i += kDqGroupThreads) {
+                    const int2 e = csr_s[i];
+                    const int row = e.x >> 8, kk = e.x & (kDqBlockK - 1), r7 = row & 7;
+                    __nv_bfloat16* w = reinterpret_cast<__nv_bfloat16*>(A + (row >> 3) * 1024 + r7 * 128 + (((kk >> 3) ^ r7) << 4)) + (kk & 7);
+                    *w = __float2bfloat16_rn(__bfloat162float(*w) + __int_as_float(e.y));
                 }
             }
             if (tid == 0) DQ_TICK(2);
@@ -393,7 +450,7 @@ constexpr size_t kDqSmemBudget = 226 * 1024;   // dynamic shared memory; the ker
 
 size_t dequant_gemm_smem(int n_pad, int stages, int csr_cap) {
     return (size_t)stages * (kDqBlockM * 128 + (size_t)n_pad * 128) + 256 * 16 + (2 * kDqStages + 1) * 8 + 16 +
-           (size_t)csr_cap * 8 + 1024;
+           sizeof(int) * (130 + 2 * (kDqMaxTiles + 2)) + (size_t)csr_cap * 8 + 1024;
 }
 
 static __device__ int g_dq_error;  // raised when a bounded wait inside the kernel ran out

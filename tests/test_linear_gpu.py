@@ -149,3 +149,18 @@ def test_tensor_core_dequant_gemm_bf16(cuda, oracle, K, M, batch):
     if batch >= 32:
         auto = layer(torch.from_numpy(xb).to(cuda).bfloat16()).float().cpu().numpy()
         assert np.array_equal(auto, got)
+
+
+@pytest.mark.parametrize("frac", [0.0, 0.08])
+def test_tensor_core_outlier_paths(cuda, oracle, frac):
+    """No outliers at all, and so many (8 % of the cells) that a row tile's per-K-tile lists do not fit in
+    shared memory and the kernel walks the rows instead."""
+    K, M, batch = 2560, 300, 40
+    w = synth.make_vq_linear(77, K, M, block_dim=8, outlier_frac=frac, with_scales=True, with_bias=True)
+    xb = synth.to_bf16_f32(np.random.default_rng(3).standard_normal((batch, K)).astype(np.float32))
+    want = oracle.linear_forward(w.codebook, w.codes, w.scales, w.bias, w.csr, xb, block_dim=8)
+    got = ops.VQLinear.from_weights(w).forward_tensor(torch.from_numpy(xb).to(cuda).bfloat16()).float().cpu().numpy()
+    assert ojasx_b200.lib().ojasx_b200_take_device_error() == 0
+    err = np.abs(got - want)
+    assert np.all(err <= 2e-2 * np.abs(want) + 3e-2 * (1 + 20 * frac)), (err.max(), np.abs(want).max())
+
