@@ -7,7 +7,7 @@ tooling and is not part of this package.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, Tuple
+from typing import Dict, Optional, Tuple
 
 import torch
 
@@ -64,6 +64,10 @@ class QuantizedWeight:
     codebooks: torch.Tensor
     row_scales: torch.Tensor
     metrics: Dict[str, object] = field(default_factory=dict)
+    # CSR outliers added after the row scale, as SplitManifoldLinear does (ojasx_lut.h:66-71):
+    # (row_ptrs i32[M+1], col_indices i32[nnz], values f32[nnz]) on the tensors' device.  The reference
+    # container has no such field; it is carried for the 8-bit single-stage layout only.
+    outliers: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None
 
     def __post_init__(self) -> None:
         if len(self.original_shape) != 2:
@@ -109,8 +113,9 @@ class QuantizedWeight:
         return unpack_codes(self.packed_codes[stage], self.bits_per_stage, self.vector_count)
 
     def to(self, device) -> "QuantizedWeight":
+        outliers = None if self.outliers is None else tuple(t.to(device) for t in self.outliers)
         return QuantizedWeight(self.original_shape, self.block_size, self.bits_per_stage, self.packed_codes.to(device),
-                               self.codebooks.to(device), self.row_scales.to(device), dict(self.metrics))
+                               self.codebooks.to(device), self.row_scales.to(device), dict(self.metrics), outliers=outliers)
 
 
 def dequantize_weight(encoded: QuantizedWeight) -> torch.Tensor:

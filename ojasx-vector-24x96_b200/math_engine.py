@@ -37,13 +37,19 @@ def _run(encoded: QuantizedWeight, flat_x: torch.Tensor, bias: Optional[torch.Te
         # split-manifold layout: activations stay in their dtype, the kernel widens and rounds
         x = flat_x.contiguous()
         out = torch.empty((batch, n), device=dev, dtype=x.dtype)
+        nnz, rp, ci, va = 0, None, None, None
+        if encoded.outliers is not None and encoded.outliers[2].numel() > 0:
+            rp, ci, va = (t.data_ptr() for t in encoded.outliers)
+            nnz = int(encoded.outliers[2].numel())
         rc = lib().ojasx_b200_linear_forward_raw(
             encoded.packed_codes.data_ptr(), encoded.codebooks.data_ptr(), encoded.row_scales.data_ptr(),
-            0 if b32 is None else b32.data_ptr(), 0, None, None, None, x.data_ptr(), out.data_ptr(), batch,
+            0 if b32 is None else b32.data_ptr(), nnz, rp, ci, va, x.data_ptr(), out.data_ptr(), batch,
             0 if x.dtype == torch.float32 else 1, encoded.block_size, 256, rows, columns, row_start, row_stop,
             _stream(dev))
         check(rc, "ojasx_b200_linear_forward_raw")
         return out
+    if encoded.outliers is not None and encoded.outliers[2].numel() > 0:
+        raise OjasxB200Error("CSR outliers are carried for the 8-bit single-stage layout only")
     x = flat_x.to(torch.float32).contiguous()
     out = torch.empty((batch, n), device=dev, dtype=torch.float32)
     rc = lib().ojasx_b200_rvq_fused_gemm(

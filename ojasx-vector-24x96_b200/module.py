@@ -29,13 +29,18 @@ class ResidualVQLinear(nn.Module):
         self.register_buffer("codebooks", encoded.codebooks)
         self.register_buffer("row_scales", encoded.row_scales)
         self.register_buffer("bias", None if bias is None else bias.to(torch.float32))
+        rp, ci, va = encoded.outliers if encoded.outliers is not None else (None, None, None)
+        self.register_buffer("csr_row_ptrs", rp)
+        self.register_buffer("csr_col_indices", ci)
+        self.register_buffer("csr_values", va)
         self.subspace_lut_mode = True
         self.fused_native_gemm = False
         self.cached_weight_bytes = 0  # no dense weight is ever materialised
 
     def encoded(self) -> QuantizedWeight:
+        outliers = None if self.csr_values is None else (self.csr_row_ptrs, self.csr_col_indices, self.csr_values)
         return QuantizedWeight((self.out_features, self.in_features), self.block_size, self.bits_per_stage,
-                               self.packed_codes, self.codebooks, self.row_scales, {})
+                               self.packed_codes, self.codebooks, self.row_scales, {}, outliers=outliers)
 
     def set_subspace_lut_mode(self, enabled: bool) -> None:
         self.subspace_lut_mode = bool(enabled)
