@@ -253,6 +253,16 @@ OJASX_API int ojasx_b200_add_int(int* d_values, int count, int delta, void* stre
 OJASX_API int ojasx_b200_kvq_set_static_plan(OjasxKvqHandle handle, int enabled);
 OJASX_API int ojasx_b200_kvq_sync_len(OjasxKvqHandle handle);
 
+/* ---- offline encoder: nearest-centroid assignment of n block vectors [n, block_dim] (fp32, 16-byte aligned)
+ * to a codebook [codebook_size <= 256, block_dim]: codes[i] = arg-min_k |v_i - c_k|^2, first minimum.  With
+ * d_sums (f64 [codebook_size, block_dim]) and d_counts (u64 [codebook_size]) not null, the per-cluster sums
+ * and sizes of a k-means update are ADDED to them (zero them first).  Device pointers; the hot step of
+ * SplitManifoldLUTLinear.from_dense (split_manifold_lut_experiment/engine/split_manifold_engine.py:140-160,
+ * torch.cdist + argmin + index_add_ there). */
+OJASX_API int ojasx_b200_vq_assign(const float* d_vectors, size_t n_vectors, int block_dim, const float* d_centroids,
+                                   int codebook_size, uint8_t* d_codes, double* d_sums, unsigned long long* d_counts,
+                                   void* stream);
+
 #ifdef __cplusplus
 }
 #endif
