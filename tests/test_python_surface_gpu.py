@@ -26,7 +26,9 @@ def _random_encoded(seed, rows, cols, block, bits, stages, device):
 
 
 CASES = [(64, 48, 8, 4, 2), (33, 50, 8, 4, 3), (40, 64, 4, 2, 4), (17, 24, 4, 1, 5), (128, 256, 8, 8, 1),
-         (96, 100, 8, 8, 1), (70, 512, 16, 8, 1), (50, 60, 8, 8, 2), (31, 37, 4, 8, 1)]
+         (96, 100, 8, 8, 1), (70, 512, 16, 8, 1), (50, 60, 8, 8, 2), (31, 37, 4, 8, 1),
+         # word-aligned rows of narrow codes: the table kernel of rvq_generic.cu (ragged last block included)
+         (200, 256, 8, 4, 4), (77, 250, 8, 4, 3), (64, 512, 8, 1, 8), (300, 2560, 8, 4, 4), (45, 128, 4, 2, 2)]
 
 
 @pytest.mark.parametrize("rows,cols,block,bits,stages", CASES)
@@ -42,6 +44,18 @@ def test_subspace_lut_rvq_gemm_matches_dequantised_linear(cuda, rows, cols, bloc
         assert (got - want).abs().max().item() < 1e-4
     out, sched = tilelang_backend.dispatch_universal_compressed_gemm(torch.randn(5, cols, device=cuda), enc, bias)
     assert out.shape == (5, rows) and sched.backend == "cuda_sm_100a"
+
+
+def test_narrow_width_table_kernel_agrees_with_the_compatibility_kernel(cuda, monkeypatch):
+    """4 bits x 4 stages (the reference's default artefacts): table kernel against the dequantise-and-dot kernel
+    (OJASX_B200_RVQ_COMPAT=1) on the same layer, batch and row slice."""
+    enc = _random_encoded(9, 700, 2560, 8, 4, 4, cuda)
+    x = torch.randn(3, 2560, device=cuda)
+    fast = math_engine.fused_rvq_gemm_native(enc, x, 100, 650)
+    monkeypatch.setenv("OJASX_B200_RVQ_COMPAT", "1")
+    slow = math_engine.fused_rvq_gemm_native(enc, x, 100, 650)
+    assert fast.shape == slow.shape == (3, 550)
+    assert torch.allclose(fast, slow, rtol=1e-4, atol=1e-4)
 
 
 def test_pack_unpack_roundtrip():
