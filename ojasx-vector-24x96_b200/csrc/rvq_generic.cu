@@ -88,13 +88,24 @@ __global__ void __launch_bounds__(kRvqLutThreads) rvq_lut_kernel(const uint8_t* 
     for (int b = 0; b < batch; ++b) {
         for (int i = tid; i < G * D; i += kRvqLutThreads) xs[i] = i < columns ? x[(size_t)b * columns + i] : 0.0f;
         __syncthreads();
-        for (int i = tid; i < stages * G * Q; i += kRvqLutThreads) {
-            const int q = i % Q, g = (i / Q) % G, s = i / (Q * G);
-            const float* c = codebooks + ((size_t)s * Q + q) * D;
-            const float* xg = xs + g * D;
-            float dot = 0.0f;
-            for (int d = 0; d < D; ++d) dot = fmaf(xg[d], c[d], dot);
-            lut[i] = dot;
+        {   // thread = (codebook entry q, group slot): no runtime division, consecutive threads write consecutive cells
+            const int q = tid & (Q - 1), gslot = tid >> BITS;
+            constexpr int kSlots = kRvqLutThreads >> BITS;
+            for (int s = 0; s < stages; ++s) {
+                const float* c = codebooks + ((size_t)s * Q + q) * D;
+                float* ls = lut + (size_t)s * G * Q;
+                for (int g = gslot; g < G; g += kSlots) {
+                    const float* xg = xs + g * D;
+                    float dot = 0.0f;
+                    for (int d = 0; d < D; d += 4) {   // block sizes are multiples of 4
+                        const float4 xv = *reinterpret_cast<const float4*>(xg + d);
+                        const float4 cv = *reinterpret_cast<const float4*>(c + d);
+                        dot = fmaf(xv.x, cv.x, dot); dot = fmaf(xv.y, cv.y, dot);
+                        dot = fmaf(xv.z, cv.z, dot); dot = fmaf(xv.w, cv.w, dot);
+                    }
+                    ls[g * Q + q] = dot;
+                }
+            }
         }
         __syncthreads();
         for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
@@ -104,11 +115,18 @@ __global__ void __launch_bounds__(kRvqLutThreads) rvq_lut_kernel(const uint8_t* 
                 for (int s = 0; s < stages; ++s) {
                     const unsigned* rw = words + (size_t)s * stage_words + (size_t)r * wpr;
                     const float* ls = lut + (size_t)s * G * Q;
-                    for (int w = t; w < wpr; w += 8) {
-                        const unsigned word = rw[w];
-                        const float* lw = ls + (size_t)w * CPW * Q;
+                    for (int w0 = t; w0 < wpr; w0 += 8 * 4) {   // four words of this lane in flight
+                        unsigned word[4];
 #pragma unroll
-                        for (int j = 0; j < CPW; ++j) acc += lw[j * Q + ((word >> (j * BITS)) & mask)];
+                        for (int u = 0; u < 4; ++u) word[u] = w0 + 8 * u < wpr ? rw[w0 + 8 * u] : 0u;
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            if (w0 + 8 * u < wpr) {
+                                const float* lw = ls + (size_t)(w0 + 8 * u) * CPW * Q;
+#pragma unroll
+                                for (int j = 0; j < CPW; ++j) acc += lw[j * Q + ((word[u] >> (j * BITS)) & mask)];
+                            }
+                        }
                     }
                 }
             }
@@ -133,8 +151,16 @@ static int launch_rvq_lut(const uint8_t* packed, const float* codebooks, const f
     const int tiles = (row_stop - row_start + kRvqLutRows - 1) / kRvqLutRows;
     const int cap = 8 * num_sms();
     const int grid = tiles < cap ? tiles : cap;
+    if (D % 4 != 0 || (reinterpret_cast<uintptr_t>(codebooks) & 15)) return OJX_ERR_UNSUPPORTED;
     auto go = [&](auto kern) -> int {
-        if (smem > 48 * 1024) OJX_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        static thread_local size_t opted[16][3] = {};   // largest opt-in so far, per device and width
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) dev = 0;
+        size_t& have = opted[dev][bits == 1 ? 0 : bits == 2 ? 1 : 2];
+        if (smem > 48 * 1024 && smem > have) {
+            OJX_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            have = smem;
+        }
         kern<<<grid, kRvqLutThreads, smem, s>>>(packed, codebooks, row_scales, bias, x, batch, stages, D, rows, columns,
                                                 row_start, row_stop, out);
         OJX_CUDA_TRY(cudaGetLastError());
