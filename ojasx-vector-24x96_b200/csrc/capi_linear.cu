@@ -89,6 +89,7 @@ LinearHandle::~LinearHandle() {
     DeviceGuard g(dev);
     cudaFree(codes); cudaFree(codebook); cudaFree(scales); cudaFree(bias);
     cudaFree(row_ptrs); cudaFree(cols); cudaFree(vals); cudaFree(d_x); cudaFree(d_y); cudaFree(dq_scratch);
+    if (host_graph) cudaGraphExecDestroy(host_graph);
     if (pin_x) cudaFreeHost(pin_x);
     if (pin_y) cudaFreeHost(pin_y);
     if (stream) cudaStreamDestroy(stream);
@@ -258,9 +259,38 @@ int ojasx_linear_forward(OjasxLinearHandle handle, const float* x, float* y, int
     }
     void* y_dev = h->pin_y_dev;
     std::memcpy(h->pin_x, x, xb);
-    OJX_CUDA_TRY(cudaMemcpyAsync(h->d_x, h->pin_x, xb, cudaMemcpyHostToDevice, h->stream));
-    rc = launch_linear(h->problem(h->d_x, y_dev, batch_size, OJX_F32, 0, h->out), h->stream);
-    if (rc != OJX_OK) return rc;
+    // The copy and the kernel have the same arguments on every call of a given batch size, so they are
+    // recorded once as a graph and replayed with one launch call (OJASX_B200_HOST_GRAPH=0 disables).
+    static const bool use_graph = [] { const char* e = getenv("OJASX_B200_HOST_GRAPH"); return !(e && e[0] == '0'); }();
+    const bool graph_ok = use_graph && h->host_graph && h->host_graph_batch == batch_size && h->host_graph_key[0] == h->pin_x &&
+                          h->host_graph_key[1] == h->d_x && h->host_graph_key[2] == y_dev;
+    if (graph_ok) {
+        OJX_CUDA_TRY(cudaGraphLaunch(h->host_graph, h->stream));
+    } else if (use_graph) {
+        if (h->host_graph) { cudaGraphExecDestroy(h->host_graph); h->host_graph = nullptr; }
+        cudaGraph_t g = nullptr;
+        OJX_CUDA_TRY(cudaStreamBeginCapture(h->stream, cudaStreamCaptureModeThreadLocal));
+        cudaError_t ce = cudaMemcpyAsync(h->d_x, h->pin_x, xb, cudaMemcpyHostToDevice, h->stream);
+        rc = ce == cudaSuccess ? launch_linear(h->problem(h->d_x, y_dev, batch_size, OJX_F32, 0, h->out), h->stream) : OJX_ERR_CUDA;
+        const cudaError_t ee = cudaStreamEndCapture(h->stream, &g);
+        if (rc != OJX_OK || ee != cudaSuccess || !g) {
+            if (g) cudaGraphDestroy(g);
+            (void)cudaGetLastError();
+            if (rc != OJX_OK) return rc;
+            set_last_error("cudaStreamEndCapture", ee);
+            return OJX_ERR_CUDA;
+        }
+        ce = cudaGraphInstantiate(&h->host_graph, g, 0);
+        cudaGraphDestroy(g);
+        if (ce != cudaSuccess) { h->host_graph = nullptr; set_last_error("cudaGraphInstantiate", ce); return OJX_ERR_CUDA; }
+        h->host_graph_batch = batch_size;
+        h->host_graph_key[0] = h->pin_x; h->host_graph_key[1] = h->d_x; h->host_graph_key[2] = y_dev;
+        OJX_CUDA_TRY(cudaGraphLaunch(h->host_graph, h->stream));
+    } else {
+        OJX_CUDA_TRY(cudaMemcpyAsync(h->d_x, h->pin_x, xb, cudaMemcpyHostToDevice, h->stream));
+        rc = launch_linear(h->problem(h->d_x, y_dev, batch_size, OJX_F32, 0, h->out), h->stream);
+        if (rc != OJX_OK) return rc;
+    }
     if ((rc = wait_stream(h->stream)) != OJX_OK) return rc;
     std::memcpy(y, h->pin_y, yb);
     return OJX_OK;

@@ -45,6 +45,10 @@ struct LinearHandle {
     cudaStream_t stream = nullptr;
     void* dq_scratch = nullptr;    // tensor-core path: tile counters and split-K partial sums
     size_t dq_scratch_cap = 0;
+    // host-pointer forward: the copy of x and the kernel as one instantiated graph (one launch call per forward)
+    cudaGraphExec_t host_graph = nullptr;
+    int host_graph_batch = 0;
+    const void* host_graph_key[3] = {nullptr, nullptr, nullptr};   // pin_x, d_x, pin_y_dev it was captured with
 
     ~LinearHandle();
     LinearProblem problem(const void* x, void* y, int batch, int io_dtype, int row_start, int row_stop) const;
