@@ -266,6 +266,7 @@ int ojasx_linear_forward(OjasxLinearHandle handle, const float* x, float* y, int
                           h->host_graph_key[1] == h->d_x && h->host_graph_key[2] == y_dev;
     if (graph_ok) {
         OJX_CUDA_TRY(cudaGraphLaunch(h->host_graph, h->stream));
+        count_launch(1);   // the graph's one kernel
     } else if (use_graph) {
         if (h->host_graph) { cudaGraphExecDestroy(h->host_graph); h->host_graph = nullptr; }
         cudaGraph_t g = nullptr;
