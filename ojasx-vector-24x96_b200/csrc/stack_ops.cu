@@ -18,26 +18,52 @@ __device__ __forceinline__ void st_io(void* p, size_t i, int dt, float v) {
 }
 
 // out[r, :] = x[r, :] * rsqrt(mean(x[r, :]^2) + eps) * w ; optionally x[r, :] += add[r, :] first
-// (the residual add that precedes the norm), with the sum also written back to x.
+// (the residual add that precedes the norm), with the sum also written back to x.  A thread keeps its
+// elements in registers between the two passes (up to kNormKeep of them; rows longer than
+// 256 * kNormKeep re-read the rest), and the row sum is a shuffle tree per warp plus one exchange.
+constexpr int kNormKeep = 16;
+
 __global__ void __launch_bounds__(256) rmsnorm_kernel(void* __restrict__ x, const void* __restrict__ add,
                                                       const float* __restrict__ w, void* __restrict__ out, int H, float eps,
                                                       int io_dtype) {
-    __shared__ float red[256];
+    __shared__ float red[8];
     const size_t base = (size_t)blockIdx.x * H;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float keep[kNormKeep];
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    auto element = [&](int i) {   // the (updated) value of x[r, i] as it is stored, i.e. rounded to the io dtype
         float v = ld_io(x, base + i, io_dtype);
-        if (add) { v += ld_io(add, base + i, io_dtype); st_io(x, base + i, io_dtype, v); v = ld_io(x, base + i, io_dtype); }
+        if (add) {
+            v += ld_io(add, base + i, io_dtype);
+            if (io_dtype == OJX_BF16) v = __bfloat162float(__float2bfloat16_rn(v));
+            st_io(x, base + i, io_dtype, v);
+        }
+        return v;
+    };
+#pragma unroll
+    for (int u = 0; u < kNormKeep; ++u) {
+        const int i = tid + u * 256;
+        keep[u] = i < H ? element(i) : 0.0f;
+        ss += keep[u] * keep[u];
+    }
+    for (int i = tid + kNormKeep * 256; i < H; i += 256) {
+        const float v = element(i);
         ss += v * v;
     }
-    red[threadIdx.x] = ss;
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    if (lane == 0) red[warp] = ss;
     __syncthreads();
-    for (int s = blockDim.x / 2; s > 0; s >>= 1) {
-        if (threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s];
-        __syncthreads();
+    float total = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) total += red[k];
+    const float inv = rsqrtf(total / (float)H + eps);
+#pragma unroll
+    for (int u = 0; u < kNormKeep; ++u) {
+        const int i = tid + u * 256;
+        if (i < H) st_io(out, base + i, io_dtype, keep[u] * inv * w[i]);
     }
-    const float inv = rsqrtf(red[0] / (float)H + eps);
-    for (int i = threadIdx.x; i < H; i += blockDim.x) st_io(out, base + i, io_dtype, ld_io(x, base + i, io_dtype) * inv * w[i]);
+    for (int i = tid + kNormKeep * 256; i < H; i += 256) st_io(out, base + i, io_dtype, ld_io(x, base + i, io_dtype) * inv * w[i]);
 }
 
 // Rotate-half rotary embedding in place on q [B, Hq, hd] and k [B, Hkv, hd] at positions pos[b].
