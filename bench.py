@@ -435,7 +435,8 @@ def bench_stack(args, dev):
     W = ie.make_stack_weights(2024, cfg)
     out["host_weight_seconds"] = round(time.perf_counter() - t0, 1)
     for B in args.stack_batches:
-        stack = ie.VQDecoderStack(W, cfg, batch=B, use_graph=not args.stack_eager)
+        stack = ie.VQDecoderStack(W, cfg, batch=B, use_graph=not args.stack_eager,
+                                  dtype=torch.bfloat16 if args.stack_dtype == "bf16" else torch.float32)
         ids = torch.randint(0, cfg.vocab, (B, args.stack_prompt), device=dev, generator=torch.Generator(device=dev).manual_seed(3))
         torch.cuda.synchronize()
         t0 = time.perf_counter()
@@ -449,7 +450,7 @@ def bench_stack(args, dev):
         out[f"B{B}"] = {"prefill_tokens_per_s": round(B * args.stack_prompt / (t1 - t0), 1),
                         "decode_tokens_per_s": round(B * args.stack_new / (t2 - t1), 1),
                         "ms_per_decode_step": round((t2 - t1) / args.stack_new * 1e3, 3),
-                        "prompt": args.stack_prompt, "new_tokens": args.stack_new}
+                        "prompt": args.stack_prompt, "new_tokens": args.stack_new, "dtype": args.stack_dtype}
         del stack
         torch.cuda.empty_cache()
     return out
@@ -515,6 +516,8 @@ def main():
     ap.add_argument("--stack-prompt", type=int, default=512)
     ap.add_argument("--stack-new", type=int, default=256)
     ap.add_argument("--stack-batches", type=int, nargs="+", default=[1, 32])
+    ap.add_argument("--stack-dtype", default="f32", choices=["f32", "bf16"],
+                    help="activation dtype of the stack; bf16 batches >= 32 take the tensor-core linears")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
