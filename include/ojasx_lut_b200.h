@@ -263,6 +263,24 @@ OJASX_API int ojasx_b200_vq_assign(const float* d_vectors, size_t n_vectors, int
                                    int codebook_size, uint8_t* d_codes, double* d_sums, unsigned long long* d_counts,
                                    void* stream);
 
+/* ---- paged int8 KV cache: device side of PagedCompressedKVCache (ojasx_24x96/long_context.py:212-279).
+ * quantize: n_vectors rows [head_dim] of io_dtype -> int8 rows and one fp16 scale per row, the arithmetic of
+ * _quantize_int8 (:236-241: abs-max clamped at 1e-8, / 127, round half to even, clamp to +-127).
+ * decode: softmax(q K^T * scale) V of one query per (sequence, head) over the resident pages, read as int8.
+ * Pools are [slots, batch, kv_heads, page_size, head_dim] int8 and [slots, batch, kv_heads, page_size] fp16;
+ * d_page_slot[i] is the pool slot of the i-th resident page (oldest first) and d_page_start the prefix sums
+ * of the pages' token counts (n_pages + 1 entries, total_tokens last).  d_scratch: at least
+ * ojasx_b200_paged_kv_scratch_floats(batch, q_heads, head_dim, total_tokens) floats; d_counters: batch * q_heads
+ * ints, zero before the first call (they return to zero).  head_dim 64, 128 or 256; scale <= 0 = 1/sqrt(head_dim). */
+OJASX_API int ojasx_b200_paged_kv_quantize(const void* d_src, int io_dtype, size_t n_vectors, int head_dim, int8_t* d_q8,
+                                           void* d_scales_f16, void* stream);
+OJASX_API int ojasx_b200_paged_kv_scratch_floats(int batch, int q_heads, int head_dim, int max_tokens);
+OJASX_API int ojasx_b200_paged_kv_decode(const void* d_q, void* d_out, const int8_t* d_k_pool, const int8_t* d_v_pool,
+                                         const void* d_k_scales_f16, const void* d_v_scales_f16, const int* d_page_slot,
+                                         const int* d_page_start, int n_pages, int total_tokens, int batch, int q_heads,
+                                         int kv_heads, int head_dim, int page_size, float scale, int io_dtype,
+                                         float* d_scratch, int* d_counters, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -47,6 +47,9 @@ SIGNATURES = {
     "ojasx_ggml_forward_linear": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
     "ojasx_ggml_forward_moe": (_i, [_vp, _vp, _vp, _vp, _i, _vp]),
     "ojasx_ggml_forward_kv_attention": (_i, [_vp, _vp, _i, _f, _vp]),
+    "ojasx_b200_paged_kv_quantize": (_i, [_vp, _i, _sz, _i, _vp, _vp, _vp]),
+    "ojasx_b200_paged_kv_scratch_floats": (_i, [_i, _i, _i, _i]),
+    "ojasx_b200_paged_kv_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp, _vp]),
     "ojasx_b200_vq_assign": (_i, [_vp, _sz, _i, _vp, _i, _vp, _vp, _vp, _vp]),
     "ojasx_b200_last_error": (C.c_char_p, []),
     "ojasx_b200_launch_count": (C.c_ulonglong, []),
