@@ -268,6 +268,8 @@ def run_ours(args):
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         return float(tt.item())
 
+    if args.e2e_threads <= 0:
+        args.e2e_threads = min(4, max(1, (os.cpu_count() or 4) // max(1, world)))
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
     dt1 = e2e_time(1)
     n1 = ojasx_b200.launch_count()
@@ -506,7 +508,9 @@ def main():
     ap.add_argument("--layers", type=int, default=1480, help="independent layers per GPU per step (10 per SM)")
     ap.add_argument("--e2e-layers", type=int, default=148)
     ap.add_argument("--e2e-steps", type=int, default=5)
-    ap.add_argument("--e2e-threads", type=int, default=4, help="host threads that issue the synchronous per-layer calls of the e2e leg")
+    ap.add_argument("--e2e-threads", type=int, default=0,
+                    help="host threads that issue the synchronous per-layer calls of the e2e leg (0 = up to 4, as many as the "
+                         "host cores allow each rank, since every caller polls for completion)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-moe", dest="moe", action="store_false")
     ap.add_argument("--no-moe-csr", dest="moe_csr", action="store_false")
