@@ -244,6 +244,7 @@ int ojasx_linear_forward(OjasxLinearHandle handle, const float* x, float* y, int
     if (!handle || !x || !y) return OJX_ERR_ARG;  // ojasx_lut_c_api.cpp:100
     auto* h = static_cast<LinearHandle*>(handle);
     if (batch_size <= 0) return OJX_OK;           // the reference's batch loop simply does not run
+    std::lock_guard<std::mutex> lock(h->host_mu);   // concurrent callers of one layer take turns (as safe as the const CPU method)
     DeviceGuard g(h->dev);
     const size_t xb = sizeof(float) * (size_t)batch_size * h->in, yb = sizeof(float) * (size_t)batch_size * h->out;
     int rc;

@@ -2,6 +2,8 @@
 // host pointers (split_manifold_lut_experiment/native/src/ojasx_lut_c_api.cpp:131-287) and the
 // ojasx_b200_moe_* / ojasx_b200_kvq_* device-pointer entry points.
 #include "../../include/ojasx_lut_b200.h"
+#include <mutex>
+
 #include "handles.h"
 #include "launch.h"
 
@@ -213,6 +215,7 @@ int ojasx_moe_forward(OjasxMoEHandle handle, const float* x, const int* top_k_in
     if (!handle || !x || !top_k_indices || !top_k_weights || !y_out) return OJX_ERR_ARG;  // ojasx_lut_c_api.cpp:267
     if (k_active <= 0) return OJX_OK;                                                       // ojasx_lut_cpu.cpp:220
     auto* h = static_cast<MoeHandle*>(handle);
+    std::lock_guard<std::mutex> lock(h->host_mu);
     DeviceGuard g(h->dev);
     const size_t xb = sizeof(float) * (size_t)h->H, kb = (size_t)k_active * 4;
     int rc = ensure_capacity(&h->stage, &h->stage_cap, 2 * xb + 2 * kb + 64);
@@ -409,6 +412,7 @@ int ojasx_kv_cache_append(OjasxKVHandle handle, int head_idx, const float* k, co
     if (!handle || !k || !v) return OJX_ERR_ARG;
     auto* kv = static_cast<LegacyKvHandle*>(handle);
     if (head_idx < 0 || head_idx >= kv->num_heads) return OJX_ERR_RANGE;
+    std::lock_guard<std::mutex> lock(kv->host_mu);
     DeviceGuard g(kv->dev);
     auto& h = kv->heads[head_idx];
     if (h.len >= h.cap) {
@@ -433,6 +437,7 @@ int ojasx_kv_cache_attention(OjasxKVHandle handle, int head_idx, const float* q,
     if (!handle || !q || !out_context) return OJX_ERR_ARG;
     auto* kv = static_cast<LegacyKvHandle*>(handle);
     if (head_idx < 0 || head_idx >= kv->num_heads) return OJX_ERR_RANGE;
+    std::lock_guard<std::mutex> lock(kv->host_mu);
     auto& h = kv->heads[head_idx];
     if (h.len == 0) return OJX_OK;  // ojasx_lut_c_api.cpp:173: out_context is left untouched
     DeviceGuard g(kv->dev);

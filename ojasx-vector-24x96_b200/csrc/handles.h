@@ -1,6 +1,7 @@
 // Host-side objects behind the opaque C handles.
 #pragma once
 #include "common.cuh"
+#include <mutex>
 #include <vector>
 
 namespace ojx {
@@ -43,6 +44,7 @@ struct LinearHandle {
     void* pin_y_dev = nullptr;     // device alias of pin_y (cached)
     void* pin_y_dev_of = nullptr;  // the pin_y it was taken from
     cudaStream_t stream = nullptr;
+    std::mutex host_mu;            // the host-pointer entry points use this handle's staging buffers one call at a time
     void* dq_scratch = nullptr;    // tensor-core path: tile counters and split-K partial sums
     size_t dq_scratch_cap = 0;
     // host-pointer forward: the copy of x and the kernel as one instantiated graph (one launch call per forward)
@@ -92,6 +94,7 @@ struct MoeHandle {
     void* stage = nullptr;                   // host-pointer forward staging
     size_t stage_cap = 0;
     cudaStream_t stream = nullptr;
+    std::mutex host_mu;                      // host-pointer forwards of one handle run one at a time
 
     ~MoeHandle();
     int reserve(int n_tokens, int k);
@@ -131,6 +134,7 @@ struct LegacyKvHandle {
     void* logits = nullptr;
     size_t logits_cap = 0;
     cudaStream_t stream = nullptr;
+    std::mutex host_mu;       // append / attention of one cache run one at a time
     ~LegacyKvHandle();
 };
 

@@ -142,3 +142,32 @@ def test_kv_error_codes(cuda):
     assert L.ojasx_kv_cache_append(cache._handle, -1, v.ctypes.data, v.ctypes.data) == -2
     out = np.zeros(64, np.float32)
     assert L.ojasx_kv_cache_attention(cache._handle, 5, v.ctypes.data, out.ctypes.data, C.c_float(1.0)) == -2
+
+
+def test_concurrent_callers_of_one_handle(cuda, oracle):
+    """Several host threads calling ojasx_linear_forward on ONE handle with their own buffers: the calls are
+    serialised inside the library, so every caller gets the result of its own input (the reference's CPU
+    handle is stateless between calls, ojasx_lut_c_api.cpp:100-118)."""
+    import threading
+
+    L = ojasx_b200.lib()
+    w = synth.make_vq_linear(77, 512, 384, block_dim=8, outlier_frac=0.01)
+    layer = ops.VQLinear.from_weights(w)
+    rng = np.random.default_rng(4)
+    xs = [rng.standard_normal(512).astype(np.float32) for _ in range(4)]
+    want = [_lin(oracle, w, x[None])[0] for x in xs]
+    bad = []
+
+    def run(i):
+        y = np.zeros(384, np.float32)
+        for _ in range(50):
+            if L.ojasx_linear_forward(layer.handle, xs[i].ctypes.data, y.ctypes.data, 1, 0) != 0 or not np.array_equal(y, want[i]):
+                bad.append(i)
+                return
+
+    threads = [threading.Thread(target=run, args=(i,)) for i in range(4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not bad
