@@ -5,6 +5,7 @@
 // table build, code gather and CSR outlier add all happen in the CTA that owns the rows, and y
 // is written once.
 #include "lut_core.cuh"
+#include "lut_chain.cuh"
 #include "launch.h"
 #include "handles.h"
 
@@ -24,7 +25,7 @@ __device__ __forceinline__ const LinearProblem& find_problem(const LinearProblem
 template <int D>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 lut_linear_kernel(const LinearProblem* __restrict__ probs, int nprobs, int total_items,
-                  const __grid_constant__ LinearProblem single) {
+                  const __grid_constant__ LinearProblem single, int chain_walk) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     CoreSmem& sm = *reinterpret_cast<CoreSmem*>(smem_raw);
 
@@ -46,20 +47,39 @@ lut_linear_kernel(const LinearProblem* __restrict__ probs, int nprobs, int total
         rs.aligned = ((P.G & 15) == 0) && ((reinterpret_cast<uintptr_t>(P.codes) & 15) == 0);
         const XLoad xl{static_cast<const char*>(P.x) + (size_t)b * P.K * esz, P.K, P.io_dtype};
 
-        RowWalker<D> walker(sm, rs);
-        if (walker.nslices == 0)
-            for (int lr = threadIdx.x; lr < n; lr += kThreads) sm.acc[lr] = 0.0f;
-        walker.run(xl, P.codebook, P.Kcb, [&]() { if (P.csr.nnz > 0) csr_prefetch_l2(P.csr, r0, n); });
+        // Lanes share a row (conflict-free gathers) whenever the code rows split into 16-byte pieces.
+        bool chain = false;
+        if constexpr (D <= 16) chain = chain_walk && ChainWalker<D>::usable(smem_raw, rs.base0, P.codebook, P.G);
+        float* accp = sm.acc;
+        float* area = sm.lut;
+        int* rp = reinterpret_cast<int*>(sm.ring);
+        if constexpr (D <= 16) {
+            if (chain) {
+                const ChainWalker<D> cw(smem_raw, rs.base0, n, P.G);
+                accp = cw.acc();
+                area = cw.table();
+                rp = cw.ring_hi_ints();
+            }
+        }
+        if (P.G == 0)
+            for (int lr = threadIdx.x; lr < n; lr += kThreads) accp[lr] = 0.0f;
+        auto ask_l2 = [&]() { if (P.csr.nnz > 0) csr_prefetch_l2(P.csr, r0, n); };
+        if constexpr (D <= 16) {
+            if (chain) ChainWalker<D>(smem_raw, rs.base0, n, P.G).run(xl, P.codebook, P.Kcb, ask_l2);
+            else RowWalker<D>(sm, rs).run(xl, P.codebook, P.Kcb, ask_l2);
+        } else {
+            RowWalker<D>(sm, rs).run(xl, P.codebook, P.Kcb, ask_l2);
+        }
         __syncthreads();
 
         // Epilogue (ojasx_lut_cpu.cpp:178-182 then :117-127): scale, bias, outlier row, one store.
-        if (P.csr.nnz > 0) csr_rows_to_smem(sm, P.csr, r0, n, 0, xl);
+        if (P.csr.nnz > 0) csr_rows_to_area(area, rp, P.csr, r0, n, 0, xl);
         for (int lr = threadIdx.x; lr < n; lr += kThreads) {
             const int m = r0 + lr;
-            float res = sm.acc[lr];
+            float res = accp[lr];
             if (P.scales) res = __fmul_rn(res, P.scales[m]);
             if (P.bias) res = __fadd_rn(res, P.bias[m]);
-            if (P.csr.nnz > 0) res = __fadd_rn(res, sm.lut[lr]);
+            if (P.csr.nnz > 0) res = __fadd_rn(res, area[lr]);
             const size_t o = (size_t)b * rows_out + (m - P.row_start);
             if (P.io_dtype == OJX_BF16) reinterpret_cast<__nv_bfloat16*>(P.y)[o] = __float2bfloat16_rn(res);
             else reinterpret_cast<float*>(P.y)[o] = res;
@@ -68,7 +88,7 @@ lut_linear_kernel(const LinearProblem* __restrict__ probs, int nprobs, int total
     }
 }
 
-using LinearKernel = void (*)(const LinearProblem*, int, int, const LinearProblem);
+using LinearKernel = void (*)(const LinearProblem*, int, int, const LinearProblem, int);
 
 static LinearKernel pick_linear_kernel(int D) {
     switch (D) {
@@ -114,6 +134,12 @@ static bool force_persistent() {
 }
 bool linear_cluster_disabled() { return force_persistent(); }
 
+// OJASX_B200_LINEAR_WALK=rows keeps the walk that gives every lane a row of its own (RowWalker).
+static int chain_walk_enabled() {
+    const char* e = getenv("OJASX_B200_LINEAR_WALK");
+    return !(e && e[0] == 'r');
+}
+
 int validate_linear(const LinearProblem& P) {
     if (!P.codes || !P.codebook || !P.x || !P.y) return OJX_ERR_ARG;
     if (P.batch <= 0 || P.K <= 0 || P.G < 0 || P.row_stop <= P.row_start || P.row_start < 0) return OJX_ERR_ARG;
@@ -141,7 +167,7 @@ int launch_linear(LinearProblem P, cudaStream_t stream) {
     if (rc != OJX_OK) return rc;
     const int cap = kCtasPerSm * num_sms();
     const int grid = total < cap ? total : cap;
-    k<<<grid, kThreads, sizeof(CoreSmem), stream>>>(nullptr, 0, total, P);
+    k<<<grid, kThreads, sizeof(CoreSmem), stream>>>(nullptr, 0, total, P, chain_walk_enabled());
     count_launch(1);
     OJX_CUDA_TRY(cudaGetLastError());
     return OJX_OK;
@@ -156,7 +182,7 @@ int launch_linear_group(const LinearProblem* d_probs, int nprobs, int total_item
     const int cap = kCtasPerSm * num_sms();
     const int grid = total_items < cap ? total_items : cap;
     LinearProblem dummy{};
-    k<<<grid, kThreads, sizeof(CoreSmem), stream>>>(d_probs, nprobs, total_items, dummy);
+    k<<<grid, kThreads, sizeof(CoreSmem), stream>>>(d_probs, nprobs, total_items, dummy, chain_walk_enabled());
     count_launch(1);
     OJX_CUDA_TRY(cudaGetLastError());
     return OJX_OK;

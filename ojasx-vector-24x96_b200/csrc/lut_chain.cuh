@@ -1,0 +1,316 @@
+// Row walk of the split-manifold LUT path with conflict-free table gathers.
+//
+// RowWalker (lut_core.cuh) gives every lane one row: the 32 gathers of a warp instruction hit
+// random banks of the table and cost about four shared-memory wavefronts.  Here the 32 lanes of a
+// warp share one row instead: lane l owns the four groups 4l..4l+3 of the table slice, and the
+// slice is stored code-major with lane l's entries in bank l, so a gather instruction is one
+// wavefront whatever the codes are.
+//
+// The reference adds a row's table entries in ascending group order into one fp32 accumulator
+// (split_manifold_lut_experiment/native/src/ojasx_lut_cpu.cpp:161-175).  That order is kept by
+// passing the running sum of a row from lane to lane: in step t lane l works on row t - l, takes
+// the sum that lane l - 1 produced for that row one step earlier (one shuffle), adds its four
+// entries in order and hands the sum on.  Thirty-two rows are in flight in a warp, each one lane
+// further than the next; lane 0 starts a row from the sum parked in shared memory (zero in the
+// first slice) and the last active lane parks it again.
+//
+// Shared memory, by absolute shared-space address (the walker is used only when the dynamic area
+// starts at 1024, which is checked at run time):
+//     1024  parked row sums           f32[6912]
+//    28672  activations of the slice  f32[2048], element d of group p at d*SG + p
+//    36864  code rings of warps 0..6  (4 KB each)
+//    65536  table, groups j = 0, 1    entry (code k, j, lane l) at 65536 + k*256 + j*128 + l*4
+//   131072  table, groups j = 2, 3    entry at 131072 + k*256 + (j-2)*128 + l*4
+//   196608  code rings of warps 7..15
+// Both table halves start on a 64 KB boundary, so the address of an entry is the constant word
+// (half | l*4) with the code byte dropped into bits 8..15: one byte-permute instruction per gather.
+//
+// Code bytes: a warp owns a contiguous run of rows and a ring of 32 slots of 128 bytes, slot
+// (row & 31) holding the row's bytes of the current slice, so lane l finds its four codes in word
+// l of the slot (bank l again).  The bytes are requested with 16-byte cp.async pieces, each piece
+// kLead steps before the first lane needs it: the eight lanes 8k..8k+7 use their 32-byte sector of
+// row u in steps u+8k .. u+8k+7, so that sector is requested in step u+8k-kLead.  A lane reads its
+// word two steps before it uses it; with kLead = 22 a piece lands at least two steps after the last
+// read of the slot's previous row and is complete six steps before its first read.
+//
+// Rows outside the warp's run (while the chain fills and drains) are walked like the others with
+// whatever bytes the slot holds: every byte is a valid table index, their sums travel only along
+// their own diagonal, and nothing of them is stored.
+#pragma once
+#include "lut_core.cuh"
+
+namespace ojx {
+
+constexpr uint32_t kChAcc = 1024, kChXs = 28672, kChRingLo = 36864, kChTab = 65536, kChRingHi = 196608;
+constexpr int kChRingBytes = 4096, kChLoWarps = 7;
+static_assert(kChAcc + kAccRows * 4 == kChXs && kChXs + kXsFloats * 4 == kChRingLo, "front area");
+static_assert(kChRingLo + kChLoWarps * kChRingBytes == kChTab, "rings of the first warps end at the table");
+static_assert(kChRingHi + (kWarps - kChLoWarps) * kChRingBytes == kChAcc + sizeof(CoreSmem), "whole dynamic area");
+static_assert(kChTab + kSliceGroups * 256 * 4 == kChRingHi, "table");
+
+__device__ __forceinline__ uint32_t ch_prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+template <int OFF>
+__device__ __forceinline__ float ch_lds_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(addr), "n"(OFF));
+    return v;
+}
+__device__ __forceinline__ uint32_t ch_lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+template <int D>
+struct ChainWalker {
+    static constexpr int SG = slice_groups<D>();
+    static constexpr int kSlots = 32;
+    static constexpr int kSlotBytes = 128;
+    static constexpr int kLead = 22;
+    static constexpr int kPrologue = 24;  // kLead rounded up to the request cadence of four steps
+    static_assert(kSlots * kSlotBytes == kChRingBytes, "ring");
+    static_assert(SG <= 128 && SG % 16 == 0, "a slice is at most 32 lanes x 4 groups");
+
+    unsigned char* const raw;  // start of the dynamic shared memory (shared address 1024)
+    const uint8_t* base;       // code row 0 of the work item
+    const int n, G;
+    const int warp, lane, nslices;
+
+    __device__ ChainWalker(unsigned char* raw_, const uint8_t* base_, int n_, int G_)
+        : raw(raw_), base(base_), n(n_), G(G_), warp(threadIdx.x >> 5), lane(threadIdx.x & 31),
+          nslices((G_ + SG - 1) / SG) {}
+
+    template <class T>
+    __device__ __forceinline__ T* at(uint32_t shared_addr) const { return reinterpret_cast<T*>(raw + (shared_addr - kChAcc)); }
+    __device__ __forceinline__ float* acc() const { return at<float>(kChAcc); }
+    __device__ __forceinline__ float* table() const { return at<float>(kChTab); }
+    __device__ __forceinline__ int* ring_hi_ints() const { return at<int>(kChRingHi); }
+
+    // The walker needs whole 16-byte pieces of every row, four groups per lane and the layout above.
+    __device__ static __forceinline__ bool usable(const unsigned char* raw, const uint8_t* codes, const float* codebook, int G) {
+        return D <= 16 && (G & 15) == 0 && ((reinterpret_cast<uintptr_t>(codes) & 15) == 0) &&
+               ((reinterpret_cast<uintptr_t>(codebook) & 15) == 0) &&
+               static_cast<uint32_t>(__cvta_generic_to_shared(raw)) == kChAcc;
+    }
+
+    // Table slice of groups [g0, g0 + ng): entry (k, j, l) = sum_d x[(g0+4l+j)*D + d] * cb[k*D + d], d ascending,
+    // separate multiply and add (the arithmetic of RowWalker::build_slice, so the same bits).  A thread keeps the
+    // activations of its four groups in registers and runs over the centroids, whose coordinates every lane of a
+    // warp reads from the same address.  `xr` holds this thread's share of the slice's activations, loaded before
+    // the barrier that precedes the build (load_x).
+    static constexpr int kXPerThread = kXsFloats / kThreads;
+    __device__ __forceinline__ void load_x(int g0, int ng, const XLoad& xl, float (&xr)[kXPerThread]) const {
+#pragma unroll
+        for (int q = 0; q < kXPerThread; ++q) {
+            const int i = threadIdx.x + q * kThreads;
+            xr[q] = 0.0f;
+            if (i < ng * D) {
+                const int d = i / ng, pos = i - d * ng;
+                xr[q] = xl((g0 + pos) * D + d);
+            }
+        }
+    }
+    __device__ __forceinline__ void build_slice(int ng, const float (&xr)[kXPerThread], const float* __restrict__ codebook,
+                                                int Kcb) const {
+        float* xs = at<float>(kChXs);
+#pragma unroll
+        for (int q = 0; q < kXPerThread; ++q) {
+            const int i = threadIdx.x + q * kThreads;
+            if (i < ng * D) {
+                const int d = i / ng, pos = i - d * ng;
+                xs[d * SG + pos] = xr[q];
+            }
+        }
+        __syncthreads();
+        const int lpos = ng <= 64 ? (lane & 15) : lane;  // a slice of <= 64 groups is kept twice: lanes 16..31 mirror 0..15
+        if (4 * lpos < ng) {
+            float xg[4][D];
+#pragma unroll
+            for (int d = 0; d < D; ++d) {
+                const float4 v = *reinterpret_cast<const float4*>(xs + d * SG + 4 * lpos);
+                xg[0][d] = v.x; xg[1][d] = v.y; xg[2][d] = v.z; xg[3][d] = v.w;
+            }
+            float* out = table() + lane;
+#pragma unroll 2
+            for (int k = warp; k < 256; k += kWarps) {
+                float dot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                if (k < Kcb) {
+                    const float4* cp = reinterpret_cast<const float4*>(codebook + (size_t)k * D);
+#pragma unroll
+                    for (int q = 0; q < D / 4; ++q) {
+                        const float4 c = __ldg(cp + q);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if (q == 0) dot[j] = __fmul_rn(xg[j][0], c.x);
+                            else dot[j] = __fadd_rn(dot[j], __fmul_rn(xg[j][4 * q], c.x));
+                            dot[j] = __fadd_rn(dot[j], __fmul_rn(xg[j][4 * q + 1], c.y));
+                            dot[j] = __fadd_rn(dot[j], __fmul_rn(xg[j][4 * q + 2], c.z));
+                            dot[j] = __fadd_rn(dot[j], __fmul_rn(xg[j][4 * q + 3], c.w));
+                        }
+                    }
+                }
+                out[k * 64] = dot[0];
+                out[k * 64 + 32] = dot[1];
+                out[k * 64 + 16384] = dot[2];
+                out[k * 64 + 16384 + 32] = dot[3];
+            }
+        }
+        __syncthreads();
+    }
+
+    struct Entries { float v0, v1, v2, v3; };
+    __device__ __forceinline__ Entries gather(uint32_t w, uint32_t tb) const {
+        Entries e;
+        e.v0 = ch_lds_f32<0>(ch_prmt(w, tb, 0x7604));
+        e.v1 = ch_lds_f32<128>(ch_prmt(w, tb, 0x7614));
+        e.v2 = ch_lds_f32<65536>(ch_prmt(w, tb, 0x7624));
+        e.v3 = ch_lds_f32<65536 + 128>(ch_prmt(w, tb, 0x7634));
+        return e;
+    }
+
+    // How this lane takes part in the walk of one slice.  A slice of at most 64 groups needs only 16 lanes per
+    // row, so the warp runs two chains (lanes 0..15 on the first part of its rows, lanes 16..31 on the rest); a
+    // ring slot then holds one row of each chain in its two halves.
+    struct Plan {
+        int rb, nu, nu0, nact;     // first row and row count of the warp, rows of chain 0, lanes of a chain
+        int pos, mine;             // place of the lane in its chain, chain of the lane
+        uint32_t ring;
+        // requests: the lane copies 16-byte piece (lane>>3)*2 + (lane&1) of a slot, rows four apart in time
+        int k8, delta, rnu;
+        bool piece_ok;
+        const uint8_t* gpiece;
+        uint32_t rpiece;
+    };
+    __device__ __forceinline__ Plan make_plan(int s, int W) const {
+        Plan p;
+        const int per = ((n + kWarps - 1) / kWarps + 3) & ~3;
+        p.rb = min(n, warp * per);
+        p.nu = min(n, p.rb + per) - p.rb;
+        const bool half = W <= 64;
+        p.nact = W >> 2;
+        p.nu0 = half ? min(p.nu, (((p.nu + 1) >> 1) + 3) & ~3) : p.nu;
+        p.pos = half ? (lane & 15) : lane;
+        p.mine = half ? (lane >> 4) : 0;
+        p.ring = warp < kChLoWarps ? kChRingLo + warp * kChRingBytes : kChRingHi + (warp - kChLoWarps) * kChRingBytes;
+        const int piece = 2 * (lane >> 3) + (lane & 1);
+        p.delta = (lane & 7) >> 1;
+        p.k8 = half ? ((lane >> 3) & 1) * 8 : (lane >> 3) * 8;
+        const int src_byte = half ? (piece & 3) * 16 : piece * 16;
+        p.rnu = p.mine ? p.nu - p.nu0 : p.nu0;
+        p.piece_ok = src_byte < W;
+        p.gpiece = base + (size_t)(p.rb + (p.mine ? p.nu0 : 0)) * G + s * SG + src_byte;
+        p.rpiece = p.ring + piece * 16;
+        return p;
+    }
+    __device__ __forceinline__ void request(const Plan& p, int t) const {
+        const int u = t + kLead - p.k8 + p.delta;
+        if (p.piece_ok && (unsigned)u < (unsigned)p.rnu) {
+            const uint32_t dst = p.rpiece + (u & (kSlots - 1)) * kSlotBytes;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(p.gpiece + (size_t)u * G) : "memory");
+        }
+        cp_async_commit();
+    }
+    // First requests of a slice; the warp's ring is idle since its previous walk ended, so this runs before the
+    // table build and the memory latency hides behind it.
+    __device__ __forceinline__ void prefetch(int s, int W) const {
+        const Plan p = make_plan(s, W);
+#pragma unroll
+        for (int t = -kPrologue; t < 0; t += 4) request(p, t);
+    }
+
+    // Adds the entries of slice s (W groups) to the parked sums of this warp's rows (after prefetch(s, W)).
+    template <bool FIRST>
+    __device__ __forceinline__ void walk(int s, int W) const {
+        const Plan p = make_plan(s, W);
+        if (p.nu <= 0) {
+            cp_async_wait<0>();
+            return;
+        }
+        cp_async_wait<5>();
+        __syncwarp();
+
+        const uint32_t tb = kChTab | (lane * 4);
+        // word of this lane in the slot of row (step - pos); the slot index wraps inside the 4 KB ring
+        uint32_t pr = p.ring + (((0 - p.pos) & (kSlots - 1)) * kSlotBytes) + lane * 4;
+        auto next_word = [&]() {
+            const uint32_t w = ch_lds_u32(pr);
+            pr = (pr & ~(uint32_t)(kChRingBytes - 1)) | ((pr + kSlotBytes) & (kChRingBytes - 1));
+            return w;
+        };
+        Entries cur = gather(next_word(), tb);   // step 0
+        uint32_t wnext = next_word();            // step 1
+        const int mynu = p.mine ? p.nu - p.nu0 : p.nu0;
+        float* accw = acc() + p.rb + ((p.mine && mynu > 0) ? p.nu0 : 0);   // 16-byte aligned: rb and nu0 are multiples of 4
+        const bool head = p.pos == 0;
+        const bool tail = p.pos == p.nact - 1;
+        // sums to start rows step .. step+3 from (used by the head lane); reads past the warp's rows stay inside shared memory
+        float4 start4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (!FIRST) start4 = *reinterpret_cast<const float4*>(accw);
+        float run = 0.0f;
+        const int steps = p.nu0 + p.nact - 1;
+        int t0 = 0;
+        for (; t0 < steps; t0 += 4) {
+            request(p, t0);
+            cp_async_wait<5>();
+            __syncwarp();
+            float4 startn = start4;
+            if (!FIRST) startn = *reinterpret_cast<const float4*>(accw + t0 + 4);
+            float hold[4];                                             // sums of rows t0-1-pos .. t0+2-pos
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t w2 = next_word();                       // step t0 + i + 2
+                hold[i] = run;
+                float sum = __shfl_up_sync(0xffffffffu, run, 1);
+                if (head) sum = i == 0 ? start4.x : i == 1 ? start4.y : i == 2 ? start4.z : start4.w;
+                const Entries nxt = gather(wnext, tb);                 // step t0 + i + 1
+                sum = __fadd_rn(sum, cur.v0);
+                sum = __fadd_rn(sum, cur.v1);
+                sum = __fadd_rn(sum, cur.v2);
+                sum = __fadd_rn(sum, cur.v3);
+                run = sum;
+                cur = nxt;
+                wnext = w2;
+            }
+            start4 = startn;
+            if (tail) {
+                const int ub = t0 - 1 - p.pos;                         // a multiple of 4 for the tail lane
+                if (ub >= 0 && ub + 3 < mynu) {
+                    *reinterpret_cast<float4*>(accw + ub) = make_float4(hold[0], hold[1], hold[2], hold[3]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if ((unsigned)(ub + i) < (unsigned)mynu) accw[ub + i] = hold[i];
+                }
+            }
+        }
+        {
+            const int uprev = t0 - 1 - p.pos;
+            if (tail && (unsigned)uprev < (unsigned)mynu) accw[uprev] = run;
+        }
+        cp_async_wait<0>();
+    }
+
+    // Leaves acc()[lr] = sum_{g<G} LUT_x[g, code[lr, g]] for lr < n.  All threads of the CTA must call it; on
+    // return a __syncthreads() has NOT yet been executed.  `before_last` runs once, after the table of the last
+    // slice is built.
+    template <class F>
+    __device__ void run(const XLoad& xl, const float* __restrict__ codebook, int Kcb, F before_last) const {
+        for (int s = 0; s < nslices; ++s) {
+            const int g0 = s * SG, ng = min(SG, G - g0);
+            float xr[kXPerThread];
+            load_x(g0, ng, xl, xr);
+            __syncthreads();  // every warp has left the previous slice's table and activations
+            prefetch(s, ng);
+            build_slice(ng, xr, codebook, Kcb);
+            if (s == nslices - 1) before_last();
+            if (s == 0) walk<true>(s, ng);
+            else walk<false>(s, ng);
+        }
+    }
+};
+
+}  // namespace ojx

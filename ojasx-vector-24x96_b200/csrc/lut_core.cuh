@@ -335,17 +335,43 @@ __device__ __forceinline__ void csr_prefetch_l2(const CsrView& csr, int row0, in
     for (int r = threadIdx.x * 32; r <= n; r += kThreads * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(csr.row_ptrs + row0 + r));
 }
 
-__device__ __forceinline__ void csr_rows_to_smem(CoreSmem& sm, const CsrView& csr, int row0, int n, int oacc_off,
+// `area` is a 128 KB region of shared memory that is idle after the row walk (the table), `rp` room for n + 1 ints.
+__device__ __forceinline__ void csr_rows_to_area(float* area, int* rp, const CsrView& csr, int row0, int n, int oacc_off,
                                                  const XLoad& xl) {
-    float* oacc = sm.lut + oacc_off;
-    float* xsm = sm.lut + kCsrOaccFloats;
+    float* oacc = area + oacc_off;
+    float* xsm = area + kCsrOaccFloats;
     float* prod = xsm + kCsrXFloats;
-    int* rp = reinterpret_cast<int*>(sm.ring);  // the code ring is idle between row walks
     const bool x_in_smem = xl.K <= kCsrXFloats;
-    for (int lr = threadIdx.x; lr <= n; lr += kThreads) rp[lr] = csr.row_ptrs[row0 + lr];
-    for (int lr = threadIdx.x; lr < n; lr += kThreads) oacc[lr] = 0.0f;
-    if (x_in_smem)
-        for (int k = threadIdx.x; k < xl.K; k += kThreads) xsm[k] = xl(k);
+    // loads first, stores after: the compiler cannot tell that the shared stores leave the global arrays alone
+    for (int b0 = threadIdx.x; b0 <= n; b0 += kThreads * kCsrUnroll) {
+        int v[kCsrUnroll];
+#pragma unroll
+        for (int u = 0; u < kCsrUnroll; ++u) {
+            const int lr = b0 + u * kThreads;
+            v[u] = lr <= n ? csr.row_ptrs[row0 + lr] : 0;
+        }
+#pragma unroll
+        for (int u = 0; u < kCsrUnroll; ++u) {
+            const int lr = b0 + u * kThreads;
+            if (lr <= n) rp[lr] = v[u];
+            if (lr < n) oacc[lr] = 0.0f;
+        }
+    }
+    if (x_in_smem) {
+        for (int b0 = threadIdx.x; b0 < xl.K; b0 += kThreads * kCsrUnroll) {
+            float v[kCsrUnroll];
+#pragma unroll
+            for (int u = 0; u < kCsrUnroll; ++u) {
+                const int k = b0 + u * kThreads;
+                v[u] = k < xl.K ? xl(k) : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < kCsrUnroll; ++u) {
+                const int k = b0 + u * kThreads;
+                if (k < xl.K) xsm[k] = v[u];
+            }
+        }
+    }
     __syncthreads();
     const int jb = rp[0], je = rp[n];
     for (int jc = jb; jc < je; jc += kCsrChunk) {
@@ -377,6 +403,12 @@ __device__ __forceinline__ void csr_rows_to_smem(CoreSmem& sm, const CsrView& cs
         }
         __syncthreads();
     }
+}
+
+__device__ __forceinline__ void csr_rows_to_smem(CoreSmem& sm, const CsrView& csr, int row0, int n, int oacc_off,
+                                                 const XLoad& xl) {
+    // the code ring is idle between row walks
+    csr_rows_to_area(sm.lut, reinterpret_cast<int*>(sm.ring), csr, row0, n, oacc_off, xl);
 }
 
 }  // namespace ojx
