@@ -222,6 +222,59 @@ struct ChainWalker {
         for (int t = -kPrologue; t < 0; t += 4) request(p, t);
     }
 
+    // State of a lane between steps of the walk.
+    struct Lane {
+        uint32_t pr;        // shared address of the lane's word in the slot of the row it reads next
+        uint32_t tb;        // table half 0 | lane*4
+        Entries cur;        // entries of the step about to be added
+        uint32_t wnext;     // code word of the step after
+        float run;          // sum after the lane's last step
+        // requests (incremental: row index, slot address, source address)
+        int ru;
+        unsigned rlim;
+        uint32_t rdst;
+        const uint8_t* rsrc;
+        size_t rstride;
+    };
+    __device__ __forceinline__ uint32_t next_word(Lane& L) const {
+        const uint32_t w = ch_lds_u32(L.pr);
+        L.pr = (L.pr & ~(uint32_t)(kChRingBytes - 1)) | ((L.pr + kSlotBytes) & (kChRingBytes - 1));
+        return w;
+    }
+    __device__ __forceinline__ void next_request(Lane& L) const {
+        asm volatile(
+            "{\n .reg .pred p;\n setp.lt.u32 p, %2, %3;\n @p cp.async.cg.shared.global [%0], [%1], 16;\n cp.async.commit_group;\n}\n" ::"r"(L.rdst),
+            "l"(L.rsrc), "r"(L.ru), "r"(L.rlim)
+            : "memory");
+        L.ru += 4;
+        L.rsrc += L.rstride;
+        L.rdst = (L.rdst & ~(uint32_t)(kChRingBytes - 1)) | ((L.rdst + 4 * kSlotBytes) & (kChRingBytes - 1));
+    }
+    // Four steps.  `use` holds the sums the head lane starts the four rows from; the tail lane parks the four sums
+    // that the previous four steps completed (rows ub .. ub+3, ub a multiple of 4; rows past the chain's last one
+    // belong to nobody -- row counts of warps and chains are multiples of 4 except at the end of the work item).
+    __device__ __forceinline__ void four_steps(Lane& L, const float4& use, bool head, uint32_t park_addr, int ub, unsigned park_lim) const {
+        float hold[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t w2 = next_word(L);
+            hold[i] = L.run;
+            float sum = __shfl_up_sync(0xffffffffu, L.run, 1);
+            if (head) sum = i == 0 ? use.x : i == 1 ? use.y : i == 2 ? use.z : use.w;
+            const Entries nxt = gather(L.wnext, L.tb);
+            sum = __fadd_rn(sum, L.cur.v0);
+            sum = __fadd_rn(sum, L.cur.v1);
+            sum = __fadd_rn(sum, L.cur.v2);
+            sum = __fadd_rn(sum, L.cur.v3);
+            L.run = sum;
+            L.cur = nxt;
+            L.wnext = w2;
+        }
+        asm volatile("{\n .reg .pred p;\n setp.lt.u32 p, %5, %6;\n @p st.shared.v4.f32 [%0], {%1, %2, %3, %4};\n}\n" ::"r"(park_addr),
+                     "f"(hold[0]), "f"(hold[1]), "f"(hold[2]), "f"(hold[3]), "r"(ub), "r"(park_lim)
+                     : "memory");
+    }
+
     // Adds the entries of slice s (W groups) to the parked sums of this warp's rows (after prefetch(s, W)).
     template <bool FIRST>
     __device__ __forceinline__ void walk(int s, int W) const {
@@ -233,64 +286,45 @@ struct ChainWalker {
         cp_async_wait<5>();
         __syncwarp();
 
-        const uint32_t tb = kChTab | (lane * 4);
-        // word of this lane in the slot of row (step - pos); the slot index wraps inside the 4 KB ring
-        uint32_t pr = p.ring + (((0 - p.pos) & (kSlots - 1)) * kSlotBytes) + lane * 4;
-        auto next_word = [&]() {
-            const uint32_t w = ch_lds_u32(pr);
-            pr = (pr & ~(uint32_t)(kChRingBytes - 1)) | ((pr + kSlotBytes) & (kChRingBytes - 1));
-            return w;
-        };
-        Entries cur = gather(next_word(), tb);   // step 0
-        uint32_t wnext = next_word();            // step 1
+        Lane L;
+        L.tb = kChTab | (lane * 4);
+        L.pr = p.ring + (((0 - p.pos) & (kSlots - 1)) * kSlotBytes) + lane * 4;
+        L.cur = gather(next_word(L), L.tb);   // step 0
+        L.wnext = next_word(L);               // step 1
+        L.run = 0.0f;
+        L.ru = kLead - p.k8 + p.delta;        // request of step 0
+        L.rlim = p.piece_ok ? (unsigned)p.rnu : 0u;
+        L.rdst = p.rpiece + (L.ru & (kSlots - 1)) * kSlotBytes;
+        L.rsrc = p.gpiece + (ptrdiff_t)L.ru * G;
+        L.rstride = (size_t)4 * G;
         const int mynu = p.mine ? p.nu - p.nu0 : p.nu0;
-        float* accw = acc() + p.rb + ((p.mine && mynu > 0) ? p.nu0 : 0);   // 16-byte aligned: rb and nu0 are multiples of 4
+        const int row0 = p.rb + ((p.mine && mynu > 0) ? p.nu0 : 0);   // a multiple of 4: rb and nu0 are
+        const float* accw = acc() + row0;
         const bool head = p.pos == 0;
         const bool tail = p.pos == p.nact - 1;
+        const unsigned park_lim = tail ? (unsigned)mynu : 0u;
+        int ub = -1 - p.pos;                                           // row whose sum `run` holds at step 0
+        uint32_t park = kChAcc + (uint32_t)(row0 + ub) * 4;
         // sums to start rows step .. step+3 from (used by the head lane); reads past the warp's rows stay inside shared memory
-        float4 start4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        if (!FIRST) start4 = *reinterpret_cast<const float4*>(accw);
-        float run = 0.0f;
+        float4 sa = make_float4(0.0f, 0.0f, 0.0f, 0.0f), sb = sa;
+        if (!FIRST) sa = *reinterpret_cast<const float4*>(accw);
         const int steps = p.nu0 + p.nact - 1;
         int t0 = 0;
-        for (; t0 < steps; t0 += 4) {
-            request(p, t0);
+        for (; t0 < steps; t0 += 8) {
+            next_request(L);
             cp_async_wait<5>();
             __syncwarp();
-            float4 startn = start4;
-            if (!FIRST) startn = *reinterpret_cast<const float4*>(accw + t0 + 4);
-            float hold[4];                                             // sums of rows t0-1-pos .. t0+2-pos
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t w2 = next_word();                       // step t0 + i + 2
-                hold[i] = run;
-                float sum = __shfl_up_sync(0xffffffffu, run, 1);
-                if (head) sum = i == 0 ? start4.x : i == 1 ? start4.y : i == 2 ? start4.z : start4.w;
-                const Entries nxt = gather(wnext, tb);                 // step t0 + i + 1
-                sum = __fadd_rn(sum, cur.v0);
-                sum = __fadd_rn(sum, cur.v1);
-                sum = __fadd_rn(sum, cur.v2);
-                sum = __fadd_rn(sum, cur.v3);
-                run = sum;
-                cur = nxt;
-                wnext = w2;
-            }
-            start4 = startn;
-            if (tail) {
-                const int ub = t0 - 1 - p.pos;                         // a multiple of 4 for the tail lane
-                if (ub >= 0 && ub + 3 < mynu) {
-                    *reinterpret_cast<float4*>(accw + ub) = make_float4(hold[0], hold[1], hold[2], hold[3]);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        if ((unsigned)(ub + i) < (unsigned)mynu) accw[ub + i] = hold[i];
-                }
-            }
+            if (!FIRST) sb = *reinterpret_cast<const float4*>(accw + t0 + 4);
+            four_steps(L, sa, head, park, ub, park_lim);
+            next_request(L);
+            cp_async_wait<5>();
+            __syncwarp();
+            if (!FIRST) sa = *reinterpret_cast<const float4*>(accw + t0 + 8);
+            four_steps(L, sb, head, park + 16, ub + 4, park_lim);
+            ub += 8;
+            park += 32;
         }
-        {
-            const int uprev = t0 - 1 - p.pos;
-            if (tail && (unsigned)uprev < (unsigned)mynu) accw[uprev] = run;
-        }
+        if (tail && (unsigned)ub < (unsigned)mynu) acc()[row0 + ub] = L.run;
         cp_async_wait<0>();
     }
 
