@@ -63,7 +63,9 @@ lut_linear_kernel(const LinearProblem* __restrict__ probs, int nprobs, int total
         }
         if (P.G == 0)
             for (int lr = threadIdx.x; lr < n; lr += kThreads) accp[lr] = 0.0f;
-        auto ask_l2 = [&]() { if (P.csr.nnz > 0) csr_prefetch_l2(P.csr, r0, n); };
+        // (Asking L2 for the outlier arrays ahead of the epilogue was measured and costs 5 %: with the code stream
+        // running close to the DRAM limit the lines are gone again before they are used.)
+        auto ask_l2 = [&]() {};
         if constexpr (D <= 16) {
             if (chain) ChainWalker<D>(smem_raw, rs.base0, n, P.G).run(xl, P.codebook, P.Kcb, ask_l2);
             else RowWalker<D>(sm, rs).run(xl, P.codebook, P.Kcb, ask_l2);

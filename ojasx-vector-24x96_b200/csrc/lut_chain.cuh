@@ -93,7 +93,7 @@ struct ChainWalker {
     // The walker needs whole 16-byte pieces of every row, four groups per lane and the layout above.
     __device__ static __forceinline__ bool usable(const unsigned char* raw, const uint8_t* codes, const float* codebook, int G) {
         return D <= 16 && (G & 15) == 0 && ((reinterpret_cast<uintptr_t>(codes) & 15) == 0) &&
-               ((reinterpret_cast<uintptr_t>(codebook) & 15) == 0) &&
+               ((reinterpret_cast<uintptr_t>(codebook) & 7) == 0) &&
                static_cast<uint32_t>(__cvta_generic_to_shared(raw)) == kChAcc;
     }
 
@@ -114,8 +114,24 @@ struct ChainWalker {
             }
         }
     }
-    __device__ __forceinline__ void build_slice(int ng, const float (&xr)[kXPerThread], const float* __restrict__ codebook,
-                                                int Kcb) const {
+    // Centroids of a warp: warp w builds the entries of centroids w, w+16, ..., 16 rows of D floats = 32 lanes x D/2
+    // floats.  Every lane loads its D/2 floats once per work item; the build broadcasts them with shuffles, so its
+    // loop has no global loads (a load per centroid from L2 cost about 700 clocks each under the code stream).
+    static constexpr int kCbRegs = D / 2;
+    static_assert(D % 4 == 0 && kCbRegs >= 2, "centroid pieces");
+    __device__ __forceinline__ void load_centroids(const float* __restrict__ codebook, int Kcb, float (&cr)[kCbRegs]) const {
+        const int flat = lane * kCbRegs;             // position in the warp's [16][D] array
+        const int k = warp + kWarps * (flat / D);
+        const float* src = codebook + (size_t)k * D + (flat % D);
+#pragma unroll
+        for (int r = 0; r < kCbRegs; r += 2) {
+            float2 v = make_float2(0.0f, 0.0f);
+            if (k < Kcb) v = __ldg(reinterpret_cast<const float2*>(src + r));
+            cr[r] = v.x;
+            cr[r + 1] = v.y;
+        }
+    }
+    __device__ __forceinline__ void build_slice(int ng, const float (&xr)[kXPerThread], const float (&cr)[kCbRegs], int Kcb) const {
         float* xs = at<float>(kChXs);
 #pragma unroll
         for (int q = 0; q < kXPerThread; ++q) {
@@ -127,32 +143,30 @@ struct ChainWalker {
         }
         __syncthreads();
         const int lpos = ng <= 64 ? (lane & 15) : lane;  // a slice of <= 64 groups is kept twice: lanes 16..31 mirror 0..15
-        if (4 * lpos < ng) {
-            float xg[4][D];
+        const bool mine = 4 * lpos < ng;
+        float xg[4][D];
 #pragma unroll
-            for (int d = 0; d < D; ++d) {
-                const float4 v = *reinterpret_cast<const float4*>(xs + d * SG + 4 * lpos);
-                xg[0][d] = v.x; xg[1][d] = v.y; xg[2][d] = v.z; xg[3][d] = v.w;
-            }
-            float* out = table() + lane;
+        for (int d = 0; d < D; ++d) {
+            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (mine) v = *reinterpret_cast<const float4*>(xs + d * SG + 4 * lpos);
+            xg[0][d] = v.x; xg[1][d] = v.y; xg[2][d] = v.z; xg[3][d] = v.w;
+        }
+        float* out = table() + lane;
 #pragma unroll 2
-            for (int k = warp; k < 256; k += kWarps) {
-                float dot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                if (k < Kcb) {
-                    const float4* cp = reinterpret_cast<const float4*>(codebook + (size_t)k * D);
+        for (int i = 0; i < 256 / kWarps; ++i) {
+            const int k = warp + kWarps * i;
+            float c[D];
 #pragma unroll
-                    for (int q = 0; q < D / 4; ++q) {
-                        const float4 c = __ldg(cp + q);
+            for (int d = 0; d < D; ++d) c[d] = __shfl_sync(0xffffffffu, cr[d % kCbRegs], 2 * i + (d >= kCbRegs ? 1 : 0));
+            float dot[4];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            if (q == 0) dot[j] = __fmul_rn(xg[j][0], c.x);
-                            else dot[j] = __fadd_rn(dot[j], __fmul_rn(xg[j][4 * q], c.x));
-                            dot[j] = __fadd_rn(dot[j], __fmul_rn(xg[j][4 * q + 1], c.y));
-                            dot[j] = __fadd_rn(dot[j], __fmul_rn(xg[j][4 * q + 2], c.z));
-                            dot[j] = __fadd_rn(dot[j], __fmul_rn(xg[j][4 * q + 3], c.w));
-                        }
-                    }
-                }
+            for (int j = 0; j < 4; ++j) {
+                dot[j] = __fmul_rn(xg[j][0], c[0]);
+#pragma unroll
+                for (int d = 1; d < D; ++d) dot[j] = __fadd_rn(dot[j], __fmul_rn(xg[j][d], c[d]));
+                if (k >= Kcb) dot[j] = 0.0f;
+            }
+            if (mine) {
                 out[k * 64] = dot[0];
                 out[k * 64 + 32] = dot[1];
                 out[k * 64 + 16384] = dot[2];
@@ -333,13 +347,15 @@ struct ChainWalker {
     // slice is built.
     template <class F>
     __device__ void run(const XLoad& xl, const float* __restrict__ codebook, int Kcb, F before_last) const {
+        float cr[kCbRegs];
+        load_centroids(codebook, Kcb, cr);
         for (int s = 0; s < nslices; ++s) {
             const int g0 = s * SG, ng = min(SG, G - g0);
             float xr[kXPerThread];
             load_x(g0, ng, xl, xr);
             __syncthreads();  // every warp has left the previous slice's table and activations
             prefetch(s, ng);
-            build_slice(ng, xr, codebook, Kcb);
+            build_slice(ng, xr, cr, Kcb);
             if (s == nslices - 1) before_last();
             if (s == 0) walk<true>(s, ng);
             else walk<false>(s, ng);

@@ -320,7 +320,7 @@ __global__ void __launch_bounds__(256) lut_prebuild_kernel(const void* __restric
 constexpr int kCsrOaccFloats = 8192;                                   // >= kAccRows
 constexpr int kCsrXFloats = 8192;                                      // activations staged when K fits
 constexpr int kCsrChunk = kSliceGroups * 256 - kCsrOaccFloats - kCsrXFloats;  // products per pass
-constexpr int kCsrUnroll = 8;
+constexpr int kCsrUnroll = 16;
 static_assert(kCsrOaccFloats >= kAccRows, "outlier sums need one slot per row");
 static_assert((kAccRows + 1) * sizeof(int) <= sizeof(CoreSmem::ring), "row pointers are staged in the ring area");
 
