@@ -75,6 +75,27 @@ lut_linear_kernel(const LinearProblem* __restrict__ probs, int nprobs, int total
         __syncthreads();
 
         // Epilogue (ojasx_lut_cpu.cpp:178-182 then :117-127): scale, bias, outlier row, one store.
+        auto store_y = [&](int m, float res) {
+            const size_t o = (size_t)b * rows_out + (m - P.row_start);
+            if (P.io_dtype == OJX_BF16) reinterpret_cast<__nv_bfloat16*>(P.y)[o] = __float2bfloat16_rn(res);
+            else reinterpret_cast<float*>(P.y)[o] = res;
+        };
+        if constexpr (D <= 16) {
+            if (chain) {
+                // every warp finishes the rows it walked; only the staging of x needs the whole CTA
+                const ChainWalker<D> cw(smem_raw, rs.base0, n, P.G);
+                const float* xsm = nullptr;
+                if (P.csr.nnz > 0 && P.K <= kCsrXFloats) {
+                    float* xw = cw.epilogue_x();
+                    for (int k = threadIdx.x; k < P.K; k += kThreads) xw[k] = xl(k);
+                    __syncthreads();
+                    xsm = xw;
+                }
+                cw.warp_epilogue(P.csr, r0, P.scales, P.bias, xsm, xl, store_y);
+                __syncthreads();
+                continue;
+            }
+        }
         if (P.csr.nnz > 0) csr_rows_to_area(area, rp, P.csr, r0, n, 0, xl);
         for (int lr = threadIdx.x; lr < n; lr += kThreads) {
             const int m = r0 + lr;

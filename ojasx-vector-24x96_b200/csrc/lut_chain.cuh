@@ -342,6 +342,88 @@ struct ChainWalker {
         cp_async_wait<0>();
     }
 
+    // Epilogue of the warp's own rows (ojasx_lut_cpu.cpp:178-182 then :117-127): y = (sum * scale + bias) + outlier
+    // row sum, the outlier sum formed on its own from zero in entry order, multiply then add.  Each warp finishes
+    // the rows it walked, so apart from the staging of x there is no CTA-wide barrier: the warp copies its row
+    // pointers into its (idle) code ring, then takes 128 rows at a time -- all lanes multiply the entries of those
+    // rows into the warp's part of the (idle) table area with coalesced loads of (col, val), then lane l adds the
+    // products of rows l, l+32, l+64, l+96 in order.  `xsm` is x staged in shared memory by the CTA (null: x is read
+    // from global memory).  Call after a __syncthreads() that follows the staging.
+    static constexpr int kEpiRows = 128;
+    static constexpr int kEpiProducts = 1536;   // products per pass of a warp: (128 KB - 32 KB of x) / 16 warps
+    static constexpr int kEpiUnroll = 16;
+    __device__ __forceinline__ float* epilogue_x() const { return table(); }
+    template <class Store>
+    __device__ __forceinline__ void warp_epilogue(const CsrView& csr, int row0, const float* __restrict__ scales,
+                                                  const float* __restrict__ bias, const float* xsm, const XLoad& xl,
+                                                  Store store) const {
+        const int per = ((n + kWarps - 1) / kWarps + 3) & ~3;
+        const int rb = min(n, warp * per);
+        const int nu = min(n, rb + per) - rb;
+        if (nu <= 0) return;
+        const bool has = csr.nnz > 0;
+        const uint32_t ring = warp < kChLoWarps ? kChRingLo + warp * kChRingBytes : kChRingHi + (warp - kChLoWarps) * kChRingBytes;
+        int* rpw = at<int>(ring);                                   // nu + 1 <= 433 row pointers
+        float* prod = table() + kCsrXFloats + warp * kEpiProducts;
+        const float* accw = acc() + rb;
+        if (has) {
+            for (int i = lane; i <= nu; i += 32) rpw[i] = csr.row_ptrs[row0 + rb + i];
+            __syncwarp();
+        }
+        for (int q0 = 0; q0 < nu; q0 += kEpiRows) {
+            const int R = min(kEpiRows, nu - q0);
+            float osum[kEpiRows / 32];
+#pragma unroll
+            for (int i = 0; i < kEpiRows / 32; ++i) osum[i] = 0.0f;
+            if (has) {
+                const int jb = rpw[q0], je = rpw[q0 + R];
+                for (int jc = jb; jc < je; jc += kEpiProducts) {
+                    const int ce = min(jc + kEpiProducts, je);
+                    for (int base = jc + lane; base < ce; base += 32 * kEpiUnroll) {
+                        int col[kEpiUnroll];
+                        float val[kEpiUnroll];
+#pragma unroll
+                        for (int u = 0; u < kEpiUnroll; ++u) {
+                            const int j = base + u * 32;
+                            col[u] = j < ce ? csr.cols[j] : 0;
+                            val[u] = j < ce ? csr.vals[j] : 0.0f;
+                        }
+#pragma unroll
+                        for (int u = 0; u < kEpiUnroll; ++u) {
+                            const int j = base + u * 32;
+                            const float xv = xsm ? xsm[col[u]] : xl(col[u]);
+                            if (j < ce) prod[j - jc] = __fmul_rn(val[u], xv);
+                        }
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < kEpiRows / 32; ++i) {
+                        const int row = q0 + lane + 32 * i;
+                        if (row < q0 + R) {
+                            const int sb = max(rpw[row], jc), se = min(rpw[row + 1], ce);
+                            float a = osum[i];
+                            for (int j = sb; j < se; ++j) a = __fadd_rn(a, prod[j - jc]);
+                            osum[i] = a;
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < kEpiRows / 32; ++i) {
+                const int row = q0 + lane + 32 * i;
+                if (row < q0 + R) {
+                    const int m = row0 + rb + row;
+                    float res = accw[row];
+                    if (scales) res = __fmul_rn(res, scales[m]);
+                    if (bias) res = __fadd_rn(res, bias[m]);
+                    if (has) res = __fadd_rn(res, osum[i]);
+                    store(m, res);
+                }
+            }
+        }
+    }
+
     // Leaves acc()[lr] = sum_{g<G} LUT_x[g, code[lr, g]] for lr < n.  All threads of the CTA must call it; on
     // return a __syncthreads() has NOT yet been executed.  `before_last` runs once, after the table of the last
     // slice is built.
