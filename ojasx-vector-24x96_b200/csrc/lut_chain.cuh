@@ -369,6 +369,12 @@ struct ChainWalker {
         if (has) {
             for (int i = lane; i <= nu; i += 32) rpw[i] = csr.row_ptrs[row0 + rb + i];
             __syncwarp();
+            // ask for all of the warp's entries at once (a 128-byte line per lane and step), so that the loads
+            // below find them on their way or in L2 instead of paying a DRAM round trip per batch
+            for (int j = (rpw[0] & ~31) + lane * 32; j < rpw[nu]; j += 32 * 32) {
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(csr.cols + j));
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(csr.vals + j));
+            }
         }
         for (int q0 = 0; q0 < nu; q0 += kEpiRows) {
             const int R = min(kEpiRows, nu - q0);
