@@ -354,7 +354,7 @@ def run_ours(args):
 
 # DRAM bytes (read + write) per 2560->6912 layer of lut_linear_kernel<8> from the ncu capture
 # summarised in profiles/; None until a capture exists.
-TRAFFIC_PER_LAYER = 4557432   # 674.5 MB per 148-layer launch (profiles/lut_linear_kernel_gemv_2560x6912.md)
+TRAFFIC_PER_LAYER = 4142938   # 613.2 MB per 148-layer launch (profiles/lut_linear_kernel_gemv_2560x6912.md)
 
 
 def bench_moe(args, dev, rank, world):
