@@ -22,6 +22,8 @@ __device__ __forceinline__ const LinearProblem& find_problem(const LinearProblem
     return probs[lo];
 }
 
+constexpr int kChainMinRows = 32 * kWarps;
+
 template <int D>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 lut_linear_kernel(const LinearProblem* __restrict__ probs, int nprobs, int total_items,
@@ -49,7 +51,8 @@ lut_linear_kernel(const LinearProblem* __restrict__ probs, int nprobs, int total
 
         // Lanes share a row (conflict-free gathers) whenever the code rows split into 16-byte pieces.
         bool chain = false;
-        if constexpr (D <= 16) chain = chain_walk && ChainWalker<D>::usable(smem_raw, rs.base0, P.codebook, P.G);
+        // (a chain needs 31 steps to fill and drain per slice: below 32 rows per warp the row-per-lane walk wins)
+        if constexpr (D <= 16) chain = chain_walk && n >= kChainMinRows && ChainWalker<D>::usable(smem_raw, rs.base0, P.codebook, P.G);
         float* accp = sm.acc;
         float* area = sm.lut;
         int* rp = reinterpret_cast<int*>(sm.ring);

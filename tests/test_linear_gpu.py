@@ -94,6 +94,48 @@ def test_linear_group_launch(cuda, oracle):
         assert np.array_equal(y[i, : w.out_features], want)
 
 
+@pytest.mark.parametrize("K,M,D,kcb,dtype", [
+    (2560, 1000, 8, 256, "f32"),    # G 320: slices of 128, 128 and 64 groups (two 16-lane chains), ragged last warp
+    (768, 600, 16, 256, "f32"),     # G 48: one slice of 48 groups, 12 lanes per chain
+    (640, 777, 4, 256, "f32"),      # G 160: 128 + 32
+    (6912, 520, 8, 256, "f32"),     # G 864: six full slices and one of 96 groups (24 of 32 lanes)
+    (1280, 515, 8, 16, "f32"),      # small codebook: table rows above it are zero
+    (2560, 1000, 8, 256, "bf16"),
+])
+def test_grouped_layers_walk_variants(cuda, oracle, monkeypatch, K, M, D, kcb, dtype):
+    """150 layers in one grouped launch (one work item per layer, so every warp walks a long run of rows): the walk
+    in which the lanes of a warp share a row and the walk with a row per lane give the same bits as the oracle
+    (row sums in ascending group order, ojasx_lut_cpu.cpp:161-175; scale, bias, outliers :178-182, :117-127)."""
+    rng = np.random.default_rng(K + M)
+    ws = []
+    for i in range(3):
+        w = synth.make_vq_linear(300 + i, K, M, block_dim=D, outlier_frac=0.01, with_scales=True, with_bias=True)
+        if kcb < 256:
+            w.codes = (w.codes % kcb).astype(np.uint8)
+            w.codebook = w.codebook[:kcb].copy()
+        ws.append(w)
+    layers = [ops.VQLinear(w.codebook, w.codes, w.scales, w.bias, w.csr, block_dim=D, codebook_size=kcb) for w in ws]
+    P = 150
+    group = ops.VQLinearGroup([layers[i % 3] for i in range(P)])
+    x = rng.standard_normal((P, K)).astype(np.float32)
+    if dtype == "bf16":
+        x = synth.to_bf16_f32(x)
+    xt = torch.from_numpy(x).to(cuda)
+    if dtype == "bf16":
+        xt = xt.bfloat16()
+    want = np.empty((P, M), np.float32)
+    for i, w in enumerate(ws):
+        want[i::3] = oracle.linear_forward(w.codebook, w.codes, w.scales, w.bias, w.csr, x[i::3], block_dim=D, codebook_size=kcb)
+    if dtype == "bf16":
+        want = synth.to_bf16_f32(want)
+    for walk in ("chain", "rows"):
+        monkeypatch.setenv("OJASX_B200_LINEAR_WALK", walk)
+        y = torch.zeros((P, M), device=cuda, dtype=xt.dtype)
+        group.forward(xt, y)
+        got = y.float().cpu().numpy()
+        assert np.array_equal(got, want), (walk, np.abs(got - want).max())
+
+
 def test_linear_errors(cuda):
     w = synth.make_vq_linear(1, 64, 32, block_dim=16, outlier_frac=0)
     layer = ops.VQLinear.from_weights(w)
