@@ -220,7 +220,12 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
     constexpr int kGp = R * D <= 32 ? 2 : 1;                                    // groups per value thread
     constexpr int kVu = 2;                                                      // tokens per step of a value thread
     const int G = P.G, hd = P.head_dim, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    float* lut = reinterpret_cast<float*>(smem_raw);               // [G][256][R]
+    float* lut = reinterpret_cast<float*>(smem_raw);               // [G][256][R], or [256][G][R] (see code_major)
+    // One 16-byte entry (R = 4) per (group, centroid) and 16 groups: the table is kept centroid-major, so that the
+    // entry of group g lies in 16-byte bank group g % 8 whatever the code is.  A score thread then walks the
+    // groups starting at its own (g = (i + lane) & 15 in step i): the eight lanes that a 128-bit shared load
+    // serves together read eight different bank groups, and the gather costs 4 wavefronts instead of 10.8.
+    const bool code_major = R == 4 && G == 16;
     const int vrep = P.v_copies;                                   // 1 or 8 copies of the value codebook
     float* vcb = lut + (size_t)G * 256 * R;                        // [D/4][256][vrep] float4
     float* qs = vcb + 256 * D * vrep;                              // [R*hd]
@@ -280,7 +285,7 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
                 for (int d = 0; d < D; ++d) dot = fmaf(qv[d], c[d], dot);
                 e[r] = dot;
             }
-            st_heads<R>(lut + ((size_t)g * 256 + cen) * R, e);
+            st_heads<R>(lut + (code_major ? (size_t)cen * 16 + g : (size_t)g * 256 + cen) * R, e);
         }
     }
     __syncthreads();
@@ -358,7 +363,45 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
 #pragma unroll
                 for (int j = 0; j < kTpt; ++j) vt[(size_t)gq * vrow + tid + j * kHalf] = vword[j];
             };
-            if (ahead) {
+            if (ahead && code_major) {
+                uint4 kw[kTpt], vw[kTpt];
+#pragma unroll
+                for (int j = 0; j < kTpt; ++j) {
+                    kw[j] = k_next[j];
+                    vw[j] = v_next[j];
+                }
+                if (it + 1 < n_passes) fetch(base + kSub);
+                // the 16 code bytes of a token, rotated so that byte i is the code of group (i + rot) & 15
+                const int rot = tid & 15, sh = (rot & 3) * 8;
+                unsigned rk[kTpt][4];
+#pragma unroll
+                for (int j = 0; j < kTpt; ++j) {
+                    unsigned a0 = __funnelshift_r(kw[j].x, kw[j].y, sh), a1 = __funnelshift_r(kw[j].y, kw[j].z, sh);
+                    unsigned a2 = __funnelshift_r(kw[j].z, kw[j].w, sh), a3 = __funnelshift_r(kw[j].w, kw[j].x, sh);
+                    if (rot & 4) { const unsigned t = a0; a0 = a1; a1 = a2; a2 = a3; a3 = t; }
+                    if (rot & 8) { unsigned t = a0; a0 = a2; a2 = t; t = a1; a1 = a3; a3 = t; }
+                    rk[j][0] = a0; rk[j][1] = a1; rk[j][2] = a2; rk[j][3] = a3;
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int goff = ((i + rot) & 15) * R;
+#pragma unroll
+                    for (int j = 0; j < kTpt; ++j) {
+                        const unsigned code = (rk[j][i >> 2] >> (8 * (i & 3))) & 255u;
+                        float e[R];
+                        ld_heads<R>(lut + code * (16 * R) + goff, e);
+#pragma unroll
+                        for (int r = 0; r < R; ++r) s[j][r] += e[r];
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < kTpt; ++j) {
+                    vt[(size_t)0 * vrow + tid + j * kHalf] = vw[j].x;
+                    vt[(size_t)1 * vrow + tid + j * kHalf] = vw[j].y;
+                    vt[(size_t)2 * vrow + tid + j * kHalf] = vw[j].z;
+                    vt[(size_t)3 * vrow + tid + j * kHalf] = vw[j].w;
+                }
+            } else if (ahead) {
                 uint4 kw[kTpt], vw[kTpt];
 #pragma unroll
                 for (int j = 0; j < kTpt; ++j) {

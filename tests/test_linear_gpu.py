@@ -100,6 +100,7 @@ def test_linear_group_launch(cuda, oracle):
     (640, 777, 4, 256, "f32"),      # G 160: 128 + 32
     (6912, 520, 8, 256, "f32"),     # G 864: six full slices and one of 96 groups (24 of 32 lanes)
     (1280, 515, 8, 16, "f32"),      # small codebook: table rows above it are zero
+    (9216, 512, 8, 256, "f32"),     # nine slices; x too long to stage for the outlier products
     (2560, 1000, 8, 256, "bf16"),
 ])
 def test_grouped_layers_walk_variants(cuda, oracle, monkeypatch, K, M, D, kcb, dtype):
