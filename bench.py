@@ -333,7 +333,8 @@ def run_ours(args):
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "layers_per_gpu": P, "step": "one grouped launch over all layers",
                        "cold_cache": f"inputs larger than L2: {P * alg / 1e6:.0f} MB of distinct layers per pass",
-                       "distinct_host_weight_sets": N_DISTINCT},
+                       "distinct_host_weight_sets": N_DISTINCT,
+                       "row_walk": "rows" if os.environ.get("OJASX_B200_LINEAR_WALK", "").startswith("r") else "lanes of a warp share a row"},
             "us_per_layer": round(ms_step * 1e3 / P, 4),
             "code_gbs": round(world * P * code_bytes / (ms_step * 1e-3) / 1e9, 2),
             "single_launch_hot_us": round(single_us, 2),
