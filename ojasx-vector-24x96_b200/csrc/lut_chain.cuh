@@ -152,6 +152,39 @@ struct ChainWalker {
             xg[0][d] = v.x; xg[1][d] = v.y; xg[2][d] = v.z; xg[3][d] = v.w;
         }
         float* out = table() + lane;
+        if (ng <= 64) {
+            // both halves of the warp hold the same groups: each half computes every second centroid and writes
+            // the entry into both copies (its own lane's bank and the mirror lane's)
+            float* mir = table() + (lane ^ 16);
+            const int h = lane >> 4;
+#pragma unroll 2
+            for (int ii = 0; ii < 128 / kWarps; ++ii) {
+                const int i = 2 * ii + h, k = warp + kWarps * i;
+                float c[D];
+#pragma unroll
+                for (int d = 0; d < D; ++d) c[d] = __shfl_sync(0xffffffffu, cr[d % kCbRegs], 2 * i + (d >= kCbRegs ? 1 : 0));
+                float dot[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    dot[j] = __fmul_rn(xg[j][0], c[0]);
+#pragma unroll
+                    for (int d = 1; d < D; ++d) dot[j] = __fadd_rn(dot[j], __fmul_rn(xg[j][d], c[d]));
+                    if (k >= Kcb) dot[j] = 0.0f;
+                }
+                if (mine) {
+                    out[k * 64] = dot[0];
+                    out[k * 64 + 32] = dot[1];
+                    out[k * 64 + 16384] = dot[2];
+                    out[k * 64 + 16384 + 32] = dot[3];
+                    mir[k * 64] = dot[0];
+                    mir[k * 64 + 32] = dot[1];
+                    mir[k * 64 + 16384] = dot[2];
+                    mir[k * 64 + 16384 + 32] = dot[3];
+                }
+            }
+            __syncthreads();
+            return;
+        }
 #pragma unroll 2
         for (int i = 0; i < 256 / kWarps; ++i) {
             const int k = warp + kWarps * i;
