@@ -64,6 +64,10 @@ lut_linear_kernel(const LinearProblem* __restrict__ probs, int nprobs, int total
                 rp = cw.ring_hi_ints();
             }
         }
+        // A work item that took the shared-row walk ends without a barrier (its warps finish their rows on their
+        // own); the next one starts with loads into registers and meets the others at its first table build.
+        // Anything that writes shared memory earlier than that waits here for the slower warps.
+        if (!chain || P.G == 0) __syncthreads();
         if (P.G == 0)
             for (int lr = threadIdx.x; lr < n; lr += kThreads) accp[lr] = 0.0f;
         // (Asking L2 for the outlier arrays ahead of the epilogue was measured and costs 5 %: with the code stream
@@ -95,7 +99,6 @@ lut_linear_kernel(const LinearProblem* __restrict__ probs, int nprobs, int total
                     xsm = xw;
                 }
                 cw.warp_epilogue(P.csr, r0, P.scales, P.bias, xsm, xl, store_y);
-                __syncthreads();
                 continue;
             }
         }
