@@ -143,7 +143,9 @@ OJASX_API int ojasx_b200_rvq_fused_gemm(const uint8_t* packed_codes, const float
 /* One launch over many independent linear handles (no counterpart in the reference, which
  * runs one layer per call): problem p reads d_x + p*x_stride_bytes and writes
  * d_y + p*y_stride_bytes.  x_stride_bytes == 0 feeds every layer the same activations
- * (q/k/v, gate/up).  All handles must share block_dim. */
+ * (q/k/v, gate/up).  All handles must share block_dim and must outlive the group (the group
+ * borrows them; outliers set on a member after the group was made are picked up by the next
+ * forward). */
 typedef void* OjasxLinearGroupHandle;
 OJASX_API OjasxLinearGroupHandle ojasx_b200_create_linear_group(const OjasxLinearHandle* handles, int count);
 OJASX_API int ojasx_b200_linear_group_forward(OjasxLinearGroupHandle group, const void* d_x,
@@ -156,7 +158,9 @@ OJASX_API void ojasx_b200_destroy_linear_group(OjasxLinearGroupHandle group);
  * are [n_tokens, k_active] with GLOBAL expert ids; ids outside this handle's experts and
  * weights with |w| < 1e-8 are skipped (ojasx_lut_cpu.cpp:284-286).  The first call with a
  * larger n_tokens*k_active grows the handle's scratch (cudaMalloc); ojasx_b200_moe_reserve
- * does that ahead of time. */
+ * does that ahead of time.  The handle's device must be the current device (-1 otherwise), and a
+ * handle serves one stream at a time: its scratch is shared by every call on it, so calls on
+ * different streams must be ordered by the caller. */
 OJASX_API int ojasx_b200_moe_forward(OjasxMoEHandle handle, const void* d_x, const int* d_topk_idx,
                                      const float* d_topk_w, void* d_y, int n_tokens, int k_active, int io_dtype,
                                      void* stream);
@@ -249,7 +253,10 @@ OJASX_API int ojasx_b200_add_int(int* d_values, int count, int delta, void* stre
 /* Plan decode launches for the cache's capacity instead of its current length, and let the device-side
  * length be the only one consulted: the launch sequence of append/decode then never changes as the
  * context grows, so it can be replayed from a CUDA graph.  ojasx_b200_kvq_seq_len stays at the value of
- * the last eager call until ojasx_b200_kvq_sync_len reads the device length back (synchronises). */
+ * the last eager call until ojasx_b200_kvq_sync_len reads the device length back (synchronises).
+ * Under the static plan the host cannot refuse an append to a full cache: the kernel drops that
+ * token and raises a device flag; ojasx_b200_kvq_sync_len then returns -2 once (and clears the
+ * flag) instead of the length, so poll it whenever the context may have reached max_seq_len. */
 OJASX_API int ojasx_b200_kvq_set_static_plan(OjasxKvqHandle handle, int enabled);
 OJASX_API int ojasx_b200_kvq_sync_len(OjasxKvqHandle handle);
 

@@ -149,7 +149,12 @@ int ojasx_set_linear_outliers(OjasxLinearHandle handle, int nnz, const int* row_
     if (!handle) return OJX_ERR_ARG;
     auto* h = static_cast<LinearHandle*>(handle);
     if (nnz < 0 || !row_ptrs || (nnz > 0 && (!col_indices || !values))) return OJX_ERR_ARG;
+    // The reference accepts new outliers at any time (ojasx_lut_c_api.cpp:67-91).  A recorded host-pointer
+    // launch and any group snapshot still point at the arrays freed below, so both are invalidated.
+    std::lock_guard<std::mutex> lock(h->host_mu);
     DeviceGuard g(h->dev);
+    if (h->host_graph) { cudaGraphExecDestroy(h->host_graph); h->host_graph = nullptr; }
+    ++h->generation;
     cudaFree(h->row_ptrs); cudaFree(h->cols); cudaFree(h->vals);
     h->row_ptrs = nullptr; h->cols = nullptr; h->vals = nullptr; h->nnz = 0;
     int rc;
@@ -333,6 +338,8 @@ OjasxLinearGroupHandle ojasx_b200_create_linear_group(const OjasxLinearHandle* h
     auto* g = new (std::nothrow) LinearGroup();
     if (!g) return nullptr;
     g->host.resize(count);
+    g->members.resize(count);
+    g->member_generation.resize(count);
     int item = 0;
     for (int i = 0; i < count; ++i) {
         auto* h = static_cast<LinearHandle*>(handles[i]);
@@ -344,6 +351,8 @@ OjasxLinearGroupHandle ojasx_b200_create_linear_group(const OjasxLinearHandle* h
         P.item_begin = item;
         item += P.tiles;
         g->host[i] = P;
+        g->members[i] = h;
+        g->member_generation[i] = h->generation;
     }
     g->total_items = item;
     if (cudaMalloc((void**)&g->dev_probs, sizeof(LinearProblem) * (size_t)count) != cudaSuccess) { delete g; return nullptr; }
@@ -356,6 +365,17 @@ int ojasx_b200_linear_group_forward(OjasxLinearGroupHandle group, const void* d_
     if (io_dtype != OJX_F32 && io_dtype != OJX_BF16) return OJX_ERR_ARG;
     auto* g = static_cast<LinearGroup*>(group);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // A layer whose outliers were replaced since the snapshot: take its arrays again and rewrite the table.
+    for (size_t i = 0; i < g->host.size(); ++i) {
+        const LinearHandle* h = g->members[i];
+        if (h->generation == g->member_generation[i]) continue;
+        const LinearProblem old = g->host[i];
+        LinearProblem P = h->problem(old.x, old.y, 1, old.io_dtype, 0, h->out);
+        P.tile_rows = old.tile_rows; P.tiles = old.tiles; P.item_begin = old.item_begin;
+        g->host[i] = P;
+        g->member_generation[i] = h->generation;
+        g->bound_x = nullptr;
+    }
     // A few problems of one shape (q/k/v, gate/up): one cluster launch, the problems travel as kernel
     // arguments, so nothing is copied or synchronised (safe inside a stream capture).
     if (g->host.size() <= 8 && !linear_cluster_disabled()) {

@@ -9,6 +9,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdio>
 #include <new>
 #include <vector>
 
@@ -90,6 +91,19 @@ static int grow_legacy_head(LegacyKvHandle* kv, LegacyKvHandle::Head& h, int new
     return OJX_OK;
 }
 
+// The device-pointer MoE entry points allocate scratch on the current device and launch there, so the
+// handle's device must be current (the caller's stream belongs to it anyway).
+static int moe_check_device(const MoeHandle* h, const char* who) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev != h->dev) {
+        char msg[160];
+        std::snprintf(msg, sizeof(msg), "%s: the handle's device (%d) must be the current device (%d)", who, h->dev, dev);
+        set_last_error_msg(msg);
+        return OJX_ERR_ARG;
+    }
+    return OJX_OK;
+}
+
 }  // namespace ojx
 
 using namespace ojx;
@@ -166,6 +180,7 @@ int ojasx_b200_moe_forward(OjasxMoEHandle handle, const void* d_x, const int* d_
     if (!handle || !d_x || !d_topk_idx || !d_topk_w || !d_y) return OJX_ERR_ARG;
     if (n_tokens <= 0 || k_active <= 0 || (io_dtype != OJX_F32 && io_dtype != OJX_BF16)) return OJX_ERR_ARG;
     auto* h = static_cast<MoeHandle*>(handle);
+    if (int drc = moe_check_device(h, "ojasx_b200_moe_forward")) return drc;
     int rc = h->reserve(n_tokens, k_active);
     if (rc != OJX_OK) return rc;
     return launch_moe_experts(h->problem(d_x, d_y, d_topk_idx, d_topk_w, n_tokens, k_active, io_dtype),
@@ -177,6 +192,7 @@ int ojasx_b200_moe_route(OjasxMoEHandle handle, const void* d_x, int n_tokens, i
     if (!handle || !d_x || !d_idx_out || !d_w_out || n_tokens <= 0 || top_k <= 0) return OJX_ERR_ARG;
     auto* h = static_cast<MoeHandle*>(handle);
     if (!h->router) { set_last_error_msg("moe_route: no router weights set"); return OJX_ERR_ARG; }
+    if (int drc = moe_check_device(h, "ojasx_b200_moe_route")) return drc;
     int rc = h->reserve(n_tokens, top_k);
     if (rc != OJX_OK) return rc;
     float* logits = static_cast<float*>(h->route_scratch);
@@ -190,6 +206,7 @@ int ojasx_b200_moe_forward_routed(OjasxMoEHandle handle, const void* d_x, void* 
     if (!handle || !d_x || !d_y || n_tokens <= 0 || top_k <= 0) return OJX_ERR_ARG;
     auto* h = static_cast<MoeHandle*>(handle);
     if (!h->router) { set_last_error_msg("moe_forward_routed: no router weights set"); return OJX_ERR_ARG; }
+    if (int drc = moe_check_device(h, "ojasx_b200_moe_forward_routed")) return drc;
     int rc = h->reserve(n_tokens, top_k);
     if (rc != OJX_OK) return rc;
     float* logits = static_cast<float*>(h->route_scratch);
@@ -384,6 +401,15 @@ int ojasx_b200_kvq_sync_len(OjasxKvqHandle handle) {
     std::vector<int> lens(h->B);
     OJX_CUDA_TRY(cudaMemcpy(lens.data(), h->seq_lens, sizeof(int) * lens.size(), cudaMemcpyDeviceToHost));
     h->host_len = *std::max_element(lens.begin(), lens.end());
+    // An append that found its sequence full (possible only under the static plan, where the host-side
+    // capacity check is skipped) dropped the token and raised this flag: report it once and clear it.
+    int overflow = 0;
+    OJX_CUDA_TRY(cudaMemcpy(&overflow, h->error_flag, sizeof(int), cudaMemcpyDeviceToHost));
+    if (overflow) {
+        OJX_CUDA_TRY(cudaMemset(h->error_flag, 0, sizeof(int)));
+        set_last_error_msg("kvq: an append ran past max_seq_len and its token was dropped");
+        return OJX_ERR_RANGE;
+    }
     return h->host_len;
 }
 

@@ -38,20 +38,6 @@ constexpr int kDqBlockK = 64;        // bf16 elements per K tile = one 128-byte 
 constexpr int kDqStages = 8;        // most stage buffers; as many as fit next to the batch tile are used (3 at N = 256)
 constexpr int kDqSpin = 1 << 22;     // bounded mbarrier polling
 
-// Per-phase cycle counters for tuning; compiled out unless OJX_PHASE_TIMING is defined.
-#ifdef OJX_PHASE_TIMING
-__device__ unsigned long long g_dq_phase[16];
-#define DQ_TICK(i) do { if (blockIdx.x == 0 && blockIdx.y == 0) { long long n_ = clock64(); atomicAdd(&g_dq_phase[i], (unsigned long long)(n_ - t_)); t_ = n_; } } while (0)
-#define DQ_TICK_INIT long long t_ = clock64()
-// absolute time since kernel start, thread 0 of CTA (0,0,0)
-#define DQ_MARK_INIT const long long t0_ = clock64()
-#define DQ_MARK(i) do { if (threadIdx.x == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) atomicAdd(&g_dq_phase[i], (unsigned long long)(clock64() - t0_)); } while (0)
-#else
-#define DQ_MARK_INIT do { } while (0)
-#define DQ_MARK(i) do { } while (0)
-#define DQ_TICK(i) do { } while (0)
-#define DQ_TICK_INIT do { } while (0)
-#endif
 
 
 __device__ __forceinline__ void cp_async16_zfill(void* smem_dst, const void* gsrc, int src_bytes) {
@@ -117,7 +103,6 @@ struct DequantGemmProblem {
 
 __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __grid_constant__ DequantGemmProblem P) {
     extern __shared__ unsigned char dq_smem_raw[];
-    DQ_MARK_INIT;
     // swizzled tiles need 1024-byte alignment; the dynamic segment only promises 16
     unsigned char* dq_smem = dq_smem_raw + ((1024u - (smem_u32(dq_smem_raw) & 1023u)) & 1023u);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -213,7 +198,6 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem_base = *tmem_slot;
     bool ok = true;
-    DQ_MARK(10);
 
     if (warp < kDqProducers / 32) {
         // ---------------- producers: kDqGroups groups of 64 threads; group q builds K tiles q, q + 4, ... on its
@@ -259,14 +243,12 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
         };
         uint2 codes_now[2], codes_next[2];
         load_codes(gq, codes_now);
-        DQ_TICK_INIT;
         for (int kt = gq; kt < KT && ok; kt += kDqGroups) {
             const int s = kt % S;
             load_codes(kt + kDqGroups, codes_next);   // in flight while this tile is built
             // the MMAs that read this stage's previous contents must be done
             if (kt >= S) ok = mbar_wait(empty0 + 8 * s, ((kt / S) - 1) & 1);
             if (!ok) break;
-            if (tid == 0) DQ_TICK(0);
             unsigned char* A = tiles + s * stage_bytes;
             unsigned char* B = A + a_bytes;
             for (int i = gt; i < total_x; i += kDqGroupThreads) {   // X tile: 16-byte chunks straight into their swizzled place
@@ -312,17 +294,13 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
                     *w = __float2bfloat16_rn(__bfloat162float(*w) + __int_as_float(e.y));
                 }
             }
-            if (tid == 0) DQ_TICK(2);
             asm volatile("cp.async.wait_group 0;" ::: "memory");   // this thread's share of the X tile has landed
-            if (tid == 0) DQ_TICK(1);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic and cp.async stores -> visible to the tensor core
             mbar_arrive(full0 + 8 * s);
-            if (tid == 0) DQ_TICK(3);
             codes_now[0] = codes_next[0];
             codes_now[1] = codes_next[1];
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
-        DQ_MARK(11);
         // the epilogue and the split reduction address rows as (tid & 127, tid >> 7)
         const int trow = tid & 127, half = tid >> 7;
         const int m = m0 + trow;
@@ -332,7 +310,6 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
         if (row_ok && P.csr.nnz > 0) { csr_begin = P.csr.row_ptrs[m]; cend_row = P.csr.row_ptrs[m + 1]; }
         // ---------------- epilogue: accumulator row trow; the two threads of a row split the batch columns
         if (ok) ok = mbar_wait(accum, 0);
-        DQ_MARK(12);
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float sc = row_scale;
@@ -369,12 +346,10 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
     } else if (lane == 0) {
         // ---------------- MMA issuer
         const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(N >> 3) << 17) | ((unsigned)(kDqBlockM >> 4) << 24);
-        DQ_TICK_INIT;
         for (int kt = 0; kt < KT && ok; ++kt) {
             const int s = kt % S;
             ok = mbar_wait(full0 + 8 * s, (kt / S) & 1);
             if (!ok) break;
-            DQ_TICK(4);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const unsigned a_addr = smem_u32(tiles + s * stage_bytes), b_addr = a_addr + a_bytes;
 #pragma unroll
@@ -389,11 +364,9 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
             }
             // frees the stage when the MMAs that read it have completed
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(empty0 + 8 * s) : "memory");
-            DQ_TICK(5);
         }
         if (ok) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(accum) : "memory");
     }
-    DQ_MARK(13);
     if (!ok && P.error_flag) atomicExch(P.error_flag, 1);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -443,7 +416,6 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
             }
         }
     }
-    DQ_MARK(14);
 }
 
 constexpr size_t kDqSmemBudget = 226 * 1024;   // dynamic shared memory; the kernel also has a few static bytes
@@ -512,10 +484,13 @@ int launch_dequant_gemm(const LinearProblem& L, cudaStream_t stream, void** scra
         P.csr_cap = (int)(left / 8 < 8192 ? left / 8 : 8192);
     }
     const size_t smem = dequant_gemm_smem(P.n_pad, P.stages, P.csr_cap);
-    static thread_local size_t configured = 0;
-    if (smem > configured) {
+    // the opt-in is a per-device attribute of the kernel: remember what each device was given
+    static thread_local size_t configured[64] = {};
+    int cur_dev = 0;
+    OJX_CUDA_TRY(cudaGetDevice(&cur_dev));
+    if (cur_dev < 0 || cur_dev >= 64 || smem > configured[cur_dev]) {
         OJX_CUDA_TRY(cudaFuncSetAttribute(vq_dequant_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = smem;
+        if (cur_dev >= 0 && cur_dev < 64) configured[cur_dev] = smem;
     }
     const int rows = L.row_stop - L.row_start;
     dim3 grid((rows + kDqBlockM - 1) / kDqBlockM, (L.batch + 255) / 256, 1);
@@ -548,10 +523,3 @@ int launch_dequant_gemm(const LinearProblem& L, cudaStream_t stream, void** scra
 
 }  // namespace ojx
 
-#ifdef OJX_PHASE_TIMING
-extern "C" __attribute__((visibility("default"))) int ojx_read_dq_phases(unsigned long long* out, int reset) {
-    cudaMemcpyFromSymbol(out, ojx::g_dq_phase, sizeof(unsigned long long) * 16);
-    if (reset) { unsigned long long z[16] = {}; cudaMemcpyToSymbol(ojx::g_dq_phase, z, sizeof(z)); }
-    return 0;
-}
-#endif

@@ -51,6 +51,9 @@ struct LinearHandle {
     cudaGraphExec_t host_graph = nullptr;
     int host_graph_batch = 0;
     const void* host_graph_key[3] = {nullptr, nullptr, nullptr};   // pin_x, d_x, pin_y_dev it was captured with
+    // Bumped whenever the arrays a captured launch or a problem snapshot points at are replaced
+    // (ojasx_set_linear_outliers); graphs and groups built from an older generation are rebuilt.
+    unsigned generation = 0;
 
     ~LinearHandle();
     LinearProblem problem(const void* x, void* y, int batch, int io_dtype, int row_start, int row_stop) const;
@@ -61,6 +64,8 @@ struct LinearGroup {
     int D = 0;
     int total_items = 0;
     std::vector<LinearProblem> host;
+    std::vector<const LinearHandle*> members;   // borrowed: the layers must outlive the group
+    std::vector<unsigned> member_generation;    // generation of each layer when host[i] was taken
     LinearProblem* dev_probs = nullptr;
     const void* bound_x = nullptr;
     void* bound_y = nullptr;

@@ -124,15 +124,6 @@ constexpr int kKvVctPad = 4;                // words of padding per transposed c
 // named barriers (0 is __syncthreads)
 constexpr int kBarScore = 1, kBarFull = 2 /* +buf */, kBarEmpty = 4 /* +buf */, kBarValue = 6;
 
-// Per-phase cycle counters of CTA (0,0,0) for tuning; compiled out unless OJX_PHASE_TIMING is defined.
-#ifdef OJX_PHASE_TIMING
-__device__ unsigned long long g_kv_phase[16];
-#define KV_TICK(i, who) do { if (threadIdx.x == (who) && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) { long long n_ = clock64(); atomicAdd(&g_kv_phase[i], (unsigned long long)(n_ - t_)); t_ = n_; } } while (0)
-#define KV_TICK_INIT long long t_ = clock64()
-#else
-#define KV_TICK(i, who) do { } while (0)
-#define KV_TICK_INIT do { } while (0)
-#endif
 
 __device__ __forceinline__ void named_bar_sync(int id, int count) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
@@ -251,7 +242,6 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
     const uint8_t* kc = P.k_codes + (((size_t)b * P.Hkv + h) * P.max_seq) * G;
     const uint8_t* vc = P.v_codes + (((size_t)b * P.Hkv + h) * P.max_seq) * G;
 
-    KV_TICK_INIT;
     for (int i = tid; i < R * hd; i += kThreads) qs[i] = load_io(P.q, ((size_t)b * P.Hq + (size_t)h * R) * hd + i, P.io_dtype);
     for (int i0 = tid; i0 < 256 * kPieces * vrep; i0 += 4 * kThreads) {   // consecutive threads, consecutive 16-byte slots
         float4 val[4];
@@ -267,7 +257,6 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
             if (i0 + u * kThreads < 256 * kPieces * vrep) reinterpret_cast<float4*>(vcb)[i0 + u * kThreads] = val[u];
     }
     __syncthreads();
-    KV_TICK(12, 0);
     // query table: kThreads / 256 threads per centroid, groups interleaved between them
     {
         const int cen = tid & 255;
@@ -290,7 +279,6 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
     }
     __syncthreads();
 
-    KV_TICK(13, 0);
     // value mapping: threads per unit (kGp groups) capped so that the stripe partials ([stripes][R][hd + 4])
     // fit in the area of the query table and the value codebook, both dead by then
     const int units = (G + kGp - 1) / kGp;
@@ -330,7 +318,6 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
             float* wr = wred + buf * kWarpsHalf * R;
             uint32_t* vt = vct + (size_t)buf * Gq * vrow;
             if (it >= 2) named_bar_sync(kBarEmpty + buf, kThreads);   // the value warps are done with this buffer
-            KV_TICK(0, 0);
 
             // both tokens of a thread go through the groups together, so that their gathers overlap; a token
             // beyond the pass reads row 0 of the pass and is discarded
@@ -469,9 +456,7 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
                 for (int off = 16; off >= 1; off >>= 1) mloc[r] = fmaxf(mloc[r], __shfl_xor_sync(0xffffffffu, mloc[r], off));
                 if (lane == 0) wr[warp * R + r] = mloc[r];
             }
-            KV_TICK(1, 0);
             named_bar_sync(kBarScore, kHalf);
-            KV_TICK(2, 0);
 #pragma unroll
             for (int r = 0; r < R; ++r) {
                 float m = m_run[r];
@@ -498,7 +483,6 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
                 }
             }
             named_bar_arrive(kBarFull + buf, kThreads);
-            KV_TICK(3, 0);
         }
         // normaliser: fixed-shape reduction (shuffle tree here, then the warps in order after the join)
 #pragma unroll
@@ -527,7 +511,6 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
             // the unit's codes of one token sit in one word (kGp divides 4)
             const uint8_t* codes = reinterpret_cast<const uint8_t*>(vct + (size_t)buf * Gq * vrow + (size_t)(vg >> 2) * vrow) + (vg & 3);
             named_bar_sync(kBarFull + buf, kThreads);
-            KV_TICK(8, kHalf);
 #pragma unroll
             for (int r = 0; r < R; ++r) {
                 const float m = mpub[buf * R + r];
@@ -577,7 +560,6 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
                 }
             }
             if (it + 2 < n_passes) named_bar_arrive(kBarEmpty + buf, kThreads);   // only if a score pass will wait for it
-            KV_TICK(9, kHalf);
         }
         // Every value warp is past its last pass, and so are the score warps (that pass was handed over by
         // all of them): the query table and the value codebook are dead, their area takes the stripe partials.
@@ -594,7 +576,6 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
     }
 
     __syncthreads();
-    KV_TICK(14, 0);
     for (int i = tid; i < R * hd; i += kThreads) {   // stripes of one group are added in a fixed order
         const int r = i / hd, c = i - r * hd;
         float acc = 0.0f;
@@ -673,10 +654,12 @@ static int launch_decode_t(const KvqProblem& P, cudaStream_t s) {
     if (smem + 64 > 227 * 1024) return OJX_ERR_TOO_LARGE;   // 64: the kernel's few static bytes
     KvqProblem Q = P;
     Q.v_copies = kvq_decode_v_copies(P, R);
-    static thread_local size_t configured = 0;  // largest opt-in made for this instantiation
-    if (smem > configured) {
+    static thread_local size_t configured[64] = {};  // largest opt-in made for this instantiation, per device
+    int cur_dev = 0;
+    OJX_CUDA_TRY(cudaGetDevice(&cur_dev));
+    if (cur_dev < 0 || cur_dev >= 64 || smem > configured[cur_dev]) {
         OJX_CUDA_TRY(cudaFuncSetAttribute(kvq_decode_kernel<R, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = smem;
+        if (cur_dev >= 0 && cur_dev < 64) configured[cur_dev] = smem;
     }
     kvq_decode_kernel<R, D><<<dim3(P.n_chunks, P.Hkv, P.B), kvq_decode_threads(R, D), smem, s>>>(Q);
     OJX_CUDA_TRY(cudaGetLastError());
@@ -820,10 +803,3 @@ int launch_legacy_attention(const float* q, int head_dim, int block_dim, int T, 
 
 }  // namespace ojx
 
-#ifdef OJX_PHASE_TIMING
-extern "C" __attribute__((visibility("default"))) int ojx_read_kv_phases(unsigned long long* out, int reset) {
-    cudaMemcpyFromSymbol(out, ojx::g_kv_phase, sizeof(unsigned long long) * 16);
-    if (reset) { unsigned long long z[16] = {}; cudaMemcpyToSymbol(ojx::g_kv_phase, z, sizeof(z)); }
-    return 0;
-}
-#endif

@@ -16,15 +16,6 @@
 
 namespace ojx {
 
-// Per-phase cycle counters for tuning; compiled out unless OJX_PHASE_TIMING is defined.
-#ifdef OJX_PHASE_TIMING
-__device__ unsigned long long g_cl_phase[16];
-#define OJX_TICK(i) do { if (threadIdx.x == 0 && blockIdx.x == 0) { long long n_ = clock64(); atomicAdd(&g_cl_phase[i], (unsigned long long)(n_ - t_)); t_ = n_; } } while (0)
-#define OJX_TICK_INIT long long t_ = clock64()
-#else
-#define OJX_TICK(i) do { } while (0)
-#define OJX_TICK_INIT do { } while (0)
-#endif
 
 constexpr int kClThreads = 512;
 constexpr int kClProd = 2048;   // CSR products staged per pass
@@ -139,19 +130,15 @@ lut_linear_cluster_kernel(const __grid_constant__ ClusterGroup grp, const __grid
         if (tid < mine) oacc_s[tid] = acc;
     };
 
-    OJX_TICK_INIT;
     int tile = cid;
     if (tile < n_tiles) {
         stage_codes(tile);
-        OJX_TICK(0);
         outlier_sums(tile);
-        OJX_TICK(1);
     }
 
     // table slice for my groups (same arithmetic as RowWalker::build_slice)
     for (int i = tid; i < ng * D; i += kClThreads) xs[i] = xl(g0 * D + i);
     __syncthreads();
-    OJX_TICK(2);
     {
         const int kc = tid & 255;
         float c[D];
@@ -169,10 +156,8 @@ lut_linear_cluster_kernel(const __grid_constant__ ClusterGroup grp, const __grid
     for (; tile < n_tiles; tile += n_clusters) {
         const int r0 = P.row_start + tile * R;
         const int nR = min(R, P.row_stop - r0);
-        OJX_TICK(3);
         cp_async_wait<0>();
         __syncthreads();  // codes landed, table built
-        OJX_TICK(4);
 
         // gather: lane = row; every value goes to the CTA that owns the row
         const int nrb = (nR + 31) >> 5;
@@ -198,9 +183,7 @@ lut_linear_cluster_kernel(const __grid_constant__ ClusterGroup grp, const __grid
                 }
             }
         }
-        OJX_TICK(5);
         cluster_sync_all();  // all values of this tile are in their owners' shared memory
-        OJX_TICK(6);
 
         // next tile's codes can stream in while this one is summed (codes_s is no longer read)
         if (tile + n_clusters < n_tiles) stage_codes(tile + n_clusters);
@@ -235,11 +218,9 @@ lut_linear_cluster_kernel(const __grid_constant__ ClusterGroup grp, const __grid
             if (P.io_dtype == OJX_BF16) reinterpret_cast<__nv_bfloat16*>(P.y)[o] = __float2bfloat16_rn(res);
             else reinterpret_cast<float*>(P.y)[o] = res;
         }
-        OJX_TICK(7);
         __syncthreads();     // oacc_s of this tile has been consumed
         if (tile + n_clusters < n_tiles) outlier_sums(tile + n_clusters);
         cluster_sync_all();  // recv may be overwritten by the next tile; nobody exits while peers may still write
-        OJX_TICK(8);
     }
 }
 
@@ -422,10 +403,3 @@ int try_launch_linear_cluster_group(const LinearProblem* probs, int count, cudaS
 
 }  // namespace ojx
 
-#ifdef OJX_PHASE_TIMING
-extern "C" __attribute__((visibility("default"))) int ojx_read_cluster_phases(unsigned long long* out, int reset) {
-    cudaMemcpyFromSymbol(out, ojx::g_cl_phase, sizeof(unsigned long long) * 16);
-    if (reset) { unsigned long long z[16] = {}; cudaMemcpyToSymbol(ojx::g_cl_phase, z, sizeof(z)); }
-    return 0;
-}
-#endif

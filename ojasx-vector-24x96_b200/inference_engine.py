@@ -166,6 +166,8 @@ class VQDecoderStack:
     def decode_step(self, token_ids: torch.Tensor) -> torch.Tensor:
         """One token per sequence in, fp32 logits ``[batch, vocab]`` out; the KV caches grow by one."""
         ids = token_ids.to(self.device).to(torch.int64)
+        if self.position >= self.cfg.max_seq_len:
+            raise ValueError(f"the KV caches hold max_seq_len = {self.cfg.max_seq_len} tokens; reset() before decoding further")
         self.position += 1
         if not self.use_graph:
             return self._enqueue_step(ids)

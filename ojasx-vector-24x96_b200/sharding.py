@@ -86,11 +86,19 @@ class ExpertParallelMoE:
 class HeadShardedKVCache:
     """KV-head split: ``cache`` is an ``ops.VQKVCache`` holding KV heads ``split_range(Hkv, world, rank)`` only."""
 
-    def __init__(self, cache, total_q_heads: int, group=None):
+    def __init__(self, cache, total_q_heads: int, group=None, total_kv_heads: int = 0):
         self.cache, self.total_q_heads, self.group = cache, total_q_heads, group
+        world = dist.get_world_size(group)
+        # query heads held by every rank (ragged when the KV heads do not divide evenly)
+        kv = total_kv_heads or world * cache.kv_heads
+        per_kv = total_q_heads // kv
+        self.q_ranges = [(a * per_kv, b * per_kv) for a, b in all_ranges(kv, world)]
 
     def decode(self, q_local: torch.Tensor, scale: float = -1.0) -> torch.Tensor:
         o = self.cache.decode(q_local, scale)                      # [B, Hq_local, hd]
-        parts = [torch.empty_like(o) for _ in range(dist.get_world_size(self.group))]
-        dist.all_gather(parts, o.contiguous(), group=self.group)
-        return torch.cat(parts, dim=1)
+        width = max(b - a for a, b in self.q_ranges)
+        pad = o.new_zeros((o.shape[0], width, o.shape[2]))         # equal-sized pieces: ragged shards are padded
+        pad[:, : o.shape[1]] = o
+        parts = [torch.empty_like(pad) for _ in self.q_ranges]
+        dist.all_gather(parts, pad, group=self.group)
+        return torch.cat([p[:, : b - a] for p, (a, b) in zip(parts, self.q_ranges)], dim=1)

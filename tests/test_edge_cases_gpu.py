@@ -171,3 +171,59 @@ def test_concurrent_callers_of_one_handle(cuda, oracle):
     for t in threads:
         t.join()
     assert not bad
+
+
+def test_outliers_replaced_after_a_forward(cuda, oracle):
+    """ojasx_set_linear_outliers may be called at any time (ojasx_lut_c_api.cpp:67-91): a forward that was
+    already recorded for the handle, and a group that already holds the handle, must use the new arrays."""
+    L = ojasx_b200.lib()
+    K, M, D = 512, 96, 8
+    w = synth.make_vq_linear(11, K, M, block_dim=D, outlier_frac=0)
+    w2 = synth.make_vq_linear(12, K, M, block_dim=D, outlier_frac=0.02)
+    w3 = synth.make_vq_linear(13, K, M, block_dim=D, outlier_frac=0.05)
+    x = np.random.default_rng(4).standard_normal((1, K)).astype(np.float32)
+    layer = ops.VQLinear(w.codebook, w.codes, None, None, None, block_dim=D)
+    other = ops.VQLinear.from_weights(synth.make_vq_linear(14, K, M, block_dim=D, outlier_frac=0.01))
+    group = ops.VQLinearGroup([layer, other] * 5)           # 10 members: the persistent grouped kernel
+    xd = torch.from_numpy(np.repeat(x, 10, 0)).to(cuda)
+    yd = torch.zeros(10, M, device=cuda)
+    y = np.zeros((1, M), np.float32)
+
+    def host_forward():
+        assert L.ojasx_linear_forward(layer.handle, x.ctypes.data, y.ctypes.data, 1, 0) == 0
+        return y.copy()
+
+    base = oracle.linear_forward(w.codebook, w.codes, None, None, None, x, block_dim=D)
+    assert np.array_equal(host_forward(), base)
+    assert np.array_equal(host_forward(), base)              # second call replays the recorded launch
+    group.forward(xd, yd)
+    assert np.array_equal(yd[0:1].cpu().numpy(), base)
+    for csr in (w2.csr, w3.csr):                             # none -> some -> other (old arrays are freed)
+        rp, ci, va = (np.ascontiguousarray(a) for a in csr)
+        assert L.ojasx_set_linear_outliers(layer.handle, len(va), rp.ctypes.data, ci.ctypes.data, va.ctypes.data) == 0
+        want = oracle.linear_forward(w.codebook, w.codes, None, None, csr, x, block_dim=D)
+        assert not np.array_equal(want, base)
+        assert np.array_equal(host_forward(), want)
+        group.forward(xd, yd)
+        torch.cuda.synchronize()
+        assert np.array_equal(yd[0:1].cpu().numpy(), want) and np.array_equal(yd[2:3].cpu().numpy(), want)
+        assert np.array_equal(layer(torch.from_numpy(x).to(cuda)).cpu().numpy(), want)
+
+
+def test_static_plan_append_past_capacity_is_reported(cuda):
+    """Under the static plan the host cannot refuse an append to a full cache; the kernel drops the token and
+    the next ojasx_b200_kvq_sync_len returns -2 once.  (A dropped write, not a fault.)"""
+    kv = synth.make_vq_kv(21, 1, 3, kv_heads=4, q_heads=8, head_dim=96)
+    cache = ops.VQKVCache(1, 4, 8, 96, 8, 4, kv.k_codebook, kv.v_codebook)
+    cache.load(kv.k_codes, kv.v_codes)
+    cache.set_static_plan(True)
+    k = torch.from_numpy(kv.new_k).to(cuda)
+    v = torch.from_numpy(kv.new_v).to(cuda)
+    cache.append(k, v)                                       # 3 -> 4: full
+    assert cache.sync_len() == 4
+    cache.append(k, v)                                       # dropped
+    assert cache.sync_len() == -2
+    assert cache.sync_len() == 4                             # flag cleared, length unchanged
+    out = cache.decode(torch.from_numpy(kv.q).to(cuda))
+    assert torch.isfinite(out).all()
+    cache.close()

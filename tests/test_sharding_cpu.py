@@ -110,15 +110,23 @@ class _OracleKVShard:
         return torch.from_numpy(out)
 
 
-def _kv_job(rank, world):
-    kv = synth.make_vq_kv(7, 2, 40, kv_heads=4, q_heads=8, head_dim=32)
-    h0, h1 = sharding.split_range(4, world, rank)
+def _kv_job(rank, world, heads=4):
     R = 2
+    kv = synth.make_vq_kv(7, 2, 40, kv_heads=heads, q_heads=heads * R, head_dim=32)
+    h0, h1 = sharding.split_range(heads, world, rank)
     q = torch.from_numpy(kv.q)
-    full = sharding.HeadShardedKVCache(_OracleKVShard(kv, h0, h1), 8).decode(q[:, h0 * R:h1 * R])
-    want = _OracleKVShard(kv, 0, 4).decode(q)
+    full = sharding.HeadShardedKVCache(_OracleKVShard(kv, h0, h1), heads * R, total_kv_heads=heads).decode(q[:, h0 * R:h1 * R])
+    want = _OracleKVShard(kv, 0, heads).decode(q)
     return bool(np.array_equal(full.numpy(), want.numpy()))
+
+
+def _kv_job_ragged(rank, world):
+    return _kv_job(rank, world, heads=3)     # 2 + 1 heads: the shards' outputs differ in size
 
 
 def test_kv_head_shards_all_gather():
     assert _run(_kv_job) == [True, True]
+
+
+def test_kv_head_shards_ragged():
+    assert _run(_kv_job_ragged) == [True, True]
