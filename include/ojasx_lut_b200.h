@@ -115,8 +115,10 @@ OJASX_API int ojasx_b200_linear_forward(OjasxLinearHandle handle, const void* d_
  * in_features % 64 == 0 and CSR columns ascending inside each row; otherwise -4. */
 OJASX_API int ojasx_b200_linear_forward_tensor(OjasxLinearHandle handle, const void* d_x, void* d_y, int batch_size,
                                                int row_start, int row_stop, void* stream);
-/* 1 if a tensor-core launch since the last call gave up on a bounded barrier wait (its output is then
- * invalid), 0 otherwise; synchronises the device.  Negative = CUDA error. */
+/* Device-side error flags raised since the last call (the outputs of the launch that raised one are
+ * invalid), 0 if none; synchronises the device.  Bit 0: a tensor-core launch gave up on a bounded
+ * barrier wait.  Bit 1: the batched MoE expert kernel found its shared memory at an unexpected address
+ * and did nothing.  Bit 2: a bounded wait for a bulk copy of a lookup table ran out.  Negative = CUDA error. */
 OJASX_API int ojasx_b200_take_device_error(void);
 
 /* Same computation on borrowed device arrays, no handle: the device twin of

@@ -239,9 +239,11 @@ int ojasx_b200_linear_forward_tensor(OjasxLinearHandle handle, const void* d_x, 
 }
 
 int ojasx_b200_take_device_error(void) {
-    int v = 0;
+    int v = 0, m = 0, c = 0;
     int rc = take_dequant_gemm_error(&v);
-    return rc != OJX_OK ? rc : v;
+    if (rc == OJX_OK) rc = take_moe_fused_error(&m);
+    if (rc == OJX_OK) rc = take_moe_bulk_copy_error(&c);
+    return rc != OJX_OK ? rc : (v | (m ? 2 : 0) | (c ? 4 : 0));
 }
 
 int ojasx_linear_forward(OjasxLinearHandle handle, const float* x, float* y, int batch_size, int num_threads) {

@@ -25,7 +25,7 @@ MoeHandle::~MoeHandle() {
 
 int MoeHandle::reserve(int n_tokens, int k) {
     const size_t pairs = (size_t)n_tokens * k;
-    const size_t need = sizeof(float) * pairs * ((size_t)I + H) + sizeof(int) * (pairs + 1);
+    const size_t need = sizeof(float) * pairs * ((size_t)I + H) + sizeof(int) * (5 * pairs + 8);   // + work lists
     int rc = ensure_capacity(&scratch, &scratch_cap, need);
     if (rc != OJX_OK) return rc;
     // Token tables [n_tokens, G, 256] fp32, shared by the k experts of a token (up to 1 GiB).
@@ -52,6 +52,7 @@ MoeProblem MoeHandle::problem(const void* x, void* y, const int* idx, const floa
     P.inter = static_cast<float*>(scratch);
     P.expert_out = P.inter + (size_t)n_tokens * k * I;
     P.pair_list = reinterpret_cast<const int*>(P.expert_out + (size_t)n_tokens * k * H);
+    P.plan = P.pair_list;   // the two expert paths keep their work lists in the same scratch
     P.E_total = E_total;
     P.n_tokens = n_tokens; P.k_active = k; P.E = E; P.expert_offset = expert_offset;
     P.H = H; P.I = I; P.G = H / D; P.Gi = I / D; P.D = D; P.Kcb = 256; P.io_dtype = io;
@@ -215,8 +216,9 @@ int ojasx_b200_moe_forward_routed(OjasxMoEHandle handle, const void* d_x, void* 
     float* w = reinterpret_cast<float*>(idx + (size_t)n_tokens * top_k);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     MoeProblem P = h->problem(d_x, d_y, idx, w, n_tokens, top_k, io_dtype);
+    P.lut_blocks = moe_fused_wanted(P) ? 1 : 0;
     rc = launch_moe_router(h->router, d_x, io_dtype, n_tokens, h->H, h->E_total, top_k, logits, probs, idx, w, s,
-                           P.cb_in, P.Kcb, P.D, const_cast<float*>(P.lut_in));
+                           P.cb_in, P.Kcb, P.D, const_cast<float*>(P.lut_in), P.lut_blocks);
     if (rc != OJX_OK) return rc;
     P.lut_ready = P.lut_in != nullptr;
     return launch_moe_experts(P, s);

@@ -78,6 +78,12 @@ struct MoeProblem {
     int H, I, G, Gi, D, Kcb;
     int io_dtype;
     int gu_tile, gu_tiles, dn_tile, dn_tiles;
+    // fused expert kernel (moe_fused.cu): work-list scratch [4 + 5 * pairs] ints, largest chunk, floats per
+    // token in the parked sums; lut_blocks: lut_in is laid out in 16-group blocks (moe_prebuild_kernel)
+    const int* plan;
+    int mc_cmax, mc_nacc;
+    int mc_debug;
+    int lut_blocks;
 };
 
 // Codebook-VQ KV cache of one layer.  Device pointers.

@@ -36,7 +36,16 @@ int launch_silu_mul(const void* gate, const void* up, void* out, size_t n, int i
 // built by the same launch as the logits.
 int launch_moe_router(const float* Wr, const void* x, int io_dtype, int n_tokens, int H, int E, int k,
                       float* logits, float* probs, int* idx_out, float* w_out, cudaStream_t stream,
-                      const float* codebook = nullptr, int Kcb = 0, int D = 0, float* lut_out = nullptr);
+                      const float* codebook = nullptr, int Kcb = 0, int D = 0, float* lut_out = nullptr,
+                      int lut_blocks = 0);
+
+// --- moe_fused.cu: whole-expert work items (gate/up, SiLU gate and down fused) for batches of tokens
+bool moe_fused_wanted(const MoeProblem& P);   // shape fits and enough routed pairs are expected here
+int launch_moe_fused(MoeProblem P, cudaStream_t stream);   // work list, token tables (unless lut_ready), experts
+int launch_moe_prebuild_blocks(const void* x, int io_dtype, int n_tokens, int H, int D, const float* codebook, int Kcb,
+                               float* out, cudaStream_t stream);
+int take_moe_fused_error(int* out);
+int take_moe_bulk_copy_error(int* out);   // moe.cu: a bounded wait for a bulk table copy ran out
 
 // --- kv.cu
 constexpr int kKvMaxSplits = 256;   // context splits of one (sequence, KV head) in kvq decode

@@ -74,6 +74,44 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 template <int D>
 constexpr int slice_groups() { return (kXsFloats / D) < kSliceGroups ? (kXsFloats / D) : kSliceGroups; }
 
+// ---- bulk copy of a contiguous run of global memory into shared memory by the copy engine (TMA), tracked by an
+// mbarrier.  Used where a whole table slice is brought in at once: per-thread 16-byte copies keep too few bytes
+// in flight per SM for that (about 18 bytes per clock measured), the copy engine does not have that limit.
+// Every wait is bounded; a wait that runs out raises g_bulk_copy_timeout and carries on.
+static __device__ int g_bulk_copy_timeout;   // one per translation unit; moe.cu is the one that copies tables this way
+constexpr int kBulkSpin = 1 << 22;
+__device__ __forceinline__ void bulk_bar_init(void* bar) {
+    const unsigned a = static_cast<unsigned>(__cvta_generic_to_shared(bar));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(a) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+// One thread: global [src, src + bytes) -> shared dst; src, dst and bytes are multiples of 16, bytes < 1 MiB.
+__device__ __forceinline__ void bulk_copy_issue(void* bar, void* dst, const void* src, unsigned bytes) {
+    const unsigned b = static_cast<unsigned>(__cvta_generic_to_shared(bar));
+    const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(dst));
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // earlier generic accesses to dst come first
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(d), "l"(src),
+                 "r"(bytes), "r"(b)
+                 : "memory");
+}
+__device__ __forceinline__ bool bulk_copy_wait(void* bar, unsigned parity) {
+    const unsigned b = static_cast<unsigned>(__cvta_generic_to_shared(bar));
+    for (int i = 0; i < kBulkSpin; ++i) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(b), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    atomicExch(&g_bulk_copy_timeout, 1);
+    return false;
+}
+
 // Position of a warp's code stream: slice s, row block rb, 32-byte chunk cc inside the slice.
 struct StagePos {
     int s, rb, cc;
@@ -155,17 +193,10 @@ struct RowWalker {
         const int g0 = s * SG, ng = slice_ng(s);
         if (prebuilt) {
             // The table of this activation vector was built once by lut_prebuild_kernel (same
-            // arithmetic, so the same bits); copy this slice of it, 16 bytes per thread per step.
-            const float4* src = reinterpret_cast<const float4*>(prebuilt + (size_t)g0 * 256);
-            float4* dst = reinterpret_cast<float4*>(sm.lut);
-            const int n4 = ng * 64;
-            int i = threadIdx.x;
-            for (; i + 3 * kThreads < n4; i += 4 * kThreads) {
-                const float4 a = src[i], b = src[i + kThreads], c4 = src[i + 2 * kThreads], d4 = src[i + 3 * kThreads];
-                dst[i] = a; dst[i + kThreads] = b; dst[i + 2 * kThreads] = c4; dst[i + 3 * kThreads] = d4;
-            }
-            for (; i < n4; i += kThreads) dst[i] = src[i];
-            __syncthreads();
+            // arithmetic, so the same bits); this slice of it is one contiguous run: one bulk copy
+            // (the mbarrier sits in the x staging area, which the prebuilt path does not use).
+            if (threadIdx.x == 0) bulk_copy_issue(sm.xs, sm.lut, prebuilt + (size_t)g0 * 256, (unsigned)ng * 1024u);
+            bulk_copy_wait(sm.xs, (unsigned)(s & 1));
             return;
         }
         for (int i = threadIdx.x; i < ng * D; i += kThreads) sm.xs[i] = xl(g0 * D + i);
@@ -243,6 +274,7 @@ struct RowWalker {
 #pragma unroll
             for (int d = 0; d < D; ++d) c[d] = kc < Kcb ? codebook[kc * D + d] : 0.0f;
         }
+        if (prebuilt && threadIdx.x == 0) bulk_bar_init(sm.xs);   // first used after the slice loop's barrier
         StagePos prod = first();
         StagePos cons = prod;
         int issued = 0, consumed = 0;

@@ -474,6 +474,20 @@ static int launch_moe_experts_t(const MoeProblem& P, cudaStream_t s) {
 int launch_moe_experts(MoeProblem P, cudaStream_t s) {
     if (!P.x || !P.y || !P.topk_idx || !P.topk_w || !P.inter || !P.expert_out) return OJX_ERR_ARG;
     if (P.n_tokens <= 0 || P.k_active <= 0) return OJX_ERR_ARG;
+    // Batches: whole-expert work items, gate/up and down fused (moe_fused.cu); then the ordered combine.
+    if (moe_fused_wanted(P)) {
+        if (P.lut_ready && !P.lut_blocks) P.lut_ready = 0;   // tables were built in the other layout: rebuild
+        const int rc = launch_moe_fused(P, s);
+        if (rc != OJX_ERR_UNSUPPORTED) {
+            if (rc != OJX_OK) return rc;
+            const int n = P.n_tokens * P.H;
+            moe_combine_kernel<<<(n + 255) / 256, 256, 0, s>>>(P);
+            OJX_CUDA_TRY(cudaGetLastError());
+            count_launch(1);
+            return OJX_OK;
+        }
+    }
+    if (P.lut_ready && P.lut_blocks) P.lut_ready = 0;
     const int pairs = P.n_tokens * P.k_active, sms = kCtasPerSm * num_sms();
     // Tiles: spread few pairs over the SMs, keep tiles whole when there are many pairs.  An
     // expert-parallel shard expects only its share of the routed pairs.
@@ -497,11 +511,24 @@ int launch_moe_experts(MoeProblem P, cudaStream_t s) {
     }
 }
 
+int take_moe_bulk_copy_error(int* out) {
+    int v = 0, zero = 0;
+    OJX_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_bulk_copy_timeout, sizeof(int)));
+    if (v) OJX_CUDA_TRY(cudaMemcpyToSymbol(g_bulk_copy_timeout, &zero, sizeof(int)));
+    *out = v;
+    return OJX_OK;
+}
+
 int launch_moe_router(const float* Wr, const void* x, int io_dtype, int n_tokens, int H, int E, int k,
                       float* logits, float* probs, int* idx_out, float* w_out, cudaStream_t s,
-                      const float* codebook, int Kcb, int D, float* lut_out) {
+                      const float* codebook, int Kcb, int D, float* lut_out, int lut_blocks) {
     if (!Wr || !x || !logits || !probs || !idx_out || !w_out) return OJX_ERR_ARG;
     if (n_tokens <= 0 || k <= 0 || k > E) return OJX_ERR_ARG;
+    if (lut_out && lut_blocks) {   // tables in 16-group blocks for the fused expert kernel: a launch of their own
+        const int rc = launch_moe_prebuild_blocks(x, io_dtype, n_tokens, H, D, codebook, Kcb, lut_out, s);
+        if (rc != OJX_OK) return rc;
+        lut_out = nullptr;
+    }
     const int warps_per_block = 8;
     const int lx = (E + warps_per_block - 1) / warps_per_block, ly = n_tokens < 32 ? n_tokens : 32;
     if (lut_out) {   // the gate/up tables ride along (one launch less)
@@ -580,6 +607,7 @@ extern "C" int ojasx_b200_moe_forward_noalloc(OjasxMoEHandle handle, const void*
     // never read.  What an earlier call left there is therefore harmless.
     P.lut_in = nullptr;  // tables are rebuilt inside the gate/up kernel: no further scratch
     P.pair_list = nullptr;  // every pair is visited in order and skipped if it is not evaluated here
+    P.plan = nullptr;
     P.inter = scratch;
     P.expert_out = scratch + (size_t)n_tokens * k_active * h->I;
     return launch_moe_experts(P, static_cast<cudaStream_t>(stream));

@@ -105,3 +105,65 @@ def test_moe_bf16_io(cuda, oracle):
                       torch.from_numpy(wts).to(cuda)).float().cpu().numpy()
     # bf16 activation path: rel 2e-2 (north star); here the only loss is the final rounding to bf16
     assert np.allclose(got, want, rtol=2e-2, atol=1e-6)
+
+
+@pytest.fixture
+def fused_everywhere(monkeypatch):
+    """Send every batch through the whole-expert kernel (normally used from about a hundred routed pairs)."""
+    monkeypatch.setenv("OJASX_B200_MOE_FUSED_MIN_PAIRS", "1")
+
+
+@pytest.mark.parametrize("H,I,D,E,k,B", [
+    (256, 128, 8, 8, 4, 7),      # one table slice per pass; chunks of 4, 2 and 1 tokens; short chains
+    (512, 256, 8, 6, 3, 40),     # several slices; about twenty tokens per expert
+    (2560, 640, 8, 16, 10, 12),  # benchmark geometry: 10 / 5 / 5 gate-up slices, 80-group down tables with a 16-group tail
+    (1024, 512, 16, 4, 2, 9),    # block_dim 16
+    (384, 64, 4, 5, 5, 3),       # block_dim 4, every token routed to every expert
+])
+@pytest.mark.parametrize("frac", [0.0, 0.01])
+def test_moe_whole_expert_kernel_shapes(cuda, oracle, fused_everywhere, H, I, D, E, k, B, frac):
+    w = synth.make_vq_moe(H + B, E, H, I, block_dim=D, outlier_frac=frac, unit_scales=(frac == 0.0))
+    rng = np.random.default_rng(E * B)
+    x = rng.standard_normal((B, H)).astype(np.float32)
+    idx = np.stack([rng.choice(E, size=k, replace=False) for _ in range(B)]).astype(np.int32)
+    wts = rng.uniform(0.02, 0.3, size=(B, k)).astype(np.float32)
+    if B > 2:
+        idx[1, 0] = -1          # skipped pairs (ojasx_lut_cpu.cpp:284-286)
+        idx[2, k - 1] = E
+        wts[0, 1] = 5e-9
+    want = _oracle_moe(oracle, w, x, idx, wts)
+    moe = ops.VQMoE(w)
+    n0 = ojasx_b200.launch_count()
+    got = moe.forward(torch.from_numpy(x).to(cuda), torch.from_numpy(idx).to(cuda), torch.from_numpy(wts).to(cuda))
+    got = got.cpu().numpy()
+    assert ojasx_b200.lib().ojasx_b200_take_device_error() == 0
+    assert ojasx_b200.launch_count() - n0 == 4          # work list, token tables, experts, combine
+    assert _close(got, want), np.abs(got - want).max()
+    # expert shards of the same layer (expert-parallel ranks) add up to it
+    half = E // 2
+    lo, hi = ops.VQMoE(w, (0, half)), ops.VQMoE(w, (half, E))
+    args = (torch.from_numpy(x).to(cuda), torch.from_numpy(idx).to(cuda), torch.from_numpy(wts).to(cuda))
+    ys = (lo.forward(*args) + hi.forward(*args)).cpu().numpy()
+    assert np.allclose(ys, want, rtol=1e-5, atol=1e-6)
+
+
+def test_moe_config2_full_size_batch_256(cuda, oracle):
+    """BASELINE configuration 2 at full size: 512 experts, hidden 2560, inter 640, top-10, 0.38 % outliers on
+    every expert matrix, 256 tokens routed by the layer's own router.  The CPU oracle checks a sample of tokens."""
+    w = synth.make_vq_moe(77, 512, 2560, 640, block_dim=8, outlier_frac=0.0038)
+    rng = np.random.default_rng(256)
+    x = rng.standard_normal((256, 2560)).astype(np.float32)
+    moe = ops.VQMoE(w)
+    xt = torch.from_numpy(x).to(cuda)
+    idx, wts = moe.route(xt, 10)
+    oi, ow = oracle.router_topk(x, w.router, 10)
+    assert np.array_equal(idx.cpu().numpy(), oi) and np.array_equal(wts.cpu().numpy(), ow)
+    got = moe.forward_routed(xt, 10).cpu().numpy()
+    assert ojasx_b200.lib().ojasx_b200_take_device_error() == 0
+    sample = [0, 1, 2, 3, 63, 64, 127, 128, 200, 254, 255]
+    want = _oracle_moe(oracle, w, x[sample], oi[sample], ow[sample])
+    assert _close(got[sample], want), np.abs(got[sample] - want).max()
+    assert np.isfinite(got).all()
+    # the same tokens one at a time take the small-batch kernels: both paths agree within the tolerance
+    one = moe.forward_routed(xt[:4], 10).cpu().numpy()
+    assert _close(one, want[:4])
