@@ -167,6 +167,11 @@ OJASX_API int ojasx_b200_moe_forward(OjasxMoEHandle handle, const void* d_x, con
                                      const float* d_topk_w, void* d_y, int n_tokens, int k_active, int io_dtype,
                                      void* stream);
 OJASX_API int ojasx_b200_moe_reserve(OjasxMoEHandle handle, int max_tokens, int k_active);
+/* Clamp of the fused-experts operator (ResidualVQFusedExperts._apply_gate, ojasx_24x96/module.py:646-651):
+ * with limit > 0 the gate value is clamped from above to limit and the up value to [-limit, limit] before
+ * silu(gate) * up; limit <= 0 (the default) applies none, which is the reference library's MoE
+ * (ojasx_lut_cpu.cpp:325). */
+OJASX_API int ojasx_b200_moe_set_gate_limit(OjasxMoEHandle handle, float limit);
 /* CSR outliers on the expert matrices (host arrays; no counterpart in the reference MoE, which
  * has none: composed like ojasx_set_linear_outliers, ojasx_lut_c_api.h:60-66).  which = 0: the
  * flattened gate_up matrix [E*2I, hidden]; which = 1: the flattened down matrix [E*hidden, I]. */
@@ -183,6 +188,15 @@ OJASX_API int ojasx_b200_moe_route(OjasxMoEHandle handle, const void* d_x, int n
 /* Router followed by the experts, one stream, no host round trip. */
 OJASX_API int ojasx_b200_moe_forward_routed(OjasxMoEHandle handle, const void* d_x, void* d_y, int n_tokens, int top_k,
                                             int io_dtype, void* stream);
+
+/* The lookup table on its own: d_lut[t, g, k] = sum_d x[t, g*block_dim + d] * codebook[k, d], d ascending, fp32,
+ * separate multiply and add -- SplitManifoldLinear::build_lut (ojasx_lut_cpu.cpp:18-102; the Python twin is
+ * SplitManifoldLUTLinear.build_lut, split_manifold_engine.py:185-199).  d_x [n_vectors, in_features] of io_dtype
+ * (features beyond in_features read as zero), d_lut f32 [n_vectors, ceil(in_features / block_dim), 256] with
+ * entries k >= codebook_size set to zero.  The forward kernels build their tables in shared memory and never
+ * call this; it exists for callers (and tests) that want kernel (a)'s result itself. */
+OJASX_API int ojasx_b200_build_lut(const void* d_x, int n_vectors, int in_features, int block_dim,
+                                   const float* d_codebook, int codebook_size, float* d_lut, int io_dtype, void* stream);
 
 /* out[i] = silu(gate[i]) * up[i] on device arrays of io_dtype: the SwiGLU step between the gate/up and
  * down linears of a dense VQ MLP block, with the silu of the expert kernels
@@ -260,6 +274,12 @@ OJASX_API int ojasx_b200_add_int(int* d_values, int count, int delta, void* stre
  * token and raises a device flag; ojasx_b200_kvq_sync_len then returns -2 once (and clears the
  * flag) instead of the length, so poll it whenever the context may have reached max_seq_len. */
 OJASX_API int ojasx_b200_kvq_set_static_plan(OjasxKvqHandle handle, int enabled);
+/* Drops the cached tokens beyond max_len of every sequence (the crop of OjasXKVCacheManager,
+ * ojasx_24x96/kv_cache.py:196-256, for this cache); returns the new length, -2 for a negative max_len.
+ * Synchronises.  ojasx_b200_kvq_get_memory_size: bytes of code storage and codebooks the cache holds
+ * (the figure ojasx_kv_cache_get_memory_size reports for the reference's cache, ojasx_lut_c_api.h:122). */
+OJASX_API int ojasx_b200_kvq_crop(OjasxKvqHandle handle, int max_len);
+OJASX_API size_t ojasx_b200_kvq_get_memory_size(OjasxKvqHandle handle);
 OJASX_API int ojasx_b200_kvq_sync_len(OjasxKvqHandle handle);
 
 /* ---- offline encoder: nearest-centroid assignment of n block vectors [n, block_dim] (fp32, 16-byte aligned)

@@ -76,6 +76,7 @@ SIGNATURES = {
     "ojasx_b200_moe_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "ojasx_b200_moe_forward_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "ojasx_b200_silu_mul": (_i, [_vp, _vp, _vp, _sz, _i, _vp]),
+    "ojasx_b200_build_lut": (_i, [_vp, _i, _i, _i, _vp, _i, _vp, _i, _vp]),
     "ojasx_b200_moe_reserve": (_i, [_vp, _i, _i]),
     "ojasx_b200_moe_set_outliers": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "ojasx_b200_moe_set_router": (_i, [_vp, _vp, _i]),
@@ -92,6 +93,9 @@ SIGNATURES = {
     "ojasx_b200_kvq_destroy": (None, [_vp]),
     "ojasx_b200_kvq_set_static_plan": (_i, [_vp, _i]),
     "ojasx_b200_kvq_sync_len": (_i, [_vp]),
+    "ojasx_b200_kvq_crop": (_i, [_vp, _i]),
+    "ojasx_b200_kvq_get_memory_size": (_sz, [_vp]),
+    "ojasx_b200_moe_set_gate_limit": (_i, [_vp, _f]),
     "ojasx_b200_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
     "ojasx_b200_rope_qk": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp]),
     "ojasx_b200_add_int": (_i, [_vp, _i, _i, _vp]),

@@ -56,6 +56,7 @@ MoeProblem MoeHandle::problem(const void* x, void* y, const int* idx, const floa
     P.E_total = E_total;
     P.n_tokens = n_tokens; P.k_active = k; P.E = E; P.expert_offset = expert_offset;
     P.H = H; P.I = I; P.G = H / D; P.Gi = I / D; P.D = D; P.Kcb = 256; P.io_dtype = io;
+    P.gate_limit = gate_limit;
     return P;
 }
 
@@ -169,6 +170,12 @@ int ojasx_b200_moe_set_expert_offset(OjasxMoEHandle handle, int first_global_exp
     return OJX_OK;
 }
 
+int ojasx_b200_moe_set_gate_limit(OjasxMoEHandle handle, float limit) {
+    if (!handle || !(limit == limit)) return OJX_ERR_ARG;
+    static_cast<MoeHandle*>(handle)->gate_limit = limit > 0.0f ? limit : 0.0f;
+    return OJX_OK;
+}
+
 int ojasx_b200_moe_reserve(OjasxMoEHandle handle, int max_tokens, int k_active) {
     if (!handle || max_tokens <= 0 || k_active <= 0) return OJX_ERR_ARG;
     auto* h = static_cast<MoeHandle*>(handle);
@@ -222,6 +229,13 @@ int ojasx_b200_moe_forward_routed(OjasxMoEHandle handle, const void* d_x, void* 
     if (rc != OJX_OK) return rc;
     P.lut_ready = P.lut_in != nullptr;
     return launch_moe_experts(P, s);
+}
+
+int ojasx_b200_build_lut(const void* d_x, int n_vectors, int in_features, int block_dim, const float* d_codebook,
+                         int codebook_size, float* d_lut, int io_dtype, void* stream) {
+    if (io_dtype != OJX_F32 && io_dtype != OJX_BF16) return OJX_ERR_ARG;
+    return launch_build_lut(d_x, io_dtype, n_vectors, in_features, block_dim, d_codebook, codebook_size, d_lut,
+                            static_cast<cudaStream_t>(stream));
 }
 
 int ojasx_b200_silu_mul(const void* d_gate, const void* d_up, void* d_out, size_t count, int io_dtype, void* stream) {
@@ -413,6 +427,25 @@ int ojasx_b200_kvq_sync_len(OjasxKvqHandle handle) {
         return OJX_ERR_RANGE;
     }
     return h->host_len;
+}
+
+int ojasx_b200_kvq_crop(OjasxKvqHandle handle, int max_len) {
+    if (!handle) return OJX_ERR_ARG;
+    auto* h = static_cast<KvqHandle*>(handle);
+    if (max_len < 0) return OJX_ERR_RANGE;
+    DeviceGuard g(h->dev);
+    std::vector<int> lens(h->B);
+    OJX_CUDA_TRY(cudaMemcpy(lens.data(), h->seq_lens, sizeof(int) * lens.size(), cudaMemcpyDeviceToHost));
+    for (int& v : lens) v = std::min(v, max_len);
+    OJX_CUDA_TRY(cudaMemcpy(h->seq_lens, lens.data(), sizeof(int) * lens.size(), cudaMemcpyHostToDevice));
+    h->host_len = *std::max_element(lens.begin(), lens.end());
+    return h->host_len;
+}
+
+size_t ojasx_b200_kvq_get_memory_size(OjasxKvqHandle handle) {
+    if (!handle) return 0;
+    auto* h = static_cast<KvqHandle*>(handle);
+    return 2 * (size_t)h->B * h->Hkv * h->max_seq * h->G + 2 * sizeof(float) * (size_t)h->Hkv * 256 * h->D;
 }
 
 void ojasx_b200_kvq_destroy(OjasxKvqHandle handle) {

@@ -83,6 +83,8 @@ struct MoeProblem {
     const int* plan;
     int mc_cmax, mc_nacc;
     int mc_debug;
+    float gate_limit;         // > 0: gate is clamped from above and up to [-limit, limit] before silu(gate) * up
+                              // (ResidualVQFusedExperts._apply_gate, ojasx_24x96/module.py:646-651); <= 0: no clamp
     int lut_blocks;
 };
 

@@ -79,6 +79,7 @@ struct MoeHandle {
     int E_total = 0;      // experts the router scores (== E unless sharded)
     int expert_offset = 0;
     int H = 0, I = 0, top_k = 0, D = 0;
+    float gate_limit = 0.0f;   // <= 0: none
     float* cb_in = nullptr;
     float* cb_down = nullptr;
     uint8_t* gu_codes = nullptr;

@@ -31,6 +31,8 @@ int take_dequant_gemm_error(int* out);
 
 // --- moe.cu
 int launch_moe_experts(MoeProblem P, cudaStream_t stream);
+int launch_build_lut(const void* x, int io_dtype, int n_vectors, int K, int D, const float* codebook, int Kcb, float* out,
+                     cudaStream_t stream);
 int launch_silu_mul(const void* gate, const void* up, void* out, size_t n, int io_dtype, cudaStream_t stream);
 // codebook .. lut_out: when lut_out is not null the gate/up tables of the tokens ([n_tokens, H/D, 256]) are
 // built by the same launch as the logits.

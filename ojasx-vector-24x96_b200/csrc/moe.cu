@@ -84,6 +84,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) moe_gate_up_kernel(const
                 gate = __fadd_rn(gate, sm.lut[lr]);
                 up = __fadd_rn(up, sm.lut[n + lr]);
             }
+            if (P.gate_limit > 0.0f) {
+                gate = fminf(gate, P.gate_limit);
+                up = fminf(fmaxf(up, -P.gate_limit), P.gate_limit);
+            }
             P.inter[(size_t)pair * P.I + i0 + lr] = __fmul_rn(silu_ref(gate), up);
         }
         __syncthreads();
@@ -509,6 +513,24 @@ int launch_moe_experts(MoeProblem P, cudaStream_t s) {
         case 32: return launch_moe_experts_t<32>(P, s);
         default: return OJX_ERR_UNSUPPORTED;
     }
+}
+
+// Lookup table of n activation vectors, out[t, g, k] = sum_d x[t, g*D + d] * cb[k, d] (kernel (a) on its own).
+int launch_build_lut(const void* x, int io_dtype, int n_vectors, int K, int D, const float* codebook, int Kcb, float* out,
+                     cudaStream_t s) {
+    if (!x || !codebook || !out || n_vectors <= 0 || K <= 0 || D <= 0 || Kcb <= 0 || Kcb > 256) return OJX_ERR_ARG;
+    const int G = (K + D - 1) / D;
+    const dim3 grid((G + 15) / 16, n_vectors);
+    switch (D) {
+        case 4: lut_prebuild_kernel<4><<<grid, 256, 0, s>>>(x, io_dtype, K, G, codebook, Kcb, out); break;
+        case 8: lut_prebuild_kernel<8><<<grid, 256, 0, s>>>(x, io_dtype, K, G, codebook, Kcb, out); break;
+        case 16: lut_prebuild_kernel<16><<<grid, 256, 0, s>>>(x, io_dtype, K, G, codebook, Kcb, out); break;
+        case 32: lut_prebuild_kernel<32><<<grid, 256, 0, s>>>(x, io_dtype, K, G, codebook, Kcb, out); break;
+        default: return OJX_ERR_UNSUPPORTED;
+    }
+    OJX_CUDA_TRY(cudaGetLastError());
+    count_launch(1);
+    return OJX_OK;
 }
 
 int take_moe_bulk_copy_error(int* out) {

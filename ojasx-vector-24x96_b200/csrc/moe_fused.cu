@@ -593,7 +593,12 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fused_kernel(const __grid_con
         for (int idx = tid; idx < C * I; idx += kThreads) {
             const int c = idx / I, i = idx - c * I;
             const float* accc = X.at<float>(X.L.acc) + c * nAcc;
-            inter[idx] = (P.mc_debug & 16) ? accc[i] : __fmul_rn(mc_silu(accc[i]), accc[I + i]);
+            float gate = accc[i], up = accc[I + i];
+            if (P.gate_limit > 0.0f) {
+                gate = fminf(gate, P.gate_limit);
+                up = fminf(fmaxf(up, -P.gate_limit), P.gate_limit);
+            }
+            inter[idx] = __fmul_rn(mc_silu(gate), up);
         }
 
         // ------------------------------------------------------------ down rows: [e*H, (e+1)*H)

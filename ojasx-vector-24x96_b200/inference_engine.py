@@ -12,11 +12,13 @@ touches VQ codes are kernels of libojasx_lut_b200.so, so one decode step is a fi
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
-from typing import List, Optional
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Optional, Tuple, Union
 
 import numpy as np
 import torch
+
+from torch import nn
 
 from . import synth
 from .ops import VQKVCache, VQLinear, VQLinearGroup, VQMoE, add_int_, rmsnorm, rope_qk_
@@ -135,6 +137,32 @@ class VQDecoderStack:
         self.pos.zero_()
         self.position = 0
 
+    def named_quantized_ops(self):
+        """(name, operator) of every VQ-coded operator of the stack, for audits."""
+        for i, l in enumerate(self.layers):
+            for n in ("q", "k", "v", "o"):
+                yield f"layers.{i}.attn.{n}_proj", getattr(l, n)
+            yield f"layers.{i}.moe", l.moe
+        yield "lm_head", self.lm_head
+
+    @torch.no_grad()
+    def decode_step_eager(self, token_ids: torch.Tensor) -> torch.Tensor:
+        """One decode step launched kernel by kernel (no CUDA-graph replay), q/k/v as separate calls: the form
+        an audit can watch.  Advances the caches like ``decode_step``."""
+        if self._graph is not None:
+            raise RuntimeError("this stack already replays a captured step; audit a stack built with use_graph=False")
+        if self.position >= self.cfg.max_seq_len:
+            raise ValueError(f"the KV caches hold max_seq_len = {self.cfg.max_seq_len} tokens; reset() before decoding further")
+        self.position += 1
+        grouped = [l.qkv for l in self.layers]
+        for l in self.layers:
+            l.qkv = None
+        try:
+            return self._enqueue_step(token_ids.to(self.device).to(torch.int64))
+        finally:
+            for l, g in zip(self.layers, grouped):
+                l.qkv = g
+
     def _enqueue_step(self, ids: torch.Tensor) -> torch.Tensor:
         cfg, B = self.cfg, self.batch
         h = self.embed[ids].to(self.dtype)
@@ -212,20 +240,200 @@ class VQDecoderStack:
         return torch.stack(out, dim=1)
 
 
-class UniversalInferenceEngine:
-    """Thin entry class with the reference's call shape: ``engine.generate(prompt_ids, max_new_tokens=...)``."""
+@dataclass
+class LayerExecutionTrace:
+    """What one quantised layer did during an audited forward pass (``ojasx_24x96/inference_engine.py:39-65``)."""
+    layer_name: str
+    module_type: str
+    codec: str
+    call_count: int = 0
+    input_shape: Tuple[int, ...] = ()
+    output_shape: Tuple[int, ...] = ()
+    output_l2_norm: float = 0.0
+    all_finite: bool = True
+    active_experts: List[int] = field(default_factory=list)
 
-    def __init__(self, model: VQDecoderStack, tokenizer=None, *, device=None, max_context_length: Optional[int] = None,
+    def to_dict(self) -> Dict[str, object]:
+        return {"layer_name": self.layer_name, "module_type": self.module_type, "codec": self.codec,
+                "call_count": self.call_count, "input_shape": list(self.input_shape),
+                "output_shape": list(self.output_shape), "output_l2_norm": round(self.output_l2_norm, 6),
+                "all_finite": self.all_finite, "active_experts": self.active_experts}
+
+
+@dataclass
+class ForwardGraphAuditReport:
+    """Summary over every quantised layer of the model (``ojasx_24x96/inference_engine.py:68-95``)."""
+    total_quantized_modules: int
+    executed_quantized_modules: int
+    all_outputs_finite: bool
+    total_forward_calls: int
+    active_moe_experts_union: List[int]
+    traces: Dict[str, LayerExecutionTrace]
+
+    @property
+    def execution_coverage_ratio(self) -> float:
+        return 1.0 if self.total_quantized_modules == 0 else self.executed_quantized_modules / self.total_quantized_modules
+
+    def to_dict(self) -> Dict[str, object]:
+        return {"total_quantized_modules": self.total_quantized_modules,
+                "executed_quantized_modules": self.executed_quantized_modules,
+                "execution_coverage_ratio": round(self.execution_coverage_ratio, 4),
+                "all_outputs_finite": self.all_outputs_finite, "total_forward_calls": self.total_forward_calls,
+                "active_moe_experts_union": self.active_moe_experts_union,
+                "traces": {k: v.to_dict() for k, v in self.traces.items()}}
+
+
+def _set_submodule(model: nn.Module, path: str, new: nn.Module) -> None:
+    parent = model
+    parts = path.split(".")
+    for p in parts[:-1]:
+        parent = getattr(parent, p)
+    setattr(parent, parts[-1], new)
+
+
+class UniversalInferenceEngine:
+    """Entry class with the reference's call shape (``ojasx_24x96/inference_engine.py:149-389``).
+
+    ``model`` is either a ``VQDecoderStack`` of this module (the decode driver of the benchmark configuration)
+    or any ``torch.nn.Module`` whose quantised layers are this package's ``ResidualVQLinear`` /
+    ``ResidualVQFusedExperts`` (what ``from_oqpack`` produces from a skeleton and a package)."""
+
+    def __init__(self, model, tokenizer=None, *, device=None, max_context_length: Optional[int] = None,
                  subspace_lut_mode: bool = True, fused_native_gemm: bool = False):
+        from .module import ResidualVQLinear
         self.model, self.tokenizer = model, tokenizer
-        self.max_context_length = max_context_length or model.cfg.max_seq_len
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        if isinstance(model, nn.Module):
+            model.eval()
+            for _, mod in model.named_modules():
+                if isinstance(mod, ResidualVQLinear):
+                    mod.set_subspace_lut_mode(subspace_lut_mode)
+                    mod.set_fused_native_gemm(fused_native_gemm)
+            self.max_context_length = int(max_context_length or 4096)
+        else:
+            self.max_context_length = int(max_context_length or model.cfg.max_seq_len)
 
     @classmethod
     def from_synthetic(cls, seed: int, cfg: StackConfig, batch: int = 1, dtype: torch.dtype = torch.float32):
         return cls(VQDecoderStack(make_stack_weights(seed, cfg), cfg, batch, dtype))
 
+    @classmethod
+    def from_oqpack(cls, skeleton_or_factory: Union[nn.Module, Callable[[], nn.Module]], package_dir, *, tokenizer=None,
+                    device="cuda", verify_checksums: bool = True, streaming_decode: bool = True,
+                    subspace_lut_mode: bool = True) -> Tuple["UniversalInferenceEngine", Dict[str, object]]:
+        """``(engine, manifest)`` from an ``.oqpack`` directory (``ojasx_24x96/inference_engine.py:190-232``): the
+        package's quantised linears replace the same-named sub-modules of the skeleton (a module, or a factory
+        that builds one), their tensors going from the shard files straight to ``device``; everything else of
+        the skeleton (norms, embeddings) is moved to ``device`` as it is.  Layers the kernels do not cover
+        are left as the skeleton has them and listed under ``manifest["skipped_layers"]``."""
+        from . import oqpack
+        skeleton = skeleton_or_factory() if callable(skeleton_or_factory) and not isinstance(skeleton_or_factory, nn.Module) \
+            else skeleton_or_factory
+        layers, skipped = oqpack.load_quantized_layers(str(package_dir), device=device, verify_checksums=verify_checksums)
+        known = dict(skeleton.named_modules())
+        for name, layer in layers.items():
+            if name not in known:
+                raise oqpack.OQPackValidationError(f"Package layer {name} has no counterpart in the skeleton")
+            _set_submodule(skeleton, name, layer)
+        model = skeleton.to(device)
+        manifest = dict(oqpack.read_manifest(str(package_dir)))
+        manifest["skipped_layers"] = skipped
+        return cls(model, tokenizer=tokenizer, device=device, subspace_lut_mode=subspace_lut_mode), manifest
+
+    def forward_any(self, *args, **kwargs) -> Any:
+        """The model's own forward on whatever inputs it takes."""
+        return self.model(*args, **kwargs)
+
+    # ------------------------------------------------------------------ audit
+    def _quantized_ops(self) -> Dict[str, Tuple[Any, str, str]]:
+        """name -> (object, module type, codec) of every top-level quantised operator of the model."""
+        from .module import ResidualVQFusedExperts, ResidualVQLinear
+        found: Dict[str, Tuple[Any, str, str]] = {}
+        if isinstance(self.model, nn.Module):
+            inside: List[str] = []
+            for name, mod in self.model.named_modules():
+                if any(name.startswith(p) for p in inside):
+                    continue
+                if isinstance(mod, ResidualVQFusedExperts):
+                    inside.append(name + ".")     # its two projections are not called on their own
+                    found[name] = (mod, "ResidualVQFusedExperts", mod.gate_up_proj.codec)
+                elif isinstance(mod, ResidualVQLinear):
+                    found[name] = (mod, "ResidualVQLinear", mod.codec)
+        else:
+            for name, op in self.model.named_quantized_ops():
+                found[name] = (op, type(op).__name__, "split_manifold_vq")
+        return found
+
+    def audit_forward_graph(self, *forward_args, **forward_kwargs) -> Tuple[Any, ForwardGraphAuditReport]:
+        """One real forward pass with every quantised linear and expert bank watched
+        (``ojasx_24x96/inference_engine.py:268-357``): call counts, shapes, output norms, finiteness and the
+        experts that were routed to.  A ``VQDecoderStack`` is stepped eagerly for this (a replayed CUDA graph runs
+        no Python), with ``forward_args`` = the token ids of one decode step."""
+        traces: Dict[str, LayerExecutionTrace] = {}
+        undo: List[Callable[[], None]] = []
+
+        def record(key: str, inputs, output) -> None:
+            tr = traces[key]
+            tr.call_count += 1
+            if inputs and isinstance(inputs[0], torch.Tensor):
+                tr.input_shape = tuple(inputs[0].shape)
+            if tr.module_type in ("ResidualVQFusedExperts", "VQMoE") and len(inputs) >= 2 and isinstance(inputs[1], torch.Tensor) \
+                    and not inputs[1].is_floating_point():
+                tr.active_experts = sorted(set(tr.active_experts).union(int(v) for v in torch.unique(inputs[1].detach()).cpu().tolist()))
+            out = output[0] if isinstance(output, tuple) else output
+            if isinstance(out, torch.Tensor):
+                tr.output_shape = tuple(out.shape)
+                tr.output_l2_norm = float(out.detach().float().norm().item())
+                tr.all_finite = tr.all_finite and bool(torch.isfinite(out).all().item())
+
+        for name, (op, mtype, codec) in self._quantized_ops().items():
+            traces[name] = LayerExecutionTrace(layer_name=name, module_type=mtype, codec=codec)
+            if isinstance(op, nn.Module):
+                h = op.register_forward_hook(lambda m, i, o, key=name: record(key, i, o))
+                undo.append(h.remove)
+            else:   # plain operator objects of the decode driver: wrap their bound methods for the duration
+                for meth in ("forward", "forward_routed"):
+                    if hasattr(op, meth):
+                        orig = getattr(op, meth)
+
+                        def wrapped(*a, _orig=orig, _key=name, _meth=meth, _op=op, **kw):
+                            out = _orig(*a, **kw)
+                            ins = a
+                            if _meth == "forward_routed":     # report the experts the layer's router chose
+                                ins = (a[0], _op.route(a[0], a[1] if len(a) > 1 else kw.get("top_k", 10))[0])
+                            record(_key, ins, out)
+                            return out
+                        setattr(op, meth, wrapped)
+                        undo.append(lambda _op=op, _meth=meth: delattr(_op, _meth))
+        try:
+            with torch.no_grad():
+                if isinstance(self.model, nn.Module):
+                    output = self.model(*forward_args, **forward_kwargs)
+                else:
+                    output = self.model.decode_step_eager(*forward_args, **forward_kwargs)
+        finally:
+            for u in undo:
+                u()
+        ran = [t for t in traces.values() if t.call_count > 0]
+        report = ForwardGraphAuditReport(
+            total_quantized_modules=len(traces), executed_quantized_modules=len(ran),
+            all_outputs_finite=all(t.all_finite for t in ran), total_forward_calls=sum(t.call_count for t in traces.values()),
+            active_moe_experts_union=sorted({e for t in traces.values() for e in t.active_experts}), traces=traces)
+        return output, report
+
     def generate(self, prompt_ids: torch.Tensor, max_new_tokens: int = 16) -> torch.Tensor:
         if prompt_ids.shape[1] + max_new_tokens > self.max_context_length:
             raise ValueError("prompt plus generated tokens exceed max_context_length")
+        if isinstance(self.model, nn.Module):
+            # generic module: logits [B, S, V] from token ids, greedy arg-max (engine.py:213-214), no cache
+            ids = prompt_ids.to(self.device)
+            out = []
+            with torch.no_grad():
+                for _ in range(max_new_tokens):
+                    logits = self.model(ids)
+                    nxt = torch.argmax(logits[:, -1].float(), dim=-1)
+                    out.append(nxt)
+                    ids = torch.cat([ids, nxt[:, None]], dim=1)
+            return torch.stack(out, dim=1)
         self.model.reset()
         return self.model.generate(prompt_ids, max_new_tokens)

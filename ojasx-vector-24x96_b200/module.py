@@ -58,15 +58,78 @@ class ResidualVQLinear(nn.Module):
 
 
 class ResidualVQFusedExperts(nn.Module):
-    """Expert bank of an MoE block in split-manifold code form.  ``weights`` is a
-    ``synth.VQMoEWeights``-shaped object (gate rows then up rows per expert, as the reference
-    flattens them, ``module.py:620-631, 647``)."""
+    """Expert bank of an MoE block, with the constructor and call of the reference adapter
+    (``ojasx_24x96/module.py:577-708``): ``gate_up_proj`` is ONE ``ResidualVQLinear`` over the flattened
+    ``[E * 2I, H]`` matrix (expert ``e`` = rows ``[e * 2I, (e + 1) * 2I)``, gate rows then up rows, ``:620-631, 647``)
+    and ``down_proj`` one over ``[E * H, I]``; ``gate_limit`` clamps the gate from above and the up value to
+    ``[-limit, limit]`` before ``act_fn(gate) * up`` (``_apply_gate``, ``:646-651``).
 
-    def __init__(self, weights, expert_range=None):
+    The two projections must be in the split-manifold layout (8-bit codes, one stage: one shared codebook per
+    projection, as ``SplitManifoldMoE`` has, ``ojasx_lut.h:156-242``) and ``act_fn`` must be SiLU: that is what the
+    expert kernels evaluate.  Their buffers -- ``packed_codes``, ``codebooks``, ``row_scales`` and the optional CSR
+    outliers over the flattened rows -- are handed to the library once, at construction.
+    ``ResidualVQFusedExperts.from_weights`` builds the same module from a ``synth.VQMoEWeights``-shaped object.
+    """
+
+    def __init__(self, num_experts: int, hidden_dim: int, intermediate_dim: int, *, gate_up_proj, down_proj,
+                 act_fn: Optional[nn.Module] = None, gate_limit: Optional[float] = None, expert_range=None) -> None:
         super().__init__()
-        self.num_experts = weights.num_experts
-        self.hidden_dim, self.intermediate_dim = weights.hidden, weights.inter
-        self._moe = VQMoE(weights, expert_range)
+        if min(num_experts, hidden_dim, intermediate_dim) <= 0:
+            raise ValueError("Expert-bank dimensions must be positive")
+        if gate_limit is not None and (not np.isfinite(gate_limit) or gate_limit <= 0):
+            raise ValueError("Expert gate limit must be finite and positive")
+        if act_fn is not None and not isinstance(act_fn, nn.SiLU) and getattr(act_fn, "__name__", "") not in ("silu",):
+            raise ValueError("the expert kernels evaluate SiLU-gated experts only")
+        self.num_experts, self.hidden_dim, self.intermediate_dim = int(num_experts), int(hidden_dim), int(intermediate_dim)
+        self.gate_up_proj, self.down_proj = gate_up_proj, down_proj
+        self.act_fn = act_fn if act_fn is not None else nn.SiLU()
+        self.gate_limit = float(gate_limit) if gate_limit is not None else None
+        self.streaming_decode = True     # dense expert weights are never formed here
+        self._moe = VQMoE(self._bank_arrays(), expert_range)
+        self._moe.set_gate_limit(self.gate_limit)
+
+    def _bank_arrays(self):
+        from types import SimpleNamespace
+        E, H, I = self.num_experts, self.hidden_dim, self.intermediate_dim
+        gu, dn = self.gate_up_proj, self.down_proj
+        for name, proj, rows, cols in (("gate_up_proj", gu, E * 2 * I, H), ("down_proj", dn, E * H, I)):
+            if not isinstance(proj, ResidualVQLinear):
+                raise TypeError(f"{name} must be a ResidualVQLinear over the flattened expert rows")
+            if (proj.out_features, proj.in_features) != (rows, cols):
+                raise ValueError(f"{name} is {proj.out_features} x {proj.in_features}, expected {rows} x {cols}")
+            if proj.bits_per_stage != 8 or proj.codebooks.shape[0] != 1 or proj.bias is not None:
+                raise ValueError(f"{name}: the expert kernels need 8-bit codes, one stage and no bias")
+        if gu.block_size != dn.block_size:
+            raise ValueError("gate_up_proj and down_proj must share block_size")
+        D = gu.block_size
+
+        def csr(p):
+            return None if p.csr_values is None else tuple(t.detach().cpu().numpy() for t in (p.csr_row_ptrs, p.csr_col_indices, p.csr_values))
+
+        return SimpleNamespace(
+            num_experts=E, hidden=H, inter=I, block_dim=D, router=None,
+            codebook=gu.codebooks[0].detach().cpu().numpy(), down_codebook=dn.codebooks[0].detach().cpu().numpy(),
+            gate_up_codes=gu.packed_codes.detach().cpu().numpy().reshape(E, 2 * I, H // D),
+            gate_up_scales=gu.row_scales.detach().cpu().numpy().reshape(E, 2 * I),
+            down_codes=dn.packed_codes.detach().cpu().numpy().reshape(E, H, I // D),
+            down_scales=dn.row_scales.detach().cpu().numpy().reshape(E, H),
+            gate_up_csr=csr(gu), down_csr=csr(dn))
+
+    @classmethod
+    def from_weights(cls, weights, expert_range=None, gate_limit: Optional[float] = None) -> "ResidualVQFusedExperts":
+        """From arrays in ``SplitManifoldMoE`` layout (``synth.VQMoEWeights``): wraps them as the two flattened
+        ``ResidualVQLinear`` projections first, so both construction routes hold the same buffers."""
+        E, H, I = weights.num_experts, weights.hidden, weights.inter
+
+        def proj(codes, codebook, scales, csr_arrays):
+            enc = encode_uint8_layout(codes.reshape(-1, codes.shape[-1]), codebook, scales.reshape(-1), "cpu")
+            if csr_arrays is not None:
+                enc.outliers = tuple(torch.from_numpy(np.ascontiguousarray(a)) for a in csr_arrays)
+            return ResidualVQLinear(enc)
+
+        return cls(E, H, I, gate_up_proj=proj(weights.gate_up_codes, weights.codebook, weights.gate_up_scales, weights.gate_up_csr),
+                   down_proj=proj(weights.down_codes, weights.down_codebook, weights.down_scales, weights.down_csr),
+                   act_fn=nn.SiLU(), gate_limit=gate_limit, expert_range=expert_range)
 
     @torch.no_grad()
     def forward(self, hidden_states: torch.Tensor, top_k_index: torch.Tensor, top_k_weights: torch.Tensor) -> torch.Tensor:

@@ -92,7 +92,8 @@ class VQLinear:
               "ojasx_b200_linear_forward")
         return out.reshape(*x.shape[:-1], rows)
 
-    __call__ = forward
+    def __call__(self, *args, **kwargs):
+        return self.forward(*args, **kwargs)
 
     def forward_tensor(self, x: torch.Tensor, row_start: int = 0, row_stop: Optional[int] = None) -> torch.Tensor:
         """bf16 batch on the tensor cores (tcgen05 dequant GEMM); tolerance of the bf16 path, not bit-exact."""
@@ -248,6 +249,10 @@ class VQMoE:
     def reserve(self, max_tokens: int, k: int = 10):
         check(lib().ojasx_b200_moe_reserve(self._h, max_tokens, k), "ojasx_b200_moe_reserve")
 
+    def set_gate_limit(self, limit: Optional[float]):
+        """Clamp of ``ResidualVQFusedExperts._apply_gate`` (module.py:646-651); ``None`` or ``<= 0`` removes it."""
+        check(lib().ojasx_b200_moe_set_gate_limit(self._h, float(limit or 0.0)), "ojasx_b200_moe_set_gate_limit")
+
     def forward(self, x: torch.Tensor, top_k_index: torch.Tensor, top_k_weights: torch.Tensor) -> torch.Tensor:
         """Argument order of ``ResidualVQFusedExperts.forward`` (ojasx_24x96/module.py:653-658)."""
         _require_cuda(x, "hidden_states")
@@ -334,6 +339,17 @@ class VQKVCache:
 
     def sync_len(self) -> int:
         return lib().ojasx_b200_kvq_sync_len(self._h)
+
+    def crop(self, max_length: int) -> int:
+        """Forget the tokens beyond ``max_length`` of every sequence; returns the new length."""
+        n = lib().ojasx_b200_kvq_crop(self._h, int(max_length))
+        if n < 0:
+            check(n, "ojasx_b200_kvq_crop")
+        return n
+
+    @property
+    def memory_bytes(self) -> int:
+        return int(lib().ojasx_b200_kvq_get_memory_size(self._h))
 
     def append(self, k: torch.Tensor, v: torch.Tensor):
         _require_cuda(k, "k")

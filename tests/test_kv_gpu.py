@@ -65,6 +65,41 @@ def test_kvq_decode_shapes_and_long_ranges(cuda, oracle, B, ctx, kv_heads, q_hea
     assert np.allclose(again, want, rtol=1e-4, atol=2e-6), np.abs(again - want).max()
 
 
+@pytest.mark.parametrize("B,ctx,samples", [(1, 32768, [(0, 0), (0, 5)]), (16, 32768, [(0, 1), (7, 3), (15, 7)]),
+                                           (1, 131072, [(0, 2), (0, 7)])])
+def test_kvq_decode_baseline_contexts(cuda, oracle, B, ctx, samples):
+    """Configuration 3 at its long contexts (32 query / 8 KV heads of 128, 16 codes per vector), one appended token
+    then one decode query.  The CPU oracle (fp64 online softmax, pinned to the reference's
+    OnlineSoftmaxBlockAttention) checks a sample of (sequence, KV head) pairs to bound its run time.
+
+    Tolerance: the kernel accumulates scores, the softmax normaliser and the context vector in fp32 over `ctx`
+    terms while the oracle (like the reference's attention) works in fp64; rounding alone gives about
+    sqrt(ctx) * 2^-24 ~ 1e-5 relative to the sum of magnitudes at these lengths, so the comparison allows
+    rel 1e-4 / abs 2e-6 and reports the largest deviation it saw."""
+    kv = synth.make_vq_kv(ctx + B, B, ctx)
+    cache = ops.VQKVCache(B, kv.kv_heads, kv.q_heads, kv.head_dim, kv.block_dim, ctx + 64, kv.k_codebook, kv.v_codebook)
+    cache.load(kv.k_codes, kv.v_codes)
+    cache.append(torch.from_numpy(kv.new_k).to(cuda), torch.from_numpy(kv.new_v).to(cuda))
+    gk, gv = cache.read(ctx, ctx + 1)
+    got = cache.decode(torch.from_numpy(kv.q).to(cuda)).cpu().numpy()
+    qb = synth.to_bf16_f32(kv.q)
+    got_b = cache.decode(torch.from_numpy(qb).to(cuda).to(torch.bfloat16)).float().cpu().numpy()
+    R = kv.q_heads // kv.kv_heads
+    worst = 0.0
+    for b, h in samples:
+        assert np.array_equal(gk[b, h, 0], oracle.kvq_encode(kv.new_k[b, h], kv.k_codebook[h], block_dim=kv.block_dim))
+        kc = np.concatenate([kv.k_codes[b, h], gk[b, h]], axis=0)
+        vc = np.concatenate([kv.v_codes[b, h], gv[b, h]], axis=0)
+        want = oracle.kvq_decode(kv.q[b, h * R:(h + 1) * R], kc, vc, kv.k_codebook[h], kv.v_codebook[h], block_dim=kv.block_dim)
+        g = got[b, h * R:(h + 1) * R]
+        assert np.allclose(g, want, rtol=1e-4, atol=2e-6), np.abs(g - want).max()
+        worst = max(worst, float(np.max(np.abs(g - want) / (np.abs(want) + 1e-3))))
+        want_b = oracle.kvq_decode(qb[b, h * R:(h + 1) * R], kc, vc, kv.k_codebook[h], kv.v_codebook[h], block_dim=kv.block_dim)
+        assert np.allclose(got_b[b, h * R:(h + 1) * R], want_b, rtol=2e-2, atol=2e-3)
+    print(f"B={B} ctx={ctx}: largest |got - want| / (|want| + 1e-3) = {worst:.2e}")
+    cache.close()
+
+
 def test_kvq_full_and_errors(cuda):
     kv = synth.make_vq_kv(1, 1, 4)
     cache = ops.VQKVCache(1, 8, 32, 128, 8, 4, kv.k_codebook, kv.v_codebook)

@@ -178,3 +178,19 @@ def test_pack_codes_matches_reference_bit_layout():
         assert np.array_equal(packed.numpy(), GOLD[f"pack/bits{bits}"])
         assert torch.equal(codec.unpack_codes(packed, bits, codes.numel()).long(), codes)
     assert codec.pack_codes(torch.tensor([1, 2, 3, 0]), 2).tolist() == [0b00111001]
+
+
+def test_kvq_oracle_against_reference_functions(oracle):
+    """The codebook-VQ KV oracle against outputs of the reference's own code (tests/golden/kvq_ref.npz, written by
+    tests/golden/make_kvq_fixture.py): codes from ojasx_24x96.codec._nearest (codec.py:217-224) and attention from
+    OnlineSoftmaxBlockAttention.forward_stream (long_context.py:92-176) over the dequantised cache."""
+    ref = np.load(os.path.join(os.path.dirname(__file__), "golden", "kvq_ref.npz"))
+    HQ, HKV, HD, D, CTX, TILE = (int(v) for v in ref["shape"])
+    codes = oracle.kvq_encode(ref["enc_vectors"], ref["enc_codebook"], block_dim=D)
+    assert np.array_equal(codes, ref["enc_codes"])
+    R = HQ // HKV
+    for tile in (256, TILE, 64):       # the oracle's own tile size must not matter; the reference used TILE
+        got = np.concatenate([oracle.kvq_decode(ref["dec_q"][h * R:(h + 1) * R], ref["dec_k_codes"][h], ref["dec_v_codes"][h],
+                                                ref["dec_k_codebook"][h], ref["dec_v_codebook"][h], block_dim=D, kv_block=tile)
+                              for h in range(HKV)])
+        assert np.allclose(got, ref["dec_out"], rtol=1e-11, atol=1e-14), np.abs(got - ref["dec_out"]).max()

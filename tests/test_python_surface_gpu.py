@@ -130,7 +130,7 @@ def test_module_toggles_descriptor_and_ggml_dispatch(cuda):
 
 def test_fused_experts_module_signature(cuda, oracle):
     w = synth.make_vq_moe(4, 8, 256, 64, block_dim=8, outlier_frac=0.0)
-    experts = module.ResidualVQFusedExperts(w)
+    experts = module.ResidualVQFusedExperts.from_weights(w)
     x = np.random.default_rng(1).standard_normal((3, 256)).astype(np.float32)
     idx = np.array([[0, 3], [7, 1], [2, 2]], np.int64)
     wts = np.array([[0.6, 0.4], [0.5, 0.5], [0.9, 0.1]], np.float32)
