@@ -232,6 +232,52 @@ OJASX_API int ojasx_b200_moe_forward_noalloc(OjasxMoEHandle handle, const void* 
                                              const float* d_topk_w, void* d_y, int n_tokens, int k_active,
                                              int io_dtype, void* stream);
 
+/* ---- Exchange between the GPUs of one box over peer memory, fused into the producing kernel (no counterpart
+ * in the reference, which has no multi-device code; the row contract it serves is row_start / row_stop of
+ * rvq_fused_gemm, ojasx_24x96/native/ojasx_backend_abi.h:97-111).  Every rank allocates one segment of the same
+ * size, exports it, opens the others' (CUDA IPC: one process per GPU on one machine) and makes a link from the
+ * n mappings.  Buffers that take part in an exchange live at the same offset in every rank's segment; n ints at
+ * flags_offset are the link's flags.  A "gather" entry point stores its shard into every rank's segment and then
+ * raises this rank's flag everywhere; ojasx_b200_peer_wait (or the consumer kernel of this library) polls all
+ * flags before the gathered buffer is read.  Waits are bounded (a few seconds): a rank that never signals
+ * raises ojasx_b200_peer_take_status instead of hanging.  A buffer may be written again two exchanges later;
+ * repeat one exchange on two alternating buffers.  Plain loads and stores only: no multicast of any kind. */
+#define OJASX_B200_PEER_HANDLE_BYTES 64
+typedef void* OjasxPeerLinkHandle;
+OJASX_API void* ojasx_b200_peer_alloc(size_t bytes);                                  /* zero-filled device segment */
+OJASX_API int ojasx_b200_peer_free(void* d_segment);
+OJASX_API int ojasx_b200_peer_export(void* d_segment, unsigned char* handle_out);    /* 64 bytes to send to the others */
+OJASX_API void* ojasx_b200_peer_open(const unsigned char* handle);                   /* mapping of another rank's segment */
+OJASX_API int ojasx_b200_peer_close(void* d_mapped);
+OJASX_API OjasxPeerLinkHandle ojasx_b200_peer_link_create(void* const* d_segments, int n_ranks, int self,
+                                                          size_t flags_offset);
+OJASX_API void ojasx_b200_peer_link_destroy(OjasxPeerLinkHandle link);
+OJASX_API int ojasx_b200_peer_signal(OjasxPeerLinkHandle link, void* stream);       /* for producers outside this library */
+OJASX_API int ojasx_b200_peer_wait(OjasxPeerLinkHandle link, void* stream);
+OJASX_API int ojasx_b200_peer_take_status(OjasxPeerLinkHandle link);                 /* 1: a wait ran out since the last call */
+/* Rows [row_start, row_stop) of the layer into columns [row_start, row_stop) of d_y_full [batch, out_features]
+ * on every rank (d_y_full inside the link's segment), then the flag: the row-split linear with its all-gather.
+ * An empty row range only raises the flag. */
+OJASX_API int ojasx_b200_linear_forward_gather(OjasxLinearHandle handle, const void* d_x, void* d_y_full, int batch_size,
+                                               int io_dtype, int row_start, int row_stop, OjasxPeerLinkHandle link,
+                                               void* stream);
+/* The same for a group: set_rows restricts every member to rows [row_start, row_stop) (clipped to its size);
+ * forward_gather writes the gathered layout ([.., out_features] per problem at y_stride_bytes) on every rank. */
+OJASX_API int ojasx_b200_linear_group_set_rows(OjasxLinearGroupHandle group, int row_start, int row_stop);
+OJASX_API int ojasx_b200_linear_group_forward_gather(OjasxLinearGroupHandle group, const void* d_x, size_t x_stride_bytes,
+                                                     void* d_y_full, size_t y_stride_bytes, int io_dtype,
+                                                     OjasxPeerLinkHandle link, void* stream);
+/* Expert-parallel MoE: this handle's experts are evaluated, every (token, expert) output row goes to
+ * d_expert_out_shared [n_tokens * k, hidden] (inside the segment) on every rank, and the combine -- which waits for
+ * all flags -- adds a token's k rows in caller order on every rank: d_y is the full layer output everywhere, with
+ * the bits a single device produces. */
+OJASX_API int ojasx_b200_moe_forward_gather(OjasxMoEHandle handle, const void* d_x, const int* d_topk_idx,
+                                            const float* d_topk_w, void* d_y, int n_tokens, int k_active, int io_dtype,
+                                            OjasxPeerLinkHandle link, float* d_expert_out_shared, void* stream);
+OJASX_API int ojasx_b200_moe_forward_routed_gather(OjasxMoEHandle handle, const void* d_x, void* d_y, int n_tokens,
+                                                   int top_k, int io_dtype, OjasxPeerLinkHandle link,
+                                                   float* d_expert_out_shared, void* stream);
+
 /* ---- Codebook-VQ KV cache of one layer (no counterpart in the reference, whose HeadKVCache
  * allocates k_codebook / v_codebook but never reads them, ojasx_lut_kv_cache.h:33-35): every
  * head vector is head_dim/block_dim uint8 codes into a per-KV-head codebook
@@ -266,6 +312,13 @@ OJASX_API int ojasx_b200_rmsnorm(void* d_x, const void* d_add, const float* d_we
 OJASX_API int ojasx_b200_rope_qk(void* d_q, void* d_k, const int* d_positions, int batch, int q_heads, int kv_heads,
                                  int head_dim, float theta, int io_dtype, void* stream);
 OJASX_API int ojasx_b200_add_int(int* d_values, int count, int delta, void* stream);
+/* KV-head shard: this cache holds some of the layer's KV heads (with their query heads); its attention outputs go
+ * to heads [first_q_head, first_q_head + q_heads) of d_out_full [batch, total_q_heads, head_dim] on every rank of the
+ * link (d_out_full inside the link's segment), then the flag is raised: the all-gather of head-sharded attention,
+ * fused into the decode kernel.  Wait with ojasx_b200_peer_wait before reading d_out_full. */
+OJASX_API int ojasx_b200_kvq_decode_gather(OjasxKvqHandle handle, const void* d_q, void* d_out_full, float scale,
+                                           int io_dtype, int total_q_heads, int first_q_head, OjasxPeerLinkHandle link,
+                                           void* stream);
 /* Plan decode launches for the cache's capacity instead of its current length, and let the device-side
  * length be the only one consulted: the launch sequence of append/decode then never changes as the
  * context grows, so it can be replayed from a CUDA graph.  ojasx_b200_kvq_seq_len stays at the value of

@@ -90,12 +90,28 @@ SIGNATURES = {
     "ojasx_b200_kvq_reset": (_i, [_vp]),
     "ojasx_b200_kvq_append": (_i, [_vp, _vp, _vp, _i, _vp]),
     "ojasx_b200_kvq_decode": (_i, [_vp, _vp, _vp, _f, _i, _vp]),
+    "ojasx_b200_kvq_decode_gather": (_i, [_vp, _vp, _vp, _f, _i, _i, _i, _vp, _vp]),
     "ojasx_b200_kvq_destroy": (None, [_vp]),
     "ojasx_b200_kvq_set_static_plan": (_i, [_vp, _i]),
     "ojasx_b200_kvq_sync_len": (_i, [_vp]),
     "ojasx_b200_kvq_crop": (_i, [_vp, _i]),
     "ojasx_b200_kvq_get_memory_size": (_sz, [_vp]),
     "ojasx_b200_moe_set_gate_limit": (_i, [_vp, _f]),
+    "ojasx_b200_peer_alloc": (_vp, [_sz]),
+    "ojasx_b200_peer_free": (_i, [_vp]),
+    "ojasx_b200_peer_export": (_i, [_vp, _vp]),
+    "ojasx_b200_peer_open": (_vp, [_vp]),
+    "ojasx_b200_peer_close": (_i, [_vp]),
+    "ojasx_b200_peer_link_create": (_vp, [_vp, _i, _i, _sz]),
+    "ojasx_b200_peer_link_destroy": (None, [_vp]),
+    "ojasx_b200_peer_signal": (_i, [_vp, _vp]),
+    "ojasx_b200_peer_wait": (_i, [_vp, _vp]),
+    "ojasx_b200_peer_take_status": (_i, [_vp]),
+    "ojasx_b200_linear_forward_gather": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
+    "ojasx_b200_linear_group_set_rows": (_i, [_vp, _i, _i]),
+    "ojasx_b200_linear_group_forward_gather": (_i, [_vp, _vp, _sz, _vp, _sz, _i, _vp, _vp]),
+    "ojasx_b200_moe_forward_gather": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
+    "ojasx_b200_moe_forward_routed_gather": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
     "ojasx_b200_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
     "ojasx_b200_rope_qk": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp]),
     "ojasx_b200_add_int": (_i, [_vp, _i, _i, _vp]),

@@ -4,6 +4,7 @@
 #include "../../include/ojasx_lut_b200.h"
 #include "handles.h"
 #include "launch.h"
+#include "peer.cuh"
 
 #include <atomic>
 #include <cstdio>
@@ -186,6 +187,19 @@ int ojasx_b200_linear_forward(OjasxLinearHandle handle, const void* d_x, void* d
     return launch_linear(P, static_cast<cudaStream_t>(stream));
 }
 
+int ojasx_b200_linear_forward_gather(OjasxLinearHandle handle, const void* d_x, void* d_y_full, int batch_size, int io_dtype,
+                                     int row_start, int row_stop, OjasxPeerLinkHandle link, void* stream) {
+    if (!handle || !d_x || !d_y_full || !link) return OJX_ERR_ARG;
+    auto* h = static_cast<LinearHandle*>(handle);
+    if (batch_size <= 0 || row_start < 0 || row_stop > h->out || row_start > row_stop) return OJX_ERR_ARG;
+    if (io_dtype != OJX_F32 && io_dtype != OJX_BF16) return OJX_ERR_ARG;
+    if (row_start == row_stop) return ojasx_b200_peer_signal(link, stream);   // a rank without rows still takes part
+    LinearProblem P = h->problem(d_x, d_y_full, batch_size, io_dtype, row_start, row_stop);
+    P.y_full = 1;
+    P.y_ld = h->out;
+    return launch_linear(P, static_cast<cudaStream_t>(stream), peer_link_of(link));
+}
+
 int ojasx_b200_linear_forward_raw(const uint8_t* d_codes, const float* d_codebook, const float* d_scales,
                                   const float* d_bias, int nnz, const int* d_row_ptrs, const int* d_col_indices,
                                   const float* d_values, const void* d_x, void* d_y, int batch_size, int io_dtype,
@@ -361,18 +375,20 @@ OjasxLinearGroupHandle ojasx_b200_create_linear_group(const OjasxLinearHandle* h
     return g;
 }
 
-int ojasx_b200_linear_group_forward(OjasxLinearGroupHandle group, const void* d_x, size_t x_stride_bytes, void* d_y,
-                                    size_t y_stride_bytes, int io_dtype, void* stream) {
+static int linear_group_forward(OjasxLinearGroupHandle group, const void* d_x, size_t x_stride_bytes, void* d_y,
+                                size_t y_stride_bytes, int io_dtype, void* stream, const PeerLink* link) {
     if (!group || !d_x || !d_y) return OJX_ERR_ARG;
     if (io_dtype != OJX_F32 && io_dtype != OJX_BF16) return OJX_ERR_ARG;
     auto* g = static_cast<LinearGroup*>(group);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int y_full = link ? 1 : 0;
+    if (g->bound_full != y_full) { g->bound_full = y_full; g->bound_x = nullptr; }
     // A layer whose outliers were replaced since the snapshot: take its arrays again and rewrite the table.
     for (size_t i = 0; i < g->host.size(); ++i) {
         const LinearHandle* h = g->members[i];
         if (h->generation == g->member_generation[i]) continue;
         const LinearProblem old = g->host[i];
-        LinearProblem P = h->problem(old.x, old.y, 1, old.io_dtype, 0, h->out);
+        LinearProblem P = h->problem(old.x, old.y, 1, old.io_dtype, old.row_start, old.row_stop);
         P.tile_rows = old.tile_rows; P.tiles = old.tiles; P.item_begin = old.item_begin;
         g->host[i] = P;
         g->member_generation[i] = h->generation;
@@ -387,8 +403,10 @@ int ojasx_b200_linear_group_forward(OjasxLinearGroupHandle group, const void* d_
             tmp[i].x = static_cast<const char*>(d_x) + i * x_stride_bytes;
             tmp[i].y = static_cast<char*>(d_y) + i * y_stride_bytes;
             tmp[i].io_dtype = io_dtype;
+            tmp[i].y_full = y_full;
+            tmp[i].y_ld = g->members[i]->out;
         }
-        const int rc = try_launch_linear_cluster_group(tmp, (int)g->host.size(), s);
+        const int rc = try_launch_linear_cluster_group(tmp, (int)g->host.size(), s, link);
         if (rc != OJX_ERR_UNSUPPORTED) return rc;
     }
     // The problem table is rewritten only when the I/O binding changes, so steady-state calls
@@ -399,6 +417,8 @@ int ojasx_b200_linear_group_forward(OjasxLinearGroupHandle group, const void* d_
             g->host[i].x = static_cast<const char*>(d_x) + i * x_stride_bytes;
             g->host[i].y = static_cast<char*>(d_y) + i * y_stride_bytes;
             g->host[i].io_dtype = io_dtype;
+            g->host[i].y_full = y_full;
+            g->host[i].y_ld = g->members[i]->out;
         }
         OJX_CUDA_TRY(cudaMemcpyAsync(g->dev_probs, g->host.data(), sizeof(LinearProblem) * g->host.size(),
                                      cudaMemcpyHostToDevice, s));
@@ -406,7 +426,39 @@ int ojasx_b200_linear_group_forward(OjasxLinearGroupHandle group, const void* d_
         g->bound_x = d_x; g->bound_y = d_y; g->bound_xs = x_stride_bytes; g->bound_ys = y_stride_bytes;
         g->bound_dtype = io_dtype;
     }
-    return launch_linear_group(g->dev_probs, (int)g->host.size(), g->total_items, g->D, s);
+    return launch_linear_group(g->dev_probs, (int)g->host.size(), g->total_items, g->D, s, link);
+}
+
+int ojasx_b200_linear_group_forward(OjasxLinearGroupHandle group, const void* d_x, size_t x_stride_bytes, void* d_y,
+                                    size_t y_stride_bytes, int io_dtype, void* stream) {
+    return linear_group_forward(group, d_x, x_stride_bytes, d_y, y_stride_bytes, io_dtype, stream, nullptr);
+}
+
+int ojasx_b200_linear_group_forward_gather(OjasxLinearGroupHandle group, const void* d_x, size_t x_stride_bytes,
+                                           void* d_y_full, size_t y_stride_bytes, int io_dtype, OjasxPeerLinkHandle link,
+                                           void* stream) {
+    if (!link) return OJX_ERR_ARG;
+    return linear_group_forward(group, d_x, x_stride_bytes, d_y_full, y_stride_bytes, io_dtype, stream, peer_link_of(link));
+}
+
+int ojasx_b200_linear_group_set_rows(OjasxLinearGroupHandle group, int row_start, int row_stop) {
+    if (!group) return OJX_ERR_ARG;
+    auto* g = static_cast<LinearGroup*>(group);
+    int item = 0;
+    for (size_t i = 0; i < g->host.size(); ++i) {
+        const LinearHandle* h = g->members[i];
+        const int a = row_start < 0 ? 0 : row_start, b = row_stop > h->out ? h->out : row_stop;
+        if (a >= b) return OJX_ERR_ARG;
+        LinearProblem& P = g->host[i];
+        P.row_start = a; P.row_stop = b;
+        P.tile_rows = plan_tile_rows(b - a, (int)g->host.size());
+        P.tiles = (b - a + P.tile_rows - 1) / P.tile_rows;
+        P.item_begin = item;
+        item += P.tiles;
+    }
+    g->total_items = item;
+    g->bound_x = nullptr;   // the device table is rewritten by the next forward
+    return OJX_OK;
 }
 
 void ojasx_b200_destroy_linear_group(OjasxLinearGroupHandle group) {

@@ -6,6 +6,7 @@
 
 #include "handles.h"
 #include "launch.h"
+#include "peer.cuh"
 
 #include <algorithm>
 #include <cmath>
@@ -195,6 +196,43 @@ int ojasx_b200_moe_forward(OjasxMoEHandle handle, const void* d_x, const int* d_
                               static_cast<cudaStream_t>(stream));
 }
 
+int ojasx_b200_moe_forward_gather(OjasxMoEHandle handle, const void* d_x, const int* d_topk_idx, const float* d_topk_w,
+                                  void* d_y, int n_tokens, int k_active, int io_dtype, OjasxPeerLinkHandle link,
+                                  float* d_expert_out_shared, void* stream) {
+    if (!handle || !d_x || !d_topk_idx || !d_topk_w || !d_y || !link || !d_expert_out_shared) return OJX_ERR_ARG;
+    if (n_tokens <= 0 || k_active <= 0 || (io_dtype != OJX_F32 && io_dtype != OJX_BF16)) return OJX_ERR_ARG;
+    auto* h = static_cast<MoeHandle*>(handle);
+    if (int drc = moe_check_device(h, "ojasx_b200_moe_forward_gather")) return drc;
+    int rc = h->reserve(n_tokens, k_active);
+    if (rc != OJX_OK) return rc;
+    MoeProblem P = h->problem(d_x, d_y, d_topk_idx, d_topk_w, n_tokens, k_active, io_dtype);
+    P.expert_out = d_expert_out_shared;
+    return launch_moe_experts(P, static_cast<cudaStream_t>(stream), peer_link_of(link));
+}
+
+int ojasx_b200_moe_forward_routed_gather(OjasxMoEHandle handle, const void* d_x, void* d_y, int n_tokens, int top_k,
+                                         int io_dtype, OjasxPeerLinkHandle link, float* d_expert_out_shared, void* stream) {
+    if (!handle || !d_x || !d_y || n_tokens <= 0 || top_k <= 0 || !link || !d_expert_out_shared) return OJX_ERR_ARG;
+    auto* h = static_cast<MoeHandle*>(handle);
+    if (!h->router) { set_last_error_msg("moe_forward_routed_gather: no router weights set"); return OJX_ERR_ARG; }
+    if (int drc = moe_check_device(h, "ojasx_b200_moe_forward_routed_gather")) return drc;
+    int rc = h->reserve(n_tokens, top_k);
+    if (rc != OJX_OK) return rc;
+    float* logits = static_cast<float*>(h->route_scratch);
+    float* probs = logits + (size_t)n_tokens * h->E_total;
+    int* idx = reinterpret_cast<int*>(probs + (size_t)n_tokens * h->E_total);
+    float* w = reinterpret_cast<float*>(idx + (size_t)n_tokens * top_k);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    MoeProblem P = h->problem(d_x, d_y, idx, w, n_tokens, top_k, io_dtype);
+    P.expert_out = d_expert_out_shared;
+    P.lut_blocks = moe_fused_wanted(P) ? 1 : 0;
+    rc = launch_moe_router(h->router, d_x, io_dtype, n_tokens, h->H, h->E_total, top_k, logits, probs, idx, w, s,
+                           P.cb_in, P.Kcb, P.D, const_cast<float*>(P.lut_in), P.lut_blocks);
+    if (rc != OJX_OK) return rc;
+    P.lut_ready = P.lut_in != nullptr;
+    return launch_moe_experts(P, s, peer_link_of(link));
+}
+
 int ojasx_b200_moe_route(OjasxMoEHandle handle, const void* d_x, int n_tokens, int top_k, int* d_idx_out, float* d_w_out,
                          int io_dtype, void* stream) {
     if (!handle || !d_x || !d_idx_out || !d_w_out || n_tokens <= 0 || top_k <= 0) return OJX_ERR_ARG;
@@ -378,7 +416,23 @@ int ojasx_b200_kvq_append(OjasxKvqHandle handle, const void* d_k, const void* d_
     return rc;
 }
 
+static int kvq_decode_impl(OjasxKvqHandle handle, const void* d_q, void* d_out, float scale, int io_dtype, void* stream,
+                           int out_heads, int out_head0, const PeerLink* link);
+
 int ojasx_b200_kvq_decode(OjasxKvqHandle handle, const void* d_q, void* d_out, float scale, int io_dtype, void* stream) {
+    return kvq_decode_impl(handle, d_q, d_out, scale, io_dtype, stream, 0, 0, nullptr);
+}
+
+int ojasx_b200_kvq_decode_gather(OjasxKvqHandle handle, const void* d_q, void* d_out_full, float scale, int io_dtype,
+                                 int total_q_heads, int first_q_head, OjasxPeerLinkHandle link, void* stream) {
+    if (!link || !handle) return OJX_ERR_ARG;
+    auto* h = static_cast<KvqHandle*>(handle);
+    if (first_q_head < 0 || first_q_head + h->Hq > total_q_heads) return OJX_ERR_RANGE;
+    return kvq_decode_impl(handle, d_q, d_out_full, scale, io_dtype, stream, total_q_heads, first_q_head, peer_link_of(link));
+}
+
+static int kvq_decode_impl(OjasxKvqHandle handle, const void* d_q, void* d_out, float scale, int io_dtype, void* stream,
+                           int out_heads, int out_head0, const PeerLink* link) {
     if (!handle || !d_q || !d_out || (io_dtype != OJX_F32 && io_dtype != OJX_BF16)) return OJX_ERR_ARG;
     auto* h = static_cast<KvqHandle*>(handle);
     if (!h->static_plan && h->host_len <= 0) return OJX_ERR_RANGE;
@@ -394,7 +448,9 @@ int ojasx_b200_kvq_decode(OjasxKvqHandle handle, const void* d_q, void* d_out, f
     int rc = ensure_capacity(&h->partials, &h->partials_cap, need);
     if (rc != OJX_OK) return rc;
     P.partials = static_cast<float*>(h->partials);
-    return launch_kvq_decode(P, static_cast<cudaStream_t>(stream));
+    P.out_heads = out_heads;
+    P.out_head0 = out_head0;
+    return launch_kvq_decode(P, static_cast<cudaStream_t>(stream), link);
 }
 
 int ojasx_b200_kvq_set_static_plan(OjasxKvqHandle handle, int enabled) {

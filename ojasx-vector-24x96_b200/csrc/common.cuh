@@ -49,6 +49,8 @@ struct LinearProblem {
     int tile_rows;            // rows per work item (multiple of 32, <= kAccRows)
     int tiles;                // ceil((row_stop-row_start)/tile_rows)
     int item_begin;           // first global work item of this problem (grouped launches)
+    int y_full;               // 0: y is [batch, row_stop - row_start]; 1: y is [batch, y_ld] and row m goes to column m
+    int y_ld;                 //    (the gathered layout of a row-split layer: every rank fills its own columns)
 };
 
 // Top-k MoE over VQ experts (layout of SplitManifoldMoE, ojasx_lut.h:156-242).  Device pointers.
@@ -83,6 +85,8 @@ struct MoeProblem {
     const int* plan;
     int mc_cmax, mc_nacc;
     int mc_debug;
+    int combine_all;          // 1: the combine adds every routed pair with a valid id (outputs of other ranks' experts were
+                              // gathered into expert_out); 0: only the pairs this handle evaluated
     float gate_limit;         // > 0: gate is clamped from above and up to [-limit, limit] before silu(gate) * up
                               // (ResidualVQFusedExperts._apply_gate, ojasx_24x96/module.py:646-651); <= 0: no clamp
     int lut_blocks;
@@ -108,6 +112,8 @@ struct KvqProblem {
     int v_copies;           // copies of the value codebook in the decode kernel's shared memory (1 or 8)
     int io_dtype;
     float scale;
+    int out_heads;          // query heads of a row of `out` (0: Hq); > Hq when this cache holds a KV-head shard and
+    int out_head0;          // writes its heads at [out_head0, out_head0 + Hq) of the gathered output
 };
 
 inline int round_up(int a, int b) { return (a + b - 1) / b * b; }

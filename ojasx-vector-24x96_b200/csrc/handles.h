@@ -71,6 +71,7 @@ struct LinearGroup {
     void* bound_y = nullptr;
     size_t bound_xs = 0, bound_ys = 0;
     int bound_dtype = -1;
+    int bound_full = 0;   // the table on the device was written for the gathered output layout
 };
 
 struct MoeHandle {

@@ -15,6 +15,7 @@
 
 #include "common.cuh"
 #include "launch.h"
+#include "peer.cuh"
 #include "handles.h"
 
 namespace ojx {
@@ -166,7 +167,7 @@ __device__ __forceinline__ void st_heads(float* p, const float (&o)[R]) {
 // The CTA that arrives last merges the partials of the R query heads: M = max m_c, weights
 // exp(m_c - M), splits in index order -- so a decode is one launch.  The counter returns to zero.
 template <int R>
-__device__ __forceinline__ void kvq_merge_if_last(const KvqProblem& P, int b, int h) {
+__device__ __forceinline__ void kvq_merge_if_last(const KvqProblem& P, int b, int h, const PeerLink& link) {
     __shared__ int s_last;
     __threadfence();   // this thread's partial is visible device-wide before the CTA is counted
     __syncthreads();
@@ -196,14 +197,17 @@ __device__ __forceinline__ void kvq_merge_if_last(const KvqProblem& P, int b, in
             }
         }
         o *= L > 0.0f ? 1.0f / L : 0.0f;
-        const size_t oi = ((size_t)b * P.Hq + (size_t)h * R + r) * hd + col;
-        if (P.io_dtype == OJX_BF16) reinterpret_cast<__nv_bfloat16*>(P.out)[oi] = __float2bfloat16_rn(o);
-        else reinterpret_cast<float*>(P.out)[oi] = o;
+        // a KV-head shard writes its heads into the gathered output of every rank (link.n > 0)
+        const int row_heads = P.out_heads > 0 ? P.out_heads : P.Hq;
+        const size_t oi = ((size_t)b * row_heads + P.out_head0 + (size_t)h * R + r) * hd + col;
+        if (P.io_dtype == OJX_BF16) peer_store(link, reinterpret_cast<__nv_bfloat16*>(P.out) + oi, __float2bfloat16_rn(o));
+        else peer_store(link, reinterpret_cast<float*>(P.out) + oi, o);
     }
 }
 
 template <int R, int D>
-__global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel(const __grid_constant__ KvqProblem P) {
+__global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel(const __grid_constant__ KvqProblem P,
+                                                                                 const __grid_constant__ PeerLink link) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int kThreads = kvq_decode_threads(R, D), kHalf = kThreads / 2;   // score threads = value threads
     constexpr int kTpt = 2, kSub = kTpt * kHalf;                               // tokens per pass
@@ -235,7 +239,8 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
     float* part = P.partials + ((((size_t)b * P.Hkv + h) * P.n_chunks + split) * R) * (hd + 2);
     if (t_begin >= t_end) {  // range beyond this sequence: neutral partial
         for (int i = tid; i < R * (hd + 2); i += kThreads) part[i] = (i % (hd + 2)) == 0 ? -INFINITY : 0.0f;
-        kvq_merge_if_last<R>(P, b, h);
+        kvq_merge_if_last<R>(P, b, h, link);
+        peer_signal_when_last(link, gridDim.x * gridDim.y * gridDim.z);
         return;
     }
     const int n_passes = (t_end - t_begin + kSub - 1) / kSub;
@@ -591,7 +596,8 @@ __global__ void __launch_bounds__(kvq_decode_threads(R, D), 1) kvq_decode_kernel
             part[(size_t)r * (hd + 2) + 1] = l;
         }
     }
-    kvq_merge_if_last<R>(P, b, h);
+    kvq_merge_if_last<R>(P, b, h, link);
+    peer_signal_when_last(link, gridDim.x * gridDim.y * gridDim.z);
 }
 
 static size_t kvq_decode_smem_copies(const KvqProblem& P, int R, int copies) {
@@ -649,7 +655,7 @@ int launch_kvq_append(const KvqProblem& P, cudaStream_t s) {
 }
 
 template <int R, int D>
-static int launch_decode_t(const KvqProblem& P, cudaStream_t s) {
+static int launch_decode_t(const KvqProblem& P, cudaStream_t s, const PeerLink& link) {
     const size_t smem = kvq_decode_smem(P, R);
     if (smem + 64 > 227 * 1024) return OJX_ERR_TOO_LARGE;   // 64: the kernel's few static bytes
     KvqProblem Q = P;
@@ -661,31 +667,33 @@ static int launch_decode_t(const KvqProblem& P, cudaStream_t s) {
         OJX_CUDA_TRY(cudaFuncSetAttribute(kvq_decode_kernel<R, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         if (cur_dev >= 0 && cur_dev < 64) configured[cur_dev] = smem;
     }
-    kvq_decode_kernel<R, D><<<dim3(P.n_chunks, P.Hkv, P.B), kvq_decode_threads(R, D), smem, s>>>(Q);
+    kvq_decode_kernel<R, D><<<dim3(P.n_chunks, P.Hkv, P.B), kvq_decode_threads(R, D), smem, s>>>(Q, link);
     OJX_CUDA_TRY(cudaGetLastError());
     count_launch(1);
     return OJX_OK;
 }
 
 template <int R>
-static int launch_decode_r(const KvqProblem& P, cudaStream_t s) {
+static int launch_decode_r(const KvqProblem& P, cudaStream_t s, const PeerLink& link) {
     switch (P.D) {
-        case 4: return launch_decode_t<R, 4>(P, s);
-        case 8: return launch_decode_t<R, 8>(P, s);
-        case 16: return launch_decode_t<R, 16>(P, s);
+        case 4: return launch_decode_t<R, 4>(P, s, link);
+        case 8: return launch_decode_t<R, 8>(P, s, link);
+        case 16: return launch_decode_t<R, 16>(P, s, link);
         default: return OJX_ERR_UNSUPPORTED;
     }
 }
 
-int launch_kvq_decode(const KvqProblem& P, cudaStream_t s) {
+int launch_kvq_decode(const KvqProblem& P, cudaStream_t s, const PeerLink* lk) {
+    const PeerLink none{};
+    const PeerLink& link = lk ? *lk : none;
     if (!P.q || !P.out || !P.partials || !P.seq_lens) return OJX_ERR_ARG;
     if (P.G > kKvMaxGroups || P.Hq % P.Hkv != 0) return OJX_ERR_UNSUPPORTED;
     if (P.head_dim > 2 * kKvThreads || P.head_dim % 4 != 0) return OJX_ERR_UNSUPPORTED;
     switch (P.Hq / P.Hkv) {
-        case 1: return launch_decode_r<1>(P, s);
-        case 2: return launch_decode_r<2>(P, s);
-        case 4: return launch_decode_r<4>(P, s);
-        case 8: return launch_decode_r<8>(P, s);
+        case 1: return launch_decode_r<1>(P, s, link);
+        case 2: return launch_decode_r<2>(P, s, link);
+        case 4: return launch_decode_r<4>(P, s, link);
+        case 8: return launch_decode_r<8>(P, s, link);
         default: return OJX_ERR_UNSUPPORTED;
     }
 }

@@ -4,16 +4,20 @@
 
 namespace ojx {
 
+struct PeerLink;   // peer.cuh: exchange over peer memory fused into a kernel's epilogue (null / n == 0: none)
+const PeerLink* peer_link_of(void* peer_link_handle);
+
 // --- linear.cu
 int plan_tile_rows(int rows, int parallel_items);
 int validate_linear(const LinearProblem& P);
-int launch_linear(LinearProblem P, cudaStream_t stream);
-int launch_linear_group(const LinearProblem* d_probs, int nprobs, int total_items, int D, cudaStream_t stream);
+int launch_linear(LinearProblem P, cudaStream_t stream, const PeerLink* link = nullptr);
+int launch_linear_group(const LinearProblem* d_probs, int nprobs, int total_items, int D, cudaStream_t stream,
+                        const PeerLink* link = nullptr);
 
 // --- linear_cluster.cu: OJX_ERR_UNSUPPORTED means "use the persistent kernel"
-int try_launch_linear_cluster(const LinearProblem& P, cudaStream_t stream);
+int try_launch_linear_cluster(const LinearProblem& P, cudaStream_t stream, const PeerLink* link = nullptr);
 // Up to 8 host-side problems with the same K, G, block_dim, batch and io dtype in one cluster launch.
-int try_launch_linear_cluster_group(const LinearProblem* probs, int count, cudaStream_t stream);
+int try_launch_linear_cluster_group(const LinearProblem* probs, int count, cudaStream_t stream, const PeerLink* link = nullptr);
 // True when OJASX_B200_LINEAR_KERNEL=persistent asks for the streaming kernel only.
 bool linear_cluster_disabled();
 
@@ -30,7 +34,8 @@ int launch_dequant_gemm(const LinearProblem& P, cudaStream_t stream, void** scra
 int take_dequant_gemm_error(int* out);
 
 // --- moe.cu
-int launch_moe_experts(MoeProblem P, cudaStream_t stream);
+// link: expert-parallel ranks gather every pair's expert output over peer memory before the combine (null: one rank)
+int launch_moe_experts(MoeProblem P, cudaStream_t stream, const PeerLink* link = nullptr);
 int launch_build_lut(const void* x, int io_dtype, int n_vectors, int K, int D, const float* codebook, int Kcb, float* out,
                      cudaStream_t stream);
 int launch_silu_mul(const void* gate, const void* up, void* out, size_t n, int io_dtype, cudaStream_t stream);
@@ -43,7 +48,7 @@ int launch_moe_router(const float* Wr, const void* x, int io_dtype, int n_tokens
 
 // --- moe_fused.cu: whole-expert work items (gate/up, SiLU gate and down fused) for batches of tokens
 bool moe_fused_wanted(const MoeProblem& P);   // shape fits and enough routed pairs are expected here
-int launch_moe_fused(MoeProblem P, cudaStream_t stream);   // work list, token tables (unless lut_ready), experts
+int launch_moe_fused(MoeProblem P, cudaStream_t stream, const PeerLink* link = nullptr);   // work list, token tables (unless lut_ready), experts
 int launch_moe_prebuild_blocks(const void* x, int io_dtype, int n_tokens, int H, int D, const float* codebook, int Kcb,
                                float* out, cudaStream_t stream);
 int take_moe_fused_error(int* out);
@@ -55,7 +60,7 @@ size_t kvq_decode_smem(const KvqProblem& P, int R);
 // Fills P.chunk (tokens per CTA) and P.n_chunks (<= kKvMaxSplits) for a context of T tokens.
 void plan_kvq_decode(KvqProblem& P, int T, int sms);
 int launch_kvq_append(const KvqProblem& P, cudaStream_t stream);
-int launch_kvq_decode(const KvqProblem& P, cudaStream_t stream);
+int launch_kvq_decode(const KvqProblem& P, cudaStream_t stream, const PeerLink* link = nullptr);
 int launch_legacy_append(const float* k, const float* v, int head_dim, int block_dim, uint8_t* k_row, uint8_t* v_row,
                          float* k_scale, float* v_scale, cudaStream_t stream);
 int launch_legacy_attention(const float* q, int head_dim, int block_dim, int T, const uint8_t* k_codes,

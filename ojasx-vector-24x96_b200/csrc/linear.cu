@@ -8,6 +8,7 @@
 #include "lut_chain.cuh"
 #include "launch.h"
 #include "handles.h"
+#include "peer.cuh"
 
 #include <cstdlib>
 
@@ -27,7 +28,7 @@ constexpr int kChainMinRows = 32 * kWarps;
 template <int D>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 lut_linear_kernel(const LinearProblem* __restrict__ probs, int nprobs, int total_items,
-                  const __grid_constant__ LinearProblem single, int chain_walk) {
+                  const __grid_constant__ LinearProblem single, int chain_walk, const __grid_constant__ PeerLink link) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     CoreSmem& sm = *reinterpret_cast<CoreSmem*>(smem_raw);
 
@@ -82,10 +83,12 @@ lut_linear_kernel(const LinearProblem* __restrict__ probs, int nprobs, int total
         __syncthreads();
 
         // Epilogue (ojasx_lut_cpu.cpp:178-182 then :117-127): scale, bias, outlier row, one store.
+        // With a link the result also goes to the same place in every other rank's copy of the output buffer
+        // (the all-gather of a row-split layer, fused into the epilogue).
         auto store_y = [&](int m, float res) {
-            const size_t o = (size_t)b * rows_out + (m - P.row_start);
-            if (P.io_dtype == OJX_BF16) reinterpret_cast<__nv_bfloat16*>(P.y)[o] = __float2bfloat16_rn(res);
-            else reinterpret_cast<float*>(P.y)[o] = res;
+            const size_t o = P.y_full ? (size_t)b * P.y_ld + m : (size_t)b * rows_out + (m - P.row_start);
+            if (P.io_dtype == OJX_BF16) peer_store(link, reinterpret_cast<__nv_bfloat16*>(P.y) + o, __float2bfloat16_rn(res));
+            else peer_store(link, reinterpret_cast<float*>(P.y) + o, res);
         };
         if constexpr (D <= 16) {
             if (chain) {
@@ -109,15 +112,14 @@ lut_linear_kernel(const LinearProblem* __restrict__ probs, int nprobs, int total
             if (P.scales) res = __fmul_rn(res, P.scales[m]);
             if (P.bias) res = __fadd_rn(res, P.bias[m]);
             if (P.csr.nnz > 0) res = __fadd_rn(res, area[lr]);
-            const size_t o = (size_t)b * rows_out + (m - P.row_start);
-            if (P.io_dtype == OJX_BF16) reinterpret_cast<__nv_bfloat16*>(P.y)[o] = __float2bfloat16_rn(res);
-            else reinterpret_cast<float*>(P.y)[o] = res;
+            store_y(m, res);
         }
         __syncthreads();
     }
+    peer_signal_when_last(link, gridDim.x);
 }
 
-using LinearKernel = void (*)(const LinearProblem*, int, int, const LinearProblem, int);
+using LinearKernel = void (*)(const LinearProblem*, int, int, const LinearProblem, int, const PeerLink);
 
 static LinearKernel pick_linear_kernel(int D) {
     switch (D) {
@@ -178,13 +180,15 @@ int validate_linear(const LinearProblem& P) {
     return OJX_OK;
 }
 
-int launch_linear(LinearProblem P, cudaStream_t stream) {
+int launch_linear(LinearProblem P, cudaStream_t stream, const PeerLink* link) {
     int rc = validate_linear(P);
     if (rc != OJX_OK) return rc;
+    const PeerLink none{};
+    const PeerLink& L = link ? *link : none;
     const int rows = P.row_stop - P.row_start;
     if (P.tile_rows <= 0 && !force_persistent()) {
         // Small single problems: the cluster kernel spreads the table build over the GPU.
-        rc = try_launch_linear_cluster(P, stream);
+        rc = try_launch_linear_cluster(P, stream, link);
         if (rc != OJX_ERR_UNSUPPORTED) return rc;
     }
     if (P.tile_rows <= 0) P.tile_rows = plan_tile_rows(rows, P.batch);
@@ -196,13 +200,14 @@ int launch_linear(LinearProblem P, cudaStream_t stream) {
     if (rc != OJX_OK) return rc;
     const int cap = kCtasPerSm * num_sms();
     const int grid = total < cap ? total : cap;
-    k<<<grid, kThreads, sizeof(CoreSmem), stream>>>(nullptr, 0, total, P, chain_walk_enabled());
+    k<<<grid, kThreads, sizeof(CoreSmem), stream>>>(nullptr, 0, total, P, chain_walk_enabled(), L);
     count_launch(1);
     OJX_CUDA_TRY(cudaGetLastError());
     return OJX_OK;
 }
 
-int launch_linear_group(const LinearProblem* d_probs, int nprobs, int total_items, int D, cudaStream_t stream) {
+int launch_linear_group(const LinearProblem* d_probs, int nprobs, int total_items, int D, cudaStream_t stream,
+                        const PeerLink* link) {
     if (!d_probs || nprobs <= 0 || total_items <= 0) return OJX_ERR_ARG;
     LinearKernel k = pick_linear_kernel(D);
     if (!k) return OJX_ERR_UNSUPPORTED;
@@ -211,7 +216,8 @@ int launch_linear_group(const LinearProblem* d_probs, int nprobs, int total_item
     const int cap = kCtasPerSm * num_sms();
     const int grid = total_items < cap ? total_items : cap;
     LinearProblem dummy{};
-    k<<<grid, kThreads, sizeof(CoreSmem), stream>>>(d_probs, nprobs, total_items, dummy, chain_walk_enabled());
+    const PeerLink none{};
+    k<<<grid, kThreads, sizeof(CoreSmem), stream>>>(d_probs, nprobs, total_items, dummy, chain_walk_enabled(), link ? *link : none);
     count_launch(1);
     OJX_CUDA_TRY(cudaGetLastError());
     return OJX_OK;

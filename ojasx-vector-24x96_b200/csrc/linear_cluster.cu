@@ -13,6 +13,7 @@
 #include "lut_core.cuh"
 #include "launch.h"
 #include "handles.h"
+#include "peer.cuh"
 
 namespace ojx {
 
@@ -61,7 +62,8 @@ __device__ __forceinline__ void cluster_sync_all() {
 
 template <int D>
 __global__ void __launch_bounds__(kClThreads, 1)
-lut_linear_cluster_kernel(const __grid_constant__ ClusterGroup grp, const __grid_constant__ ClusterPlan plan) {
+lut_linear_cluster_kernel(const __grid_constant__ ClusterGroup grp, const __grid_constant__ ClusterPlan plan,
+                          const __grid_constant__ PeerLink link) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int C = plan.C;
     const int cid_all = blockIdx.x / C;
@@ -214,18 +216,20 @@ lut_linear_cluster_kernel(const __grid_constant__ ClusterGroup grp, const __grid
         }
         if (P.csr.nnz > 0 && tid < mine) res = __fadd_rn(res, oacc_s[tid]);
         if (tid < mine) {
-            const size_t o = (size_t)b * rows_out + (size_t)(r0 + first + tid - P.row_start);
-            if (P.io_dtype == OJX_BF16) reinterpret_cast<__nv_bfloat16*>(P.y)[o] = __float2bfloat16_rn(res);
-            else reinterpret_cast<float*>(P.y)[o] = res;
+            const int m = r0 + first + tid;
+            const size_t o = P.y_full ? (size_t)b * P.y_ld + m : (size_t)b * rows_out + (size_t)(m - P.row_start);
+            if (P.io_dtype == OJX_BF16) peer_store(link, reinterpret_cast<__nv_bfloat16*>(P.y) + o, __float2bfloat16_rn(res));
+            else peer_store(link, reinterpret_cast<float*>(P.y) + o, res);
         }
         __syncthreads();     // oacc_s of this tile has been consumed
         if (tile + n_clusters < n_tiles) outlier_sums(tile + n_clusters);
         cluster_sync_all();  // recv may be overwritten by the next tile; nobody exits while peers may still write
     }
+    peer_signal_when_last(link, gridDim.x * gridDim.y);
 }
 
 template <int D>
-static int launch_cluster_t(const ClusterGroup& grp, ClusterPlan plan, cudaStream_t stream, bool dry_run) {
+static int launch_cluster_t(const ClusterGroup& grp, ClusterPlan plan, cudaStream_t stream, bool dry_run, const PeerLink& link) {
     auto kern = lut_linear_cluster_kernel<D>;
     // query_max_clusters<D> already opted this kernel in to kClSmemCap bytes of dynamic shared memory on
     // this device (plans never exceed it), so nothing has to be set per launch.
@@ -242,7 +246,7 @@ static int launch_cluster_t(const ClusterGroup& grp, ClusterPlan plan, cudaStrea
     cfg.numAttrs = 1;
     cfg.gridDim = dim3(plan.C * plan.n_clusters, grp.P[0].batch);
     if (dry_run) return OJX_OK;
-    OJX_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, grp, plan));
+    OJX_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, grp, plan, link));
     count_launch(1);
     return OJX_OK;
 }
@@ -373,32 +377,34 @@ static bool plan_cluster_group(const LinearProblem* Ps, int count, ClusterPlan* 
     return found;
 }
 
-static int launch_cluster_group(const ClusterGroup& grp, const ClusterPlan& plan, cudaStream_t stream) {
+static int launch_cluster_group(const ClusterGroup& grp, const ClusterPlan& plan, cudaStream_t stream, const PeerLink* lk) {
+    const PeerLink none{};
+    const PeerLink& link = lk ? *lk : none;
     switch (grp.P[0].D) {
-        case 4: return launch_cluster_t<4>(grp, plan, stream, false);
-        case 8: return launch_cluster_t<8>(grp, plan, stream, false);
-        case 16: return launch_cluster_t<16>(grp, plan, stream, false);
-        case 32: return launch_cluster_t<32>(grp, plan, stream, false);
+        case 4: return launch_cluster_t<4>(grp, plan, stream, false, link);
+        case 8: return launch_cluster_t<8>(grp, plan, stream, false, link);
+        case 16: return launch_cluster_t<16>(grp, plan, stream, false, link);
+        case 32: return launch_cluster_t<32>(grp, plan, stream, false, link);
         default: return OJX_ERR_UNSUPPORTED;
     }
 }
 
 // Entry used by launch_linear(): returns OJX_ERR_UNSUPPORTED when the caller should fall back
 // to the persistent kernel.
-int try_launch_linear_cluster(const LinearProblem& P, cudaStream_t stream) {
+int try_launch_linear_cluster(const LinearProblem& P, cudaStream_t stream, const PeerLink* link) {
     ClusterPlan plan;
     ClusterGroup grp;
     if (!plan_cluster_group(&P, 1, &plan, &grp)) return OJX_ERR_UNSUPPORTED;
-    return launch_cluster_group(grp, plan, stream);
+    return launch_cluster_group(grp, plan, stream, link);
 }
 
 // Same for a few problems at once (host copies of the problems; nothing is read from them after
 // the call returns).  OJX_ERR_UNSUPPORTED: use the persistent grouped kernel.
-int try_launch_linear_cluster_group(const LinearProblem* probs, int count, cudaStream_t stream) {
+int try_launch_linear_cluster_group(const LinearProblem* probs, int count, cudaStream_t stream, const PeerLink* link) {
     ClusterPlan plan;
     ClusterGroup grp;
     if (!plan_cluster_group(probs, count, &plan, &grp)) return OJX_ERR_UNSUPPORTED;
-    return launch_cluster_group(grp, plan, stream);
+    return launch_cluster_group(grp, plan, stream, link);
 }
 
 }  // namespace ojx

@@ -14,6 +14,7 @@
 #include "lut_core.cuh"
 #include "launch.h"
 #include "handles.h"
+#include "peer.cuh"
 #include "../../include/ojasx_lut_b200.h"
 
 #include <mutex>
@@ -95,7 +96,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) moe_gate_up_kernel(const
 }
 
 template <int D>
-__global__ void __launch_bounds__(kThreads, kCtasPerSm) moe_down_kernel(const __grid_constant__ MoeProblem P) {
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) moe_down_kernel(const __grid_constant__ MoeProblem P,
+                                                                        const __grid_constant__ PeerLink link) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     CoreSmem& sm = *reinterpret_cast<CoreSmem*>(smem_raw);
     const int total = (P.pair_list ? P.pair_list[0] : P.n_tokens * P.k_active) * P.dn_tiles;
@@ -125,10 +127,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) moe_down_kernel(const __
             float v = sm.acc[lr];
             if (P.dn_scales) v = __fmul_rn(v, P.dn_scales[r]);
             if (P.dn_csr.nnz > 0) v = __fadd_rn(v, sm.lut[lr]);
-            P.expert_out[(size_t)pair * P.H + h0 + lr] = v;
+            peer_store(link, P.expert_out + (size_t)pair * P.H + h0 + lr, v);   // expert-parallel: every rank gets the pair's output
         }
         __syncthreads();
     }
+    peer_signal_when_last(link, gridDim.x);
 }
 
 // Work list of one forward: the (token, expert) pairs this handle evaluates -- expert held here,
@@ -187,7 +190,17 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const __grid_constant__ 
 }
 
 // y[t,h] = sum_k expert_out[t*k+k', h] * w  in caller order (ojasx_lut_cpu.cpp:361-362).
-__global__ void moe_combine_kernel(const __grid_constant__ MoeProblem P) {
+__device__ __forceinline__ bool combine_takes(const MoeProblem& P, int pair) {
+    if (!P.combine_all) return decode_pair(P, pair).expert >= 0;
+    const int e = P.topk_idx[pair];
+    return e >= 0 && e < P.E_total && fabsf(P.topk_w[pair]) >= 1e-8f;
+}
+
+__global__ void moe_combine_kernel(const __grid_constant__ MoeProblem P, const __grid_constant__ PeerLink link) {
+    if (link.n > 0) {   // expert outputs of the other ranks land in expert_out: wait for every rank's flag first
+        if (threadIdx.x < 32) peer_wait_warp(link);
+        __syncthreads();
+    }
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= P.n_tokens * P.H) return;
     const int t = idx / P.H, h = idx - t * P.H;
@@ -198,7 +211,7 @@ __global__ void moe_combine_kernel(const __grid_constant__ MoeProblem P) {
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             const int k = k0 + u, pair = t * P.k_active + k;
-            ok[u] = k < P.k_active && decode_pair(P, pair).expert >= 0;
+            ok[u] = k < P.k_active && combine_takes(P, pair);
             v[u] = ok[u] ? P.expert_out[(size_t)pair * P.H + h] : 0.0f;
             w[u] = ok[u] ? P.topk_w[pair] : 0.0f;
         }
@@ -444,7 +457,7 @@ static int set_smem(K kern) {
 constexpr int kMoePlanMinPairs = 64;
 
 template <int D>
-static int launch_moe_experts_t(const MoeProblem& P, cudaStream_t s) {
+static int launch_moe_experts_t(const MoeProblem& P, cudaStream_t s, const PeerLink& link) {
     int rc;
     if ((rc = set_smem(moe_gate_up_kernel<D>)) != OJX_OK) return rc;
     if ((rc = set_smem(moe_down_kernel<D>)) != OJX_OK) return rc;
@@ -466,26 +479,29 @@ static int launch_moe_experts_t(const MoeProblem& P, cudaStream_t s) {
     }
     moe_gate_up_kernel<D><<<gu_items < sms ? gu_items : sms, kThreads, sizeof(CoreSmem), s>>>(P);
     OJX_CUDA_TRY(cudaGetLastError());
-    moe_down_kernel<D><<<dn_items < sms ? dn_items : sms, kThreads, sizeof(CoreSmem), s>>>(P);
+    moe_down_kernel<D><<<dn_items < sms ? dn_items : sms, kThreads, sizeof(CoreSmem), s>>>(P, link);
     OJX_CUDA_TRY(cudaGetLastError());
     const int n = P.n_tokens * P.H;
-    moe_combine_kernel<<<(n + 255) / 256, 256, 0, s>>>(P);
+    moe_combine_kernel<<<(n + 255) / 256, 256, 0, s>>>(P, link);
     OJX_CUDA_TRY(cudaGetLastError());
     count_launch(3 + extra);
     return OJX_OK;
 }
 
-int launch_moe_experts(MoeProblem P, cudaStream_t s) {
+int launch_moe_experts(MoeProblem P, cudaStream_t s, const PeerLink* lk) {
     if (!P.x || !P.y || !P.topk_idx || !P.topk_w || !P.inter || !P.expert_out) return OJX_ERR_ARG;
     if (P.n_tokens <= 0 || P.k_active <= 0) return OJX_ERR_ARG;
+    const PeerLink none{};
+    const PeerLink& link = lk ? *lk : none;
+    P.combine_all = link.n > 0 ? 1 : 0;
     // Batches: whole-expert work items, gate/up and down fused (moe_fused.cu); then the ordered combine.
     if (moe_fused_wanted(P)) {
         if (P.lut_ready && !P.lut_blocks) P.lut_ready = 0;   // tables were built in the other layout: rebuild
-        const int rc = launch_moe_fused(P, s);
+        const int rc = launch_moe_fused(P, s, lk);
         if (rc != OJX_ERR_UNSUPPORTED) {
             if (rc != OJX_OK) return rc;
             const int n = P.n_tokens * P.H;
-            moe_combine_kernel<<<(n + 255) / 256, 256, 0, s>>>(P);
+            moe_combine_kernel<<<(n + 255) / 256, 256, 0, s>>>(P, link);
             OJX_CUDA_TRY(cudaGetLastError());
             count_launch(1);
             return OJX_OK;
@@ -507,10 +523,10 @@ int launch_moe_experts(MoeProblem P, cudaStream_t s) {
     if (P.dn_tile > kAccRows) P.dn_tile = kAccRows;
     P.dn_tiles = (P.H + P.dn_tile - 1) / P.dn_tile;
     switch (P.D) {
-        case 4: return launch_moe_experts_t<4>(P, s);
-        case 8: return launch_moe_experts_t<8>(P, s);
-        case 16: return launch_moe_experts_t<16>(P, s);
-        case 32: return launch_moe_experts_t<32>(P, s);
+        case 4: return launch_moe_experts_t<4>(P, s, link);
+        case 8: return launch_moe_experts_t<8>(P, s, link);
+        case 16: return launch_moe_experts_t<16>(P, s, link);
+        case 32: return launch_moe_experts_t<32>(P, s, link);
         default: return OJX_ERR_UNSUPPORTED;
     }
 }

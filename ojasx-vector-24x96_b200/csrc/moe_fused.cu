@@ -24,6 +24,7 @@
 #include "lut_chain.cuh"
 #include "launch.h"
 #include "handles.h"
+#include "peer.cuh"
 
 #include <cstdlib>
 
@@ -460,7 +461,8 @@ __device__ __forceinline__ int mc_pick_lc(int C, int remaining_groups) {
     } while (0)
 
 template <int D>
-__global__ void __launch_bounds__(kThreads, 1) moe_fused_kernel(const __grid_constant__ MoeProblem P) {
+__global__ void __launch_bounds__(kThreads, 1) moe_fused_kernel(const __grid_constant__ MoeProblem P,
+                                                                  const __grid_constant__ PeerLink link) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     if (static_cast<uint32_t>(__cvta_generic_to_shared(smem_raw)) != 1024u) {
         if (threadIdx.x == 0) atomicExch(&g_moe_fused_error, 1);
@@ -634,7 +636,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fused_kernel(const __grid_con
                 float* out[4];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) out[c] = P.expert_out + (size_t)pair_of(c) * H;
-                auto put = [&](int c, int row, float v) { out[c][row] = v; };
+                auto put = [&](int c, int row, float v) { peer_store(link, out[c] + row, v); };
                 if (C == 4) mc_epilogue<4>(X, P.dn_csr, dn_row0, P.dn_scales, inter, I, rpw, prod2, nprod2, put);
                 else if (C == 2) mc_epilogue<2>(X, P.dn_csr, dn_row0, P.dn_scales, inter, I, rpw, prod2, nprod2, put);
                 else mc_epilogue<1>(X, P.dn_csr, dn_row0, P.dn_scales, inter, I, rpw, prod2, nprod2, put);
@@ -643,6 +645,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fused_kernel(const __grid_con
         // the barrier at the top of the loop (and the one before the next table copy) separates this
         // epilogue from the next work item
     }
+    peer_signal_when_last(link, gridDim.x);
 }
 
 // Work list of the fused kernel: the (token, expert) pairs this handle evaluates, sorted by expert, cut
@@ -814,7 +817,7 @@ bool moe_fused_wanted(const MoeProblem& P) {
 }
 
 template <int D>
-static int launch_moe_fused_t(MoeProblem P, cudaStream_t s) {
+static int launch_moe_fused_t(MoeProblem P, cudaStream_t s, const PeerLink& link) {
     static thread_local bool opted[64] = {};
     int dev = 0;
     OJX_CUDA_TRY(cudaGetDevice(&dev));
@@ -838,7 +841,7 @@ static int launch_moe_fused_t(MoeProblem P, cudaStream_t s) {
     const long long pairs = (long long)P.n_tokens * P.k_active;
     const int sms = num_sms();
     const int grid = (int)(pairs < sms ? pairs : sms);
-    moe_fused_kernel<D><<<grid, kThreads, kMcSmemBytes, s>>>(P);
+    moe_fused_kernel<D><<<grid, kThreads, kMcSmemBytes, s>>>(P, link);
     OJX_CUDA_TRY(cudaGetLastError());
     ++launches;
     count_launch(launches);
@@ -847,16 +850,18 @@ static int launch_moe_fused_t(MoeProblem P, cudaStream_t s) {
 
 // Plan + (tables) + fused experts; the caller adds the combine pass.  P.lut_in must be in block layout
 // when P.lut_ready is set.
-int launch_moe_fused(MoeProblem P, cudaStream_t s) {
+int launch_moe_fused(MoeProblem P, cudaStream_t s, const PeerLink* lk) {
+    const PeerLink none{};
+    const PeerLink& link = lk ? *lk : none;
     P.mc_cmax = moe_fused_cmax(P);
     if (P.mc_cmax <= 0) return OJX_ERR_UNSUPPORTED;
     { const char* e = getenv("OJX_MC_DEBUG"); P.mc_debug = e ? atoi(e) : 0; const char* c = getenv("OJX_MC_CMAX"); if (c && atoi(c) < P.mc_cmax) P.mc_cmax = atoi(c); }
     const int rows = P.H > 2 * P.I ? P.H : 2 * P.I;
     P.mc_nacc = mc_nacc_for(rows);
     switch (P.D) {
-        case 4: return launch_moe_fused_t<4>(P, s);
-        case 8: return launch_moe_fused_t<8>(P, s);
-        case 16: return launch_moe_fused_t<16>(P, s);
+        case 4: return launch_moe_fused_t<4>(P, s, link);
+        case 8: return launch_moe_fused_t<8>(P, s, link);
+        case 16: return launch_moe_fused_t<16>(P, s, link);
         default: return OJX_ERR_UNSUPPORTED;
     }
 }

@@ -314,6 +314,10 @@ class VQKVCache:
         if not self._h:
             check(-3, "ojasx_b200_kvq_create")
 
+    @property
+    def handle(self):
+        return self._h
+
     def load(self, k_codes, v_codes):
         kc = np.ascontiguousarray(k_codes, dtype=np.uint8)
         vc = np.ascontiguousarray(v_codes, dtype=np.uint8)

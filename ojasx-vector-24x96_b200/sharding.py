@@ -11,11 +11,19 @@ The three pieces shard independently and each needs at most one exchange:
 
 The partition arithmetic is plain Python so that it can be tested on CPU ranks (gloo); the
 compute classes hold one shard each.
+
+Two ways to exchange.  With ``segment=None`` the classes call ``torch.distributed`` collectives after the
+kernel.  With a ``PeerSegment`` (GPU ranks of one box) the exchange is fused into the kernel that produces the
+shard: its epilogue stores the shard at the same offset in every rank's segment over NVLink and raises a flag,
+and the consumer waits for all flags -- no collective launch between producer and consumer.
 """
 from __future__ import annotations
 
 from typing import List, Tuple
 
+import ctypes as C
+
+import numpy as np
 import torch
 import torch.distributed as dist
 
@@ -47,15 +55,113 @@ def gather_rows(y_local: torch.Tensor, total_rows: int, group=None) -> torch.Ten
     return torch.cat([p[:, : hi - lo] for p, (lo, hi) in zip(parts, ranges)], dim=1)
 
 
+class _DeviceView:
+    """Minimal ``__cuda_array_interface__`` carrier: lets torch wrap device memory this package allocated."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False), "version": 2}
+
+
+_TYPESTR = {torch.float32: "<f4", torch.int32: "<i4", torch.uint8: "|u1", torch.float16: "<f2"}
+
+
+class PeerSegment:
+    """This rank's shared segment, the other ranks' mappings of theirs, and the link the kernels use.
+
+    Every rank must create its segment with the same size and carve the same buffers from it in the same order
+    (``alloc``): a buffer then has the same offset everywhere, which is what the kernels rely on.  The first 256
+    bytes hold the link's flags.  bf16 buffers are carved as int16-sized views and reinterpreted."""
+
+    def __init__(self, nbytes: int, group=None):
+        from ._lib import check, lib
+        self._lib, self._check = lib(), check
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.nbytes = int(nbytes) + 256
+        self.base = self._lib.ojasx_b200_peer_alloc(self.nbytes)
+        if not self.base:
+            check(-3, "ojasx_b200_peer_alloc")
+        handle = (C.c_ubyte * 64)()
+        check(self._lib.ojasx_b200_peer_export(self.base, C.cast(handle, C.c_void_p)), "ojasx_b200_peer_export")
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle), group=group)
+        self.mapped = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.mapped.append(self.base)
+                continue
+            buf = (C.c_ubyte * 64).from_buffer_copy(h)
+            ptr = self._lib.ojasx_b200_peer_open(C.cast(buf, C.c_void_p))
+            if not ptr:
+                check(-3, f"ojasx_b200_peer_open (rank {r})")
+            self.mapped.append(ptr)
+        arr = (C.c_void_p * self.world)(*self.mapped)
+        self.link = self._lib.ojasx_b200_peer_link_create(arr, self.world, self.rank, 0)
+        if not self.link:
+            check(-3, "ojasx_b200_peer_link_create")
+        self._cursor = 256
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        dist.barrier(group=group)      # nobody stores into a segment that is not mapped everywhere yet
+
+    def alloc(self, shape, dtype=torch.float32) -> torch.Tensor:
+        esz = torch.empty((), dtype=dtype).element_size()
+        n = int(np.prod(shape)) * esz
+        off = (self._cursor + 255) // 256 * 256
+        if off + n > self.nbytes:
+            raise MemoryError(f"shared segment of {self.nbytes} bytes is full")
+        self._cursor = off + n
+        if dtype == torch.bfloat16:
+            t = torch.as_tensor(_DeviceView(self.base + off, shape, "<i2"), device=self.device).view(torch.bfloat16)
+        else:
+            t = torch.as_tensor(_DeviceView(self.base + off, shape, _TYPESTR[dtype]), device=self.device)
+        return t
+
+    def signal(self) -> None:
+        self._check(self._lib.ojasx_b200_peer_signal(self.link, torch.cuda.current_stream().cuda_stream), "ojasx_b200_peer_signal")
+
+    def wait(self) -> None:
+        self._check(self._lib.ojasx_b200_peer_wait(self.link, torch.cuda.current_stream().cuda_stream), "ojasx_b200_peer_wait")
+
+    def take_status(self) -> int:
+        return int(self._lib.ojasx_b200_peer_take_status(self.link))
+
+    def close(self) -> None:
+        if getattr(self, "link", None):
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)     # no rank unmaps while another may still store
+            self._lib.ojasx_b200_peer_link_destroy(self.link)
+            for r, p in enumerate(self.mapped):
+                if r != self.rank:
+                    self._lib.ojasx_b200_peer_close(p)
+            dist.barrier(group=self.group)
+            self._lib.ojasx_b200_peer_free(self.base)
+            self.link = None
+
+
 class ShardedVQLinear:
     """Row-split linear: this rank evaluates rows ``split_range(M, world, rank, 32)`` of a full ``ops.VQLinear``."""
 
-    def __init__(self, layer, group=None):
-        self.layer, self.group = layer, group
+    def __init__(self, layer, group=None, segment: "PeerSegment" = None, max_batch: int = 1, dtype=torch.float32):
+        self.layer, self.group, self.segment = layer, group, segment
         self.row_start, self.row_stop = split_range(layer.out_features, dist.get_world_size(group), dist.get_rank(group), 32)
+        self._turn = 0
+        if segment is not None:     # two gathered outputs, used in turn (see PeerSegment)
+            self._y = [segment.alloc((max_batch, layer.out_features), dtype) for _ in range(2)]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         x2 = x.reshape(-1, x.shape[-1])
+        if self.segment is not None:
+            from ._lib import check, lib
+            from .ops import _dtype_code, _stream_ptr
+            x2 = x2.contiguous()
+            y = self._y[self._turn][: x2.shape[0]]
+            self._turn ^= 1
+            assert y.dtype == x2.dtype and x2.shape[0] <= self._y[0].shape[0]
+            check(lib().ojasx_b200_linear_forward_gather(self.layer.handle, x2.data_ptr(), y.data_ptr(), x2.shape[0],
+                                                         _dtype_code(x2), self.row_start, self.row_stop, self.segment.link,
+                                                         _stream_ptr(x.device)), "ojasx_b200_linear_forward_gather")
+            self.segment.wait()
+            return y.reshape(*x.shape[:-1], self.layer.out_features)
         if self.row_stop > self.row_start:
             y = self.layer.forward(x2, self.row_start, self.row_stop)
         else:
@@ -66,10 +172,33 @@ class ShardedVQLinear:
 class ExpertParallelMoE:
     """Expert-parallel MoE: ``moe`` is an ``ops.VQMoE`` built with ``expert_range=split_range(E, world, rank)``."""
 
-    def __init__(self, moe, group=None):
-        self.moe, self.group = moe, group
+    def __init__(self, moe, group=None, segment: "PeerSegment" = None, max_tokens: int = 1, top_k: int = 10):
+        self.moe, self.group, self.segment = moe, group, segment
+        self._turn = 0
+        if segment is not None:     # per-pair expert outputs of every rank, two buffers used in turn
+            self._eo = [segment.alloc((max_tokens * top_k, moe.hidden), torch.float32) for _ in range(2)]
+            self.moe.reserve(max_tokens, top_k)
+
+    def _gathered(self, x, call, *args):
+        from ._lib import check
+        from .ops import _dtype_code, _stream_ptr
+        x2 = x.reshape(-1, self.moe.hidden).contiguous()
+        y = torch.empty_like(x2)
+        eo = self._eo[self._turn]
+        self._turn ^= 1
+        check(call(x2, y, eo, _dtype_code(x2), _stream_ptr(x.device), *args), "expert-parallel MoE forward")
+        return y.reshape(x.shape)
 
     def forward(self, x: torch.Tensor, top_k_index: torch.Tensor, top_k_weights: torch.Tensor) -> torch.Tensor:
+        if self.segment is not None:
+            from ._lib import lib
+            n = x.reshape(-1, self.moe.hidden).shape[0]
+            idx = top_k_index.reshape(n, -1).to(torch.int32).contiguous()
+            wts = top_k_weights.reshape(n, -1).to(torch.float32).contiguous()
+            assert idx.shape[0] * idx.shape[1] <= self._eo[0].shape[0]
+            return self._gathered(x, lambda x2, y, eo, dt, st: lib().ojasx_b200_moe_forward_gather(
+                self.moe.handle, x2.data_ptr(), idx.data_ptr(), wts.data_ptr(), y.data_ptr(), n, idx.shape[1], dt,
+                self.segment.link, eo.data_ptr(), st))
         y = self.moe.forward(x, top_k_index, top_k_weights)
         if y.dtype == torch.float32:
             dist.all_reduce(y, group=self.group)
@@ -79,6 +208,12 @@ class ExpertParallelMoE:
         return y32.to(y.dtype)
 
     def forward_routed(self, x: torch.Tensor, top_k: int = 10) -> torch.Tensor:
+        if self.segment is not None:
+            from ._lib import lib
+            n = x.reshape(-1, self.moe.hidden).shape[0]
+            assert n * top_k <= self._eo[0].shape[0]
+            return self._gathered(x, lambda x2, y, eo, dt, st: lib().ojasx_b200_moe_forward_routed_gather(
+                self.moe.handle, x2.data_ptr(), y.data_ptr(), n, top_k, dt, self.segment.link, eo.data_ptr(), st))
         idx, wts = self.moe.route(x, top_k)   # router weights are replicated: same routing on every rank
         return self.forward(x, idx, wts)
 
@@ -86,15 +221,31 @@ class ExpertParallelMoE:
 class HeadShardedKVCache:
     """KV-head split: ``cache`` is an ``ops.VQKVCache`` holding KV heads ``split_range(Hkv, world, rank)`` only."""
 
-    def __init__(self, cache, total_q_heads: int, group=None, total_kv_heads: int = 0):
-        self.cache, self.total_q_heads, self.group = cache, total_q_heads, group
+    def __init__(self, cache, total_q_heads: int, group=None, total_kv_heads: int = 0, segment: "PeerSegment" = None,
+                 dtype=torch.float32):
+        self.cache, self.total_q_heads, self.group, self.segment = cache, total_q_heads, group, segment
         world = dist.get_world_size(group)
+        self._turn = 0
+        if segment is not None:
+            self._o = [segment.alloc((cache.batch, total_q_heads, cache.head_dim), dtype) for _ in range(2)]
         # query heads held by every rank (ragged when the KV heads do not divide evenly)
         kv = total_kv_heads or world * cache.kv_heads
         per_kv = total_q_heads // kv
         self.q_ranges = [(a * per_kv, b * per_kv) for a, b in all_ranges(kv, world)]
 
     def decode(self, q_local: torch.Tensor, scale: float = -1.0) -> torch.Tensor:
+        if self.segment is not None:
+            from ._lib import check, lib
+            from .ops import _dtype_code, _stream_ptr
+            q2 = q_local.contiguous()
+            o = self._o[self._turn]
+            self._turn ^= 1
+            first = self.q_ranges[dist.get_rank(self.group)][0]
+            check(lib().ojasx_b200_kvq_decode_gather(self.cache.handle, q2.data_ptr(), o.data_ptr(), scale, _dtype_code(q2),
+                                                     self.total_q_heads, first, self.segment.link, _stream_ptr(q2.device)),
+                  "ojasx_b200_kvq_decode_gather")
+            self.segment.wait()
+            return o
         o = self.cache.decode(q_local, scale)                      # [B, Hq_local, hd]
         width = max(b - a for a, b in self.q_ranges)
         pad = o.new_zeros((o.shape[0], width, o.shape[2]))         # equal-sized pieces: ragged shards are padded
