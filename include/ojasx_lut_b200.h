@@ -254,6 +254,9 @@ OJASX_API OjasxPeerLinkHandle ojasx_b200_peer_link_create(void* const* d_segment
 OJASX_API void ojasx_b200_peer_link_destroy(OjasxPeerLinkHandle link);
 OJASX_API int ojasx_b200_peer_signal(OjasxPeerLinkHandle link, void* stream);       /* for producers outside this library */
 OJASX_API int ojasx_b200_peer_wait(OjasxPeerLinkHandle link, void* stream);
+/* d_src [bytes] (a multiple of 4) to d_dst_shared in every rank's segment, then the flag: the gather of small
+ * per-rank records (each rank puts into its own slot), e.g. the (max, index) pairs of a vocabulary-split arg-max. */
+OJASX_API int ojasx_b200_peer_put(OjasxPeerLinkHandle link, void* d_dst_shared, const void* d_src, size_t bytes, void* stream);
 OJASX_API int ojasx_b200_peer_take_status(OjasxPeerLinkHandle link);                 /* 1: a wait ran out since the last call */
 /* Rows [row_start, row_stop) of the layer into columns [row_start, row_stop) of d_y_full [batch, out_features]
  * on every rank (d_y_full inside the link's segment), then the flag: the row-split linear with its all-gather.

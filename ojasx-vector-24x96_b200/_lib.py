@@ -106,6 +106,7 @@ SIGNATURES = {
     "ojasx_b200_peer_link_destroy": (None, [_vp]),
     "ojasx_b200_peer_signal": (_i, [_vp, _vp]),
     "ojasx_b200_peer_wait": (_i, [_vp, _vp]),
+    "ojasx_b200_peer_put": (_i, [_vp, _vp, _vp, _sz, _vp]),
     "ojasx_b200_peer_take_status": (_i, [_vp]),
     "ojasx_b200_linear_forward_gather": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "ojasx_b200_linear_group_set_rows": (_i, [_vp, _i, _i]),

@@ -181,7 +181,8 @@ int ojasx_b200_linear_forward(OjasxLinearHandle handle, const void* d_x, void* d
     // bf16 batches at or above the measured switch-over run on the tensor cores (dequant_gemm.cu);
     // OJASX_B200_TENSOR_MIN_BATCH overrides the threshold (0 = never).
     if (io_dtype == OJX_BF16 && dequant_gemm_supported(P, h->csr_sorted)) {
-        static const int min_batch = [] { const char* e = getenv("OJASX_B200_TENSOR_MIN_BATCH"); return e ? atoi(e) : kTensorMinBatch; }();
+        const char* e = getenv("OJASX_B200_TENSOR_MIN_BATCH");   // read per call: a process can time both paths
+        const int min_batch = e ? atoi(e) : kTensorMinBatch;
         if (min_batch > 0 && batch_size >= min_batch) return launch_dequant_gemm(P, static_cast<cudaStream_t>(stream), &h->dq_scratch, &h->dq_scratch_cap);
     }
     return launch_linear(P, static_cast<cudaStream_t>(stream));

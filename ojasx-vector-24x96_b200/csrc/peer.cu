@@ -24,6 +24,14 @@ struct PeerLinkHandle {
 __global__ void peer_signal_kernel(const __grid_constant__ PeerLink L) { peer_signal_when_last(L, 1u); }
 __global__ void peer_wait_kernel(const __grid_constant__ PeerLink L) { peer_wait_warp(L); }
 
+// dst (same offset in every rank's segment) <- src, 4 bytes per thread and step, then the flag.
+__global__ void __launch_bounds__(256) peer_put_kernel(const __grid_constant__ PeerLink L, unsigned* __restrict__ dst,
+                                                       const unsigned* __restrict__ src, size_t words) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < words; i += (size_t)gridDim.x * blockDim.x)
+        peer_store(L, dst + i, src[i]);
+    peer_signal_when_last(L, gridDim.x);
+}
+
 const PeerLink* peer_link_of(void* handle) { return handle ? &static_cast<PeerLinkHandle*>(handle)->link : nullptr; }
 
 }  // namespace ojx
@@ -99,6 +107,18 @@ void ojasx_b200_peer_link_destroy(OjasxPeerLinkHandle link) {
 int ojasx_b200_peer_signal(OjasxPeerLinkHandle link, void* stream) {
     if (!link) return OJX_ERR_ARG;
     peer_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<PeerLinkHandle*>(link)->link);
+    OJX_CUDA_TRY(cudaGetLastError());
+    count_launch(1);
+    return OJX_OK;
+}
+
+int ojasx_b200_peer_put(OjasxPeerLinkHandle link, void* d_dst_shared, const void* d_src, size_t bytes, void* stream) {
+    if (!link || !d_dst_shared || !d_src || bytes == 0 || (bytes & 3)) return OJX_ERR_ARG;
+    const size_t words = bytes / 4;
+    const unsigned grid = (unsigned)((words + 255) / 256 < 148 ? (words + 255) / 256 : 148);
+    peer_put_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<PeerLinkHandle*>(link)->link,
+                                                                      static_cast<unsigned*>(d_dst_shared),
+                                                                      static_cast<const unsigned*>(d_src), words);
     OJX_CUDA_TRY(cudaGetLastError());
     count_launch(1);
     return OJX_OK;

@@ -92,17 +92,39 @@ def make_stack_weights(seed: int, cfg: StackConfig) -> StackWeights:
 
 
 class _Layer:
-    def __init__(self, w: LayerWeights, cfg: StackConfig, batch: int, device):
+    def __init__(self, w: LayerWeights, cfg: StackConfig, batch: int, device, segment=None, dtype=torch.float32):
         self.q, self.k, self.v, self.o = (VQLinear.from_weights(a) for a in (w.q, w.k, w.v, w.o))
-        # one sequence: q, k and v read the same vector and run as one grouped launch into a fixed buffer
-        self.qkv = VQLinearGroup([self.q, self.k, self.v]) if batch == 1 else None
-        self.qkv_out = None
-        self.moe = VQMoE(w.moe)
-        self.moe.reserve(batch, cfg.top_k)
         self.norm1 = torch.from_numpy(w.norm1).to(device)
         self.norm2 = torch.from_numpy(w.norm2).to(device)
-        self.cache = VQKVCache(batch, cfg.kv_heads, cfg.q_heads, cfg.head_dim, cfg.block_dim, cfg.max_seq_len,
-                               w.k_codebook, w.v_codebook)
+        self.qkv_out = None
+        if segment is None:
+            # one sequence: q, k and v read the same vector and run as one grouped launch into a fixed buffer
+            self.qkv = VQLinearGroup([self.q, self.k, self.v]) if batch == 1 else None
+            self.moe = VQMoE(w.moe)
+            self.moe.reserve(batch, cfg.top_k)
+            self.cache = VQKVCache(batch, cfg.kv_heads, cfg.q_heads, cfg.head_dim, cfg.block_dim, cfg.max_seq_len,
+                                   w.k_codebook, w.v_codebook)
+            return
+        # One rank of several: its KV heads with their query heads, its rows of o_proj, its experts.  The three
+        # exchanges of a layer (attention outputs, o_proj outputs, expert outputs) are fused into the producing kernels.
+        from . import sharding
+        world, rank = segment.world, segment.rank
+        if cfg.kv_heads % world:
+            raise ValueError("the KV heads must divide evenly over the ranks")
+        self.qkv = None
+        R = cfg.q_heads // cfg.kv_heads
+        self.h0, self.h1 = sharding.split_range(cfg.kv_heads, world, rank)
+        self.kv_local = self.h1 - self.h0
+        self.q_rows = (self.h0 * R * cfg.head_dim, self.h1 * R * cfg.head_dim)
+        self.kv_rows = (self.h0 * cfg.head_dim, self.h1 * cfg.head_dim)
+        self.cache = VQKVCache(batch, self.kv_local, self.kv_local * R, cfg.head_dim, cfg.block_dim, cfg.max_seq_len,
+                               w.k_codebook[self.h0:self.h1], w.v_codebook[self.h0:self.h1])
+        self.kv_sharded = sharding.HeadShardedKVCache(self.cache, cfg.q_heads, total_kv_heads=cfg.kv_heads, segment=segment,
+                                                      dtype=dtype)
+        self.o_sharded = sharding.ShardedVQLinear(self.o, segment=segment, max_batch=batch, dtype=dtype)
+        e0, e1 = sharding.split_range(cfg.experts, world, rank)
+        self.moe = VQMoE(w.moe, (e0, e1))
+        self.moe_ep = sharding.ExpertParallelMoE(self.moe, segment=segment, max_tokens=batch, top_k=cfg.top_k)
 
 
 class VQDecoderStack:
@@ -114,14 +136,26 @@ class VQDecoderStack:
     """
 
     def __init__(self, weights: StackWeights, cfg: StackConfig, batch: int = 1, dtype: torch.dtype = torch.float32,
-                 device: Optional[torch.device] = None, use_graph: bool = False):
+                 device: Optional[torch.device] = None, use_graph: bool = False, segment=None):
+        """``segment``: a ``sharding.PeerSegment`` makes this the stack of ONE rank of several GPUs: KV heads (with the
+        q/k/v rows of their heads), o_proj rows, experts and lm_head rows are split over the ranks; hidden states are
+        replicated; every exchange goes through the segment.  Every rank must drive its stack with the same calls."""
         self.cfg, self.batch, self.dtype, self.use_graph = cfg, batch, dtype, use_graph
+        self.segment = segment
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.embed = torch.from_numpy(weights.embed).to(self.device)
         self.final_norm = torch.from_numpy(weights.final_norm).to(self.device)
         self.lm_head = VQLinear.from_weights(weights.lm_head)
         n = len(weights.layers)
-        self.layers = [_Layer(weights.layers[i % n], cfg, batch, self.device) for i in range(cfg.layers)]
+        self.layers = [_Layer(weights.layers[i % n], cfg, batch, self.device, segment, dtype) for i in range(cfg.layers)]
+        if segment is not None:
+            from . import sharding
+            self.lm_sharded = sharding.ShardedVQLinear(self.lm_head, segment=segment, max_batch=batch, dtype=dtype)
+            self.vocab_rows = (self.lm_sharded.row_start, self.lm_sharded.row_stop)
+            self._best = segment.alloc((segment.world, batch, 2), torch.float32)    # (max, index) of every rank's vocabulary shard
+            self._mine = torch.empty((batch, 2), dtype=torch.float32, device=self.device)
+            self._next = None
+        self.gather_logits = True
         self.pos = torch.zeros(batch, dtype=torch.int32, device=self.device)
         self.position = 0
         self._graph = None
@@ -167,6 +201,8 @@ class VQDecoderStack:
         cfg, B = self.cfg, self.batch
         h = self.embed[ids].to(self.dtype)
         pending = None                       # residual branch not yet added to h (added inside the next norm)
+        if self.segment is not None:
+            return self._enqueue_step_sharded(h)
         for l in self.layers:
             a = rmsnorm(h, l.norm1, cfg.rms_eps, add=pending)
             if l.qkv is not None:
@@ -189,6 +225,40 @@ class VQDecoderStack:
         a = rmsnorm(h, self.final_norm, cfg.rms_eps, add=pending)
         add_int_(self.pos, 1)
         return self.lm_head(a).float()
+
+    def _enqueue_step_sharded(self, h: torch.Tensor) -> torch.Tensor:
+        """The step of one rank (see ``__init__``); returns the gathered fp32 logits and leaves the greedy next
+        token of every sequence, found by an arg-max over the ranks' vocabulary shards, in ``self._next``."""
+        cfg, B = self.cfg, self.batch
+        R = cfg.q_heads // cfg.kv_heads
+        pending = None
+        for l in self.layers:
+            a = rmsnorm(h, l.norm1, cfg.rms_eps, add=pending)
+            q = l.q.forward(a, *l.q_rows).view(B, l.kv_local * R, cfg.head_dim)
+            k = l.k.forward(a, *l.kv_rows).view(B, l.kv_local, cfg.head_dim)
+            v = l.v.forward(a, *l.kv_rows).view(B, l.kv_local, cfg.head_dim)
+            rope_qk_(q, k, self.pos, cfg.rope_theta)
+            l.cache.append(k, v)
+            att = l.kv_sharded.decode(q)                                         # [B, all query heads, hd] on every rank
+            o = l.o_sharded.forward(att.view(B, cfg.q_heads * cfg.head_dim))     # [B, hidden] on every rank
+            m = rmsnorm(h, l.norm2, cfg.rms_eps, add=o)
+            pending = l.moe_ep.forward_routed(m, cfg.top_k)
+        a = rmsnorm(h, self.final_norm, cfg.rms_eps, add=pending)
+        add_int_(self.pos, 1)
+        # lm_head split over the vocabulary: arg-max of the own shard, (max, index) to every rank, arg-max over ranks
+        # (the lowest rank wins a tie, i.e. the lowest index, as torch.argmax does on the full row)
+        v0, v1 = self.vocab_rows
+        local = self.lm_head.forward(a, v0, v1).float()
+        best, where = torch.max(local, dim=-1)
+        self._mine[:, 0] = best
+        self._mine[:, 1] = (where + v0).float()            # exact: vocabulary indices are below 2^24
+        self.segment.put(self._best[self.segment.rank], self._mine)
+        self.segment.wait()
+        pick = torch.argmax(self._best[:, :, 0], dim=0)
+        self._next = self._best[pick, torch.arange(B, device=self.device), 1].long()
+        # the full logits on every rank cost one more gather (vocab * 4 bytes per sequence): greedy decoding does
+        # not need them, so `gather_logits = False` returns this rank's shard [B, v1 - v0] instead
+        return self.lm_sharded.forward(a).float() if self.gather_logits else local
 
     @torch.no_grad()
     def decode_step(self, token_ids: torch.Tensor) -> torch.Tensor:
@@ -234,7 +304,8 @@ class VQDecoderStack:
         logits = self.prefill(prompt_ids)
         out = []
         for _ in range(max_new_tokens):
-            nxt = torch.argmax(logits, dim=-1)
+            # several ranks: the arg-max over the vocabulary shards that the step left behind (same token on every rank)
+            nxt = torch.argmax(logits, dim=-1) if self.segment is None else self._next.clone()
             out.append(nxt)
             logits = self.decode_step(nxt)
         return torch.stack(out, dim=1)

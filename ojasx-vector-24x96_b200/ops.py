@@ -138,6 +138,20 @@ class VQLinearGroup:
                                                     _stream_ptr(x.device)), "ojasx_b200_linear_group_forward")
         return y
 
+    def set_rows(self, row_start: int, row_stop: int) -> None:
+        """Restrict every member to output rows ``[row_start, row_stop)`` (a rank's share of a row-split group)."""
+        check(lib().ojasx_b200_linear_group_set_rows(self._g, row_start, row_stop), "ojasx_b200_linear_group_set_rows")
+
+    def forward_gather(self, x: torch.Tensor, y_full: torch.Tensor, link, shared_x: bool = False) -> torch.Tensor:
+        """The members' rows into the gathered layout ``y_full [P, out_features]`` on every rank of ``link``
+        (``y_full`` inside the link's shared segment), then the link's flag; wait on the link before reading."""
+        _require_cuda(x, "x")
+        xs = 0 if shared_x else x.stride(0) * x.element_size()
+        ys = y_full.stride(0) * y_full.element_size()
+        check(lib().ojasx_b200_linear_group_forward_gather(self._g, x.data_ptr(), xs, y_full.data_ptr(), ys, _dtype_code(x),
+                                                           link, _stream_ptr(x.device)), "ojasx_b200_linear_group_forward_gather")
+        return y_full
+
     def close(self):
         if getattr(self, "_g", None):
             lib().ojasx_b200_destroy_linear_group(self._g)

@@ -116,6 +116,14 @@ class PeerSegment:
             t = torch.as_tensor(_DeviceView(self.base + off, shape, _TYPESTR[dtype]), device=self.device)
         return t
 
+    def put(self, dst_shared: torch.Tensor, src: torch.Tensor) -> None:
+        """``src`` into ``dst_shared`` (a view of a buffer from ``alloc``) on every rank, then the flag."""
+        src = src.contiguous()
+        n = src.numel() * src.element_size()
+        assert n == dst_shared.numel() * dst_shared.element_size() and n % 4 == 0
+        self._check(self._lib.ojasx_b200_peer_put(self.link, dst_shared.data_ptr(), src.data_ptr(), n,
+                                                  torch.cuda.current_stream().cuda_stream), "ojasx_b200_peer_put")
+
     def signal(self) -> None:
         self._check(self._lib.ojasx_b200_peer_signal(self.link, torch.cuda.current_stream().cuda_stream), "ojasx_b200_peer_signal")
 

@@ -78,3 +78,48 @@ def test_fused_exchange_matches_unsharded_operators():
     for r in range(world):
         assert ret[r] == {"linear": True, "linear_b1": True, "moe": True, "moe_b1": True, "moe_fused": True, "kv": True,
                           "status": 0}, (r, ret[r])
+
+
+def _stack_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from ojasx_b200 import inference_engine as ie
+        from ojasx_b200 import sharding
+        cfg = ie.StackConfig(layers=2, hidden=256, q_heads=8, kv_heads=4, head_dim=32, experts=8, top_k=2, inter=128, vocab=1000,
+                             max_seq_len=24, distinct_layers=2, outlier_frac=0.01)
+        W = ie.make_stack_weights(11, cfg)
+        seg = sharding.PeerSegment(32 << 20)
+        whole = ie.VQDecoderStack(W, cfg, batch=2)                       # the unsharded stack on this device
+        ids = torch.randint(0, cfg.vocab, (2, 5), device=dev, generator=torch.Generator(device=dev).manual_seed(4))
+        want = whole.generate(ids, 6)
+        out = {}
+        for graph in (False, True):
+            part = ie.VQDecoderStack(W, cfg, batch=2, segment=seg, use_graph=graph)
+            got = part.generate(ids, 6)
+            out[f"tokens_graph{int(graph)}"] = bool(torch.equal(got, want))
+            part.reset()
+            whole.reset()
+            la, lb = part.decode_step(ids[:, 0]), whole.decode_step(ids[:, 0])
+            out[f"logits_graph{int(graph)}"] = bool(torch.allclose(la, lb, rtol=1e-4, atol=1e-5))
+            del part
+        out["status"] = seg.take_status()
+        torch.cuda.synchronize()
+        seg.close()
+        ret[rank] = out
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sharded_decoder_stack_matches_one_device():
+    """KV heads, o_proj rows, experts and the vocabulary split over two ranks: same greedy tokens as one device (the
+    expert outputs are combined in caller order on every rank, the arg-max runs over the ranks' vocabulary shards)."""
+    world = 2
+    ret = mp.Manager().dict()
+    mp.spawn(_stack_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    for r in range(world):
+        assert ret[r] == {"tokens_graph0": True, "logits_graph0": True, "tokens_graph1": True, "logits_graph1": True,
+                          "status": 0}, (r, ret[r])
