@@ -21,7 +21,7 @@
 namespace ojx {
 
 constexpr int kMaxPeers = 8;
-constexpr int kPeerSpin = 1 << 22;      // bounded polling (a couple of seconds at most)
+constexpr int kPeerSpin = 1 << 23;      // bounded polling: about two seconds with the back-off below
 
 struct PeerLink {
     long long delta[kMaxPeers];   // bytes from this rank's segment to rank p's mapping of its segment (0 for self)
@@ -66,6 +66,9 @@ __device__ __forceinline__ void peer_signal_when_last(const PeerLink& L, unsigne
 __device__ __forceinline__ void peer_wait_warp(const PeerLink& L) {
     if (L.n <= 0) return;
     const int lane = threadIdx.x & 31;
+    // Once a wait has run out the ranks are out of step and every later wait would run out too: give up at once
+    // (the host reads and clears the status), so that a broken run ends quickly instead of spinning for hours.
+    if (*reinterpret_cast<volatile int*>(L.status) != 0) return;
     const int e = *reinterpret_cast<volatile int*>(L.epoch);
     if (lane < L.n) {
         bool ok = false;
@@ -73,6 +76,7 @@ __device__ __forceinline__ void peer_wait_warp(const PeerLink& L) {
             int v;
             asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(L.flags + lane) : "memory");
             if (v - e >= 0) { ok = true; break; }
+            if (i > 1024) __nanosleep(256);
         }
         if (!ok) atomicExch(L.status, 1);
     }

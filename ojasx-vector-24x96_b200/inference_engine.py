@@ -92,7 +92,7 @@ def make_stack_weights(seed: int, cfg: StackConfig) -> StackWeights:
 
 
 class _Layer:
-    def __init__(self, w: LayerWeights, cfg: StackConfig, batch: int, device, segment=None, dtype=torch.float32):
+    def __init__(self, w: LayerWeights, cfg: StackConfig, batch: int, device, segment=None, dtype=torch.float32, shared=None):
         self.q, self.k, self.v, self.o = (VQLinear.from_weights(a) for a in (w.q, w.k, w.v, w.o))
         self.norm1 = torch.from_numpy(w.norm1).to(device)
         self.norm2 = torch.from_numpy(w.norm2).to(device)
@@ -119,12 +119,16 @@ class _Layer:
         self.kv_rows = (self.h0 * cfg.head_dim, self.h1 * cfg.head_dim)
         self.cache = VQKVCache(batch, self.kv_local, self.kv_local * R, cfg.head_dim, cfg.block_dim, cfg.max_seq_len,
                                w.k_codebook[self.h0:self.h1], w.v_codebook[self.h0:self.h1])
+        # `shared`: exchange buffers of this layer (att, o, expert outputs), handed out by the stack: consecutive layers
+        # get different ones, a layer always the same one, so a buffer is written again six exchanges later
+        att, o, eo = shared
         self.kv_sharded = sharding.HeadShardedKVCache(self.cache, cfg.q_heads, total_kv_heads=cfg.kv_heads, segment=segment,
-                                                      dtype=dtype)
-        self.o_sharded = sharding.ShardedVQLinear(self.o, segment=segment, max_batch=batch, dtype=dtype)
+                                                      dtype=dtype, buffers=(att, att))
+        self.o_sharded = sharding.ShardedVQLinear(self.o, segment=segment, max_batch=batch, dtype=dtype, buffers=(o, o))
         e0, e1 = sharding.split_range(cfg.experts, world, rank)
         self.moe = VQMoE(w.moe, (e0, e1))
-        self.moe_ep = sharding.ExpertParallelMoE(self.moe, segment=segment, max_tokens=batch, top_k=cfg.top_k)
+        self.moe_ep = sharding.ExpertParallelMoE(self.moe, segment=segment, max_tokens=batch, top_k=cfg.top_k, buffers=(eo, eo))
+        self.moe.reserve(batch, cfg.top_k)
 
 
 class VQDecoderStack:
@@ -147,7 +151,11 @@ class VQDecoderStack:
         self.final_norm = torch.from_numpy(weights.final_norm).to(self.device)
         self.lm_head = VQLinear.from_weights(weights.lm_head)
         n = len(weights.layers)
-        self.layers = [_Layer(weights.layers[i % n], cfg, batch, self.device, segment, dtype) for i in range(cfg.layers)]
+        shared = [None, None]
+        if segment is not None:      # two sets of exchange buffers, for even and odd layers
+            shared = [(segment.alloc((batch, cfg.q_heads, cfg.head_dim), dtype), segment.alloc((batch, cfg.hidden), dtype),
+                       segment.alloc((batch * cfg.top_k, cfg.hidden), torch.float32)) for _ in range(2)]
+        self.layers = [_Layer(weights.layers[i % n], cfg, batch, self.device, segment, dtype, shared[i & 1]) for i in range(cfg.layers)]
         if segment is not None:
             from . import sharding
             self.lm_sharded = sharding.ShardedVQLinear(self.lm_head, segment=segment, max_batch=batch, dtype=dtype)

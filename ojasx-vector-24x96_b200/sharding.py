@@ -149,12 +149,15 @@ class PeerSegment:
 class ShardedVQLinear:
     """Row-split linear: this rank evaluates rows ``split_range(M, world, rank, 32)`` of a full ``ops.VQLinear``."""
 
-    def __init__(self, layer, group=None, segment: "PeerSegment" = None, max_batch: int = 1, dtype=torch.float32):
+    def __init__(self, layer, group=None, segment: "PeerSegment" = None, max_batch: int = 1, dtype=torch.float32, buffers=None):
+        """``buffers``: two gathered-output tensors from ``segment.alloc`` to use instead of allocating a pair (callers
+        that run many sharded layers in a fixed order can share buffers between layers that are at least two
+        exchanges apart; pass the same tensor twice to pin a layer to one buffer)."""
         self.layer, self.group, self.segment = layer, group, segment
         self.row_start, self.row_stop = split_range(layer.out_features, dist.get_world_size(group), dist.get_rank(group), 32)
         self._turn = 0
         if segment is not None:     # two gathered outputs, used in turn (see PeerSegment)
-            self._y = [segment.alloc((max_batch, layer.out_features), dtype) for _ in range(2)]
+            self._y = list(buffers) if buffers is not None else [segment.alloc((max_batch, layer.out_features), dtype) for _ in range(2)]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         x2 = x.reshape(-1, x.shape[-1])
@@ -180,11 +183,12 @@ class ShardedVQLinear:
 class ExpertParallelMoE:
     """Expert-parallel MoE: ``moe`` is an ``ops.VQMoE`` built with ``expert_range=split_range(E, world, rank)``."""
 
-    def __init__(self, moe, group=None, segment: "PeerSegment" = None, max_tokens: int = 1, top_k: int = 10):
+    def __init__(self, moe, group=None, segment: "PeerSegment" = None, max_tokens: int = 1, top_k: int = 10, buffers=None):
         self.moe, self.group, self.segment = moe, group, segment
         self._turn = 0
         if segment is not None:     # per-pair expert outputs of every rank, two buffers used in turn
-            self._eo = [segment.alloc((max_tokens * top_k, moe.hidden), torch.float32) for _ in range(2)]
+            self._eo = list(buffers) if buffers is not None else \
+                [segment.alloc((max_tokens * top_k, moe.hidden), torch.float32) for _ in range(2)]
             self.moe.reserve(max_tokens, top_k)
 
     def _gathered(self, x, call, *args):
@@ -230,12 +234,13 @@ class HeadShardedKVCache:
     """KV-head split: ``cache`` is an ``ops.VQKVCache`` holding KV heads ``split_range(Hkv, world, rank)`` only."""
 
     def __init__(self, cache, total_q_heads: int, group=None, total_kv_heads: int = 0, segment: "PeerSegment" = None,
-                 dtype=torch.float32):
+                 dtype=torch.float32, buffers=None):
         self.cache, self.total_q_heads, self.group, self.segment = cache, total_q_heads, group, segment
         world = dist.get_world_size(group)
         self._turn = 0
         if segment is not None:
-            self._o = [segment.alloc((cache.batch, total_q_heads, cache.head_dim), dtype) for _ in range(2)]
+            self._o = list(buffers) if buffers is not None else \
+                [segment.alloc((cache.batch, total_q_heads, cache.head_dim), dtype) for _ in range(2)]
         # query heads held by every rank (ragged when the KV heads do not divide evenly)
         kv = total_kv_heads or world * cache.kv_heads
         per_kv = total_q_heads // kv
