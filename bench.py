@@ -767,6 +767,11 @@ def bench_stack(args, E):
         t0 = time.perf_counter()
         logits = stack.prefill(ids)
         E.barrier()
+        dt_pre = E.max_over_ranks(time.perf_counter() - t0)
+        # one untimed step: it records the decode step into a CUDA graph (warm-up launch + capture), which is not decoding
+        nxt = torch.argmax(logits, dim=-1) if E.seg is None else stack._next.clone()
+        logits = stack.decode_step(nxt)
+        E.barrier()
         t1 = time.perf_counter()
         for _ in range(args.stack_new):
             nxt = torch.argmax(logits, dim=-1) if E.seg is None else stack._next.clone()
@@ -774,7 +779,6 @@ def bench_stack(args, E):
         E.barrier()
         t2 = time.perf_counter()
         dt_dec = E.max_over_ranks(t2 - t1)
-        dt_pre = E.max_over_ranks(t1 - t0)
         ctx = args.stack_prompt + args.stack_new // 2
         experts_hit = cfg.experts * (1 - (1 - cfg.top_k / cfg.experts) ** B)
         step_bytes = cfg.layers * (per_layer + experts_hit * exp_bytes + B * ctx * 256) + W.lm_head.algorithmic_bytes(0)
@@ -782,6 +786,8 @@ def bench_stack(args, E):
                         "decode_tokens_per_s": round(B * args.stack_new / dt_dec, 1),
                         "ms_per_decode_step": round(dt_dec / args.stack_new * 1e3, 3),
                         "prompt": args.stack_prompt, "new_tokens": args.stack_new, "dtype": args.stack_dtype,
+                        "prefill": "positions batched through linears and MoE, attention position by position" if E.seg is None
+                                   else "token by token through the sharded decode step",
                         "bytes_per_step_estimate": int(step_bytes),
                         "roofline": hbm_roofline(step_bytes, dt_dec / args.stack_new, E.world,
                                                  note="a decode step is a chain of about 340 small launches per rank; latency, not bandwidth, bounds it"),

@@ -278,8 +278,7 @@ class VQDecoderStack:
         if not self.use_graph:
             return self._enqueue_step(ids)
         if self._graph is None:
-            if self.position != 1:
-                raise RuntimeError("the first graph-mode step must come right after reset(): capture starts on empty caches")
+            cached = self.position - 1      # tokens in the caches before this step (a prefill may have put some there)
             # warm-up on a side stream (lazy kernel attributes, occupancy queries, scratch growth) ...
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
@@ -289,8 +288,9 @@ class VQDecoderStack:
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
             # ... whose token is dropped again before the capture; a capture records launches, it runs nothing
-            self.reset()
-            self.position = 1
+            for l in self.layers:
+                l.cache.crop(cached)
+            self.pos.fill_(cached)
             self._graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self._graph):
                 self._logits = self._enqueue_step(self._ids)
@@ -299,12 +299,61 @@ class VQDecoderStack:
         return self._logits
 
     @torch.no_grad()
-    def prefill(self, prompt_ids: torch.Tensor) -> torch.Tensor:
-        """Feeds the prompt ``[batch, S]`` token by token (the quantised cache is append-only); returns the last logits."""
+    def prefill(self, prompt_ids: torch.Tensor, batched: Optional[bool] = None, max_rows: int = 1024) -> torch.Tensor:
+        """The prompt ``[batch, S]`` into the caches; returns the logits after its last token (one model call over the
+        prompt, ``ojasx_24x96/engine.py:153-175``).
+
+        ``batched`` (default on one device): all positions of a chunk of the prompt go through the linears and the MoE
+        as ONE batch -- the regime of the batched kernels: persistent table kernel in fp32, tensor-core dequant GEMM
+        for bf16 -- while attention, whose quantised cache grows a token at a time, appends and decodes position by
+        position.  Results are those of the token-by-token form (every kernel keeps its summation order whatever the
+        batch).  ``max_rows`` bounds batch * positions per chunk (scratch of the MoE grows with it).  Otherwise, and on
+        a stack split over several ranks, the prompt is fed through ``decode_step`` token by token."""
+        if batched is None:
+            batched = self.segment is None
+        if not batched or self.segment is not None:
+            logits = None
+            for s in range(prompt_ids.shape[1]):
+                logits = self.decode_step(prompt_ids[:, s])
+            return logits
+        ids = prompt_ids.to(self.device).to(torch.int64)
+        S = ids.shape[1]
+        if self.position + S > self.cfg.max_seq_len:
+            raise ValueError(f"the KV caches hold max_seq_len = {self.cfg.max_seq_len} tokens")
+        step = max(1, max_rows // self.batch)
         logits = None
-        for s in range(prompt_ids.shape[1]):
-            logits = self.decode_step(prompt_ids[:, s])
+        for s0 in range(0, S, step):
+            logits = self._prefill_chunk(ids[:, s0:s0 + step])
         return logits
+
+    def _prefill_chunk(self, ids: torch.Tensor) -> torch.Tensor:
+        """``ids [batch, Sc]``: rows are ordered position-major (row = s * batch + b), so that the q, k, v and attention
+        rows of one position are contiguous ``[batch, heads, head_dim]`` blocks for the cache calls."""
+        cfg, B = self.cfg, self.batch
+        Sc = ids.shape[1]
+        rows = B * Sc
+        h = self.embed[ids.t().reshape(-1)].to(self.dtype)
+        pos_rows = (self.pos.view(1, B) + torch.arange(Sc, device=self.device, dtype=torch.int32).view(Sc, 1)).reshape(-1).contiguous()
+        pending = None
+        for l in self.layers:
+            l.moe.reserve(rows, cfg.top_k)
+            a = rmsnorm(h, l.norm1, cfg.rms_eps, add=pending)
+            q = l.q(a).view(rows, cfg.q_heads, cfg.head_dim)
+            k = l.k(a).view(rows, cfg.kv_heads, cfg.head_dim)
+            v = l.v(a).view(rows, cfg.kv_heads, cfg.head_dim)
+            rope_qk_(q, k, pos_rows, cfg.rope_theta)
+            q4, k4, v4 = (t.view(Sc, B, t.shape[1], cfg.head_dim) for t in (q, k, v))
+            att = torch.empty_like(q4)
+            for s in range(Sc):
+                l.cache.append(k4[s], v4[s])
+                l.cache.decode(q4[s], out=att[s])
+            o = l.o(att.view(rows, cfg.q_heads * cfg.head_dim))
+            m = rmsnorm(h, l.norm2, cfg.rms_eps, add=o)
+            pending = l.moe.forward_routed(m, cfg.top_k)
+        a = rmsnorm(h, self.final_norm, cfg.rms_eps, add=pending)
+        add_int_(self.pos, Sc)
+        self.position += Sc
+        return self.lm_head(a[(Sc - 1) * B:].contiguous()).float()
 
     @torch.no_grad()
     def generate(self, prompt_ids: torch.Tensor, max_new_tokens: int) -> torch.Tensor:

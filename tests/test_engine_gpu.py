@@ -101,3 +101,28 @@ def test_decoder_stack_graph_replay_equals_eager(cuda):
         b = graph.decode_step(ids).clone()
         assert torch.equal(a, b), s
     assert graph.layers[0].cache.sync_len() == 9
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_batched_prefill_equals_token_by_token(cuda, dtype):
+    """The prompt as one batch through the linears and the MoE (attention position by position) leaves the same
+    caches and logits as feeding it token by token; a captured decode step can start on the prefilled caches."""
+    W = ie.make_stack_weights(13, CFG)
+    toks = torch.from_numpy(np.random.default_rng(1).integers(0, CFG.vocab, size=(2, 11))).to(cuda)
+    one = ie.VQDecoderStack(W, CFG, batch=2, dtype=dtype)
+    ref = one.prefill(toks, batched=False)
+    for graph in (False, True):
+        st = ie.VQDecoderStack(W, CFG, batch=2, dtype=dtype, use_graph=graph)
+        got = st.prefill(toks, max_rows=8)            # three chunks of four, four and three positions
+        if dtype == torch.float32:
+            assert torch.equal(got, ref)
+        else:                                           # bf16 batches may take another kernel than single tokens
+            assert torch.allclose(got, ref, rtol=5e-2, atol=5e-2)
+        assert st.layers[1].cache.sync_len() == 11 and st.position == 11
+        nxt = torch.argmax(ref, dim=-1)
+        a, b = st.decode_step(nxt).clone(), one.decode_step(nxt)
+        if dtype == torch.float32:
+            assert torch.equal(a, b), graph
+        assert st.layers[0].cache.sync_len() == 12
+        one.reset()
+        one.prefill(toks, batched=False)
