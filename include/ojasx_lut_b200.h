@@ -277,9 +277,12 @@ OJASX_API int ojasx_b200_linear_group_forward_gather(OjasxLinearGroupHandle grou
 OJASX_API int ojasx_b200_moe_forward_gather(OjasxMoEHandle handle, const void* d_x, const int* d_topk_idx,
                                             const float* d_topk_w, void* d_y, int n_tokens, int k_active, int io_dtype,
                                             OjasxPeerLinkHandle link, float* d_expert_out_shared, void* stream);
+/* Routed form.  d_logits_shared [n_tokens, num_experts_total] (inside the segment) or NULL: with it every rank scores
+ * only the experts it holds and stores their logits into every rank's buffer (one more exchange on the link, before
+ * the top-k pass); without it every rank scores all experts itself.  Same routing either way. */
 OJASX_API int ojasx_b200_moe_forward_routed_gather(OjasxMoEHandle handle, const void* d_x, void* d_y, int n_tokens,
                                                    int top_k, int io_dtype, OjasxPeerLinkHandle link,
-                                                   float* d_expert_out_shared, void* stream);
+                                                   float* d_expert_out_shared, float* d_logits_shared, void* stream);
 
 /* ---- Codebook-VQ KV cache of one layer (no counterpart in the reference, whose HeadKVCache
  * allocates k_codebook / v_codebook but never reads them, ojasx_lut_kv_cache.h:33-35): every

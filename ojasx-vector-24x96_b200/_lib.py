@@ -112,7 +112,7 @@ SIGNATURES = {
     "ojasx_b200_linear_group_set_rows": (_i, [_vp, _i, _i]),
     "ojasx_b200_linear_group_forward_gather": (_i, [_vp, _vp, _sz, _vp, _sz, _i, _vp, _vp]),
     "ojasx_b200_moe_forward_gather": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
-    "ojasx_b200_moe_forward_routed_gather": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp]),
+    "ojasx_b200_moe_forward_routed_gather": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "ojasx_b200_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
     "ojasx_b200_rope_qk": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp]),
     "ojasx_b200_add_int": (_i, [_vp, _i, _i, _vp]),

@@ -211,7 +211,8 @@ int ojasx_b200_moe_forward_gather(OjasxMoEHandle handle, const void* d_x, const 
 }
 
 int ojasx_b200_moe_forward_routed_gather(OjasxMoEHandle handle, const void* d_x, void* d_y, int n_tokens, int top_k,
-                                         int io_dtype, OjasxPeerLinkHandle link, float* d_expert_out_shared, void* stream) {
+                                         int io_dtype, OjasxPeerLinkHandle link, float* d_expert_out_shared,
+                                         float* d_logits_shared, void* stream) {
     if (!handle || !d_x || !d_y || n_tokens <= 0 || top_k <= 0 || !link || !d_expert_out_shared) return OJX_ERR_ARG;
     auto* h = static_cast<MoeHandle*>(handle);
     if (!h->router) { set_last_error_msg("moe_forward_routed_gather: no router weights set"); return OJX_ERR_ARG; }
@@ -226,8 +227,10 @@ int ojasx_b200_moe_forward_routed_gather(OjasxMoEHandle handle, const void* d_x,
     MoeProblem P = h->problem(d_x, d_y, idx, w, n_tokens, top_k, io_dtype);
     P.expert_out = d_expert_out_shared;
     P.lut_blocks = moe_fused_wanted(P) ? 1 : 0;
-    rc = launch_moe_router(h->router, d_x, io_dtype, n_tokens, h->H, h->E_total, top_k, logits, probs, idx, w, s,
-                           P.cb_in, P.Kcb, P.D, const_cast<float*>(P.lut_in), P.lut_blocks);
+    // with a shared logits buffer every rank scores only the experts it holds (an exchange of its own on the link)
+    rc = launch_moe_router(h->router, d_x, io_dtype, n_tokens, h->H, h->E_total, top_k, d_logits_shared ? d_logits_shared : logits,
+                           probs, idx, w, s, P.cb_in, P.Kcb, P.D, const_cast<float*>(P.lut_in), P.lut_blocks,
+                           d_logits_shared ? peer_link_of(link) : nullptr, h->expert_offset, h->expert_offset + h->E);
     if (rc != OJX_OK) return rc;
     P.lut_ready = P.lut_in != nullptr;
     return launch_moe_experts(P, s, peer_link_of(link));

@@ -44,7 +44,7 @@ int launch_silu_mul(const void* gate, const void* up, void* out, size_t n, int i
 int launch_moe_router(const float* Wr, const void* x, int io_dtype, int n_tokens, int H, int E, int k,
                       float* logits, float* probs, int* idx_out, float* w_out, cudaStream_t stream,
                       const float* codebook = nullptr, int Kcb = 0, int D = 0, float* lut_out = nullptr,
-                      int lut_blocks = 0);
+                      int lut_blocks = 0, const PeerLink* link = nullptr, int e_begin = 0, int e_end = 0);
 
 // --- moe_fused.cu: whole-expert work items (gate/up, SiLU gate and down fused) for batches of tokens
 bool moe_fused_wanted(const MoeProblem& P);   // shape fits and enough routed pairs are expected here

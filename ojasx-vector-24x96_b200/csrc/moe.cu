@@ -229,11 +229,13 @@ __global__ void moe_combine_kernel(const __grid_constant__ MoeProblem P, const _
 // off = 16..1.  One warp per expert (its row of W stays hot in L1 while the warp loops over the
 // tokens of its blockIdx.y stripe).
 
+// Experts [e_begin, e_end) only (an expert-parallel rank scores the experts it holds); with a link the logits go to
+// every rank's copy of the logits buffer.
 __device__ __forceinline__ void router_logits_block(const float* __restrict__ Wr, const void* __restrict__ x, int io_dtype,
                                                     int n_tokens, int H, int E, float* __restrict__ logits, int bx, int by,
-                                                    int nby) {
-    const int warp = (bx * 256 + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (warp >= E) return;
+                                                    int nby, int e_begin, int e_end, const PeerLink& link) {
+    const int warp = e_begin + ((bx * 256 + threadIdx.x) >> 5), lane = threadIdx.x & 31;
+    if (warp >= e_end) return;
     const float* w = Wr + (size_t)warp * H;
     const size_t esz = io_dtype == OJX_BF16 ? 2 : 4;
     for (int t = by; t < n_tokens; t += nby) {
@@ -250,14 +252,16 @@ __device__ __forceinline__ void router_logits_block(const float* __restrict__ Wr
         for (; c < H; c += 32) part = __fadd_rn(part, __fmul_rn(w[c], xl(c)));
 #pragma unroll
         for (int off = 16; off >= 1; off >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, off));
-        if (lane == 0) logits[(size_t)t * E + warp] = part;
+        if (lane == 0) peer_store(link, logits + (size_t)t * E + warp, part);
     }
 }
 
 __global__ void __launch_bounds__(256) moe_router_logits_kernel(const float* __restrict__ Wr, const void* __restrict__ x,
                                                                 int io_dtype, int n_tokens, int H, int E,
-                                                                float* __restrict__ logits) {
-    router_logits_block(Wr, x, io_dtype, n_tokens, H, E, logits, blockIdx.x, blockIdx.y, gridDim.y);
+                                                                float* __restrict__ logits, int e_begin, int e_end,
+                                                                const __grid_constant__ PeerLink link) {
+    router_logits_block(Wr, x, io_dtype, n_tokens, H, E, logits, blockIdx.x, blockIdx.y, gridDim.y, e_begin, e_end, link);
+    peer_signal_when_last(link, gridDim.x * gridDim.y);
 }
 
 // Router logits and the per-token gate/up tables in one launch: neither depends on the other, both
@@ -268,15 +272,17 @@ __global__ void __launch_bounds__(256) moe_logits_prebuild_kernel(const float* _
                                                                   int io_dtype, int n_tokens, int H, int E,
                                                                   float* __restrict__ logits, int lx, int ly, int G,
                                                                   const float* __restrict__ codebook, int Kcb,
-                                                                  float* __restrict__ lut_out) {
+                                                                  float* __restrict__ lut_out, int e_begin, int e_end,
+                                                                  const __grid_constant__ PeerLink link) {
     __shared__ float xs[16 * D];
     const int b = blockIdx.x;
     if (b < lx * ly) {
-        router_logits_block(Wr, x, io_dtype, n_tokens, H, E, logits, b % lx, b / lx, ly);
+        router_logits_block(Wr, x, io_dtype, n_tokens, H, E, logits, b % lx, b / lx, ly, e_begin, e_end, link);
     } else {
         const int j = b - lx * ly, px = (G + 15) / 16;
         lut_prebuild_block<D>(x, io_dtype, H, G, codebook, Kcb, lut_out, j % px, j / px, xs);
     }
+    peer_signal_when_last(link, gridDim.x);
 }
 
 // One warp per token: softmax over E logits, k rounds of arg-max (ties to the lower index),
@@ -288,8 +294,13 @@ constexpr int kTopkWarps = 4;
 __global__ void __launch_bounds__(kTopkWarps * 32) moe_router_topk_kernel(const float* __restrict__ logits, int n_tokens, int E,
                                                                          int k, int* __restrict__ idx_out,
                                                                          float* __restrict__ w_out,
-                                                                         float* __restrict__ probs /* [n_tokens, E] scratch */) {
+                                                                         float* __restrict__ probs /* [n_tokens, E] scratch */,
+                                                                         const __grid_constant__ PeerLink link) {
     extern __shared__ float topk_smem[];  // [kTopkWarps][E]
+    if (link.n > 0) {   // the logits of the other ranks' experts arrive over the link
+        if (threadIdx.x < 32) peer_wait_warp(link);
+        __syncthreads();
+    }
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int t = blockIdx.x * kTopkWarps + wid;
     if (t >= n_tokens) return;
@@ -343,8 +354,13 @@ template <int EPL>
 __global__ void __launch_bounds__(kTopkWarps * 32) moe_router_topk_reg_kernel(const float* __restrict__ logits, int n_tokens,
                                                                              int E, int k, int* __restrict__ idx_out,
                                                                              float* __restrict__ w_out,
-                                                                             float* __restrict__ probs) {
+                                                                             float* __restrict__ probs,
+                                                                             const __grid_constant__ PeerLink link) {
     extern __shared__ float topk_smem[];  // [kTopkWarps][E]
+    if (link.n > 0) {   // the logits of the other ranks' experts arrive over the link
+        if (threadIdx.x < 32) peer_wait_warp(link);
+        __syncthreads();
+    }
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int t = blockIdx.x * kTopkWarps + wid;
     if (t >= n_tokens) return;
@@ -512,9 +528,9 @@ int launch_moe_experts(MoeProblem P, cudaStream_t s, const PeerLink* lk) {
     // Tiles: spread few pairs over the SMs, keep tiles whole when there are many pairs.  An
     // expert-parallel shard expects only its share of the routed pairs.
     const int expect = P.E_total > P.E ? (int)(((long long)pairs * P.E + P.E_total - 1) / P.E_total) : pairs;
-    // A handful of pairs on an unsharded expert table: the work list (grouping by expert, dropping the
-    // pairs of other shards) buys nothing, so its kernel is left out and the pairs are visited in order.
-    if (pairs <= kMoePlanMinPairs && P.E_total <= P.E) P.pair_list = nullptr;
+    // A handful of pairs: the work list (grouping by expert, dropping the pairs of other shards) buys nothing, so its
+    // kernel is left out and the pairs are visited in order (pairs of other shards are skipped on sight).
+    if (pairs <= kMoePlanMinPairs) P.pair_list = nullptr;
     int want = (sms + expect - 1) / (expect > 0 ? expect : 1);
     P.gu_tile = round_up((P.I + want - 1) / want, 16);
     if (P.gu_tile > kAccRows / 2) P.gu_tile = kAccRows / 2;
@@ -559,36 +575,44 @@ int take_moe_bulk_copy_error(int* out) {
 
 int launch_moe_router(const float* Wr, const void* x, int io_dtype, int n_tokens, int H, int E, int k,
                       float* logits, float* probs, int* idx_out, float* w_out, cudaStream_t s,
-                      const float* codebook, int Kcb, int D, float* lut_out, int lut_blocks) {
+                      const float* codebook, int Kcb, int D, float* lut_out, int lut_blocks, const PeerLink* lk,
+                      int e_begin, int e_end) {
     if (!Wr || !x || !logits || !probs || !idx_out || !w_out) return OJX_ERR_ARG;
     if (n_tokens <= 0 || k <= 0 || k > E) return OJX_ERR_ARG;
+    // With a link every rank scores the experts [e_begin, e_end) it holds and stores their logits into every rank's
+    // logits buffer; the top-k pass waits for all ranks.  Without one, all E experts are scored here.
+    const PeerLink none{};
+    const PeerLink& link = lk ? *lk : none;
+    if (link.n <= 0) { e_begin = 0; e_end = E; }
+    if (e_begin < 0 || e_end > E || e_begin > e_end) return OJX_ERR_ARG;
     if (lut_out && lut_blocks) {   // tables in 16-group blocks for the fused expert kernel: a launch of their own
         const int rc = launch_moe_prebuild_blocks(x, io_dtype, n_tokens, H, D, codebook, Kcb, lut_out, s);
         if (rc != OJX_OK) return rc;
         lut_out = nullptr;
     }
     const int warps_per_block = 8;
-    const int lx = (E + warps_per_block - 1) / warps_per_block, ly = n_tokens < 32 ? n_tokens : 32;
+    const int ne = e_end - e_begin > 0 ? e_end - e_begin : 1;
+    const int lx = (ne + warps_per_block - 1) / warps_per_block, ly = n_tokens < 32 ? n_tokens : 32;
     if (lut_out) {   // the gate/up tables ride along (one launch less)
         if (!codebook || H % D != 0) return OJX_ERR_ARG;
         const int G = H / D, grid = lx * ly + (G + 15) / 16 * n_tokens;
         switch (D) {
-            case 4: moe_logits_prebuild_kernel<4><<<grid, 256, 0, s>>>(Wr, x, io_dtype, n_tokens, H, E, logits, lx, ly, G, codebook, Kcb, lut_out); break;
-            case 8: moe_logits_prebuild_kernel<8><<<grid, 256, 0, s>>>(Wr, x, io_dtype, n_tokens, H, E, logits, lx, ly, G, codebook, Kcb, lut_out); break;
-            case 16: moe_logits_prebuild_kernel<16><<<grid, 256, 0, s>>>(Wr, x, io_dtype, n_tokens, H, E, logits, lx, ly, G, codebook, Kcb, lut_out); break;
-            case 32: moe_logits_prebuild_kernel<32><<<grid, 256, 0, s>>>(Wr, x, io_dtype, n_tokens, H, E, logits, lx, ly, G, codebook, Kcb, lut_out); break;
+            case 4: moe_logits_prebuild_kernel<4><<<grid, 256, 0, s>>>(Wr, x, io_dtype, n_tokens, H, E, logits, lx, ly, G, codebook, Kcb, lut_out, e_begin, e_end, link); break;
+            case 8: moe_logits_prebuild_kernel<8><<<grid, 256, 0, s>>>(Wr, x, io_dtype, n_tokens, H, E, logits, lx, ly, G, codebook, Kcb, lut_out, e_begin, e_end, link); break;
+            case 16: moe_logits_prebuild_kernel<16><<<grid, 256, 0, s>>>(Wr, x, io_dtype, n_tokens, H, E, logits, lx, ly, G, codebook, Kcb, lut_out, e_begin, e_end, link); break;
+            case 32: moe_logits_prebuild_kernel<32><<<grid, 256, 0, s>>>(Wr, x, io_dtype, n_tokens, H, E, logits, lx, ly, G, codebook, Kcb, lut_out, e_begin, e_end, link); break;
             default: return OJX_ERR_UNSUPPORTED;
         }
     } else {
-        moe_router_logits_kernel<<<dim3(lx, ly), 256, 0, s>>>(Wr, x, io_dtype, n_tokens, H, E, logits);
+        moe_router_logits_kernel<<<dim3(lx, ly), 256, 0, s>>>(Wr, x, io_dtype, n_tokens, H, E, logits, e_begin, e_end, link);
     }
     OJX_CUDA_TRY(cudaGetLastError());
     const size_t tsm = sizeof(float) * kTopkWarps * (size_t)E;
     if (tsm > 200 * 1024) return OJX_ERR_TOO_LARGE;
     if (tsm > 48 * 1024) OJX_CUDA_TRY(cudaFuncSetAttribute(moe_router_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tsm));
     const int tgrid = (n_tokens + kTopkWarps - 1) / kTopkWarps;
-    if (E <= 512) moe_router_topk_reg_kernel<16><<<tgrid, kTopkWarps * 32, tsm, s>>>(logits, n_tokens, E, k, idx_out, w_out, probs);
-    else moe_router_topk_kernel<<<tgrid, kTopkWarps * 32, tsm, s>>>(logits, n_tokens, E, k, idx_out, w_out, probs);
+    if (E <= 512) moe_router_topk_reg_kernel<16><<<tgrid, kTopkWarps * 32, tsm, s>>>(logits, n_tokens, E, k, idx_out, w_out, probs, link);
+    else moe_router_topk_kernel<<<tgrid, kTopkWarps * 32, tsm, s>>>(logits, n_tokens, E, k, idx_out, w_out, probs, link);
     OJX_CUDA_TRY(cudaGetLastError());
     count_launch(2);
     return OJX_OK;

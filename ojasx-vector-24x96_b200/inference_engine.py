@@ -121,13 +121,14 @@ class _Layer:
                                w.k_codebook[self.h0:self.h1], w.v_codebook[self.h0:self.h1])
         # `shared`: exchange buffers of this layer (att, o, expert outputs), handed out by the stack: consecutive layers
         # get different ones, a layer always the same one, so a buffer is written again six exchanges later
-        att, o, eo = shared
+        att, o, eo, lg = shared
         self.kv_sharded = sharding.HeadShardedKVCache(self.cache, cfg.q_heads, total_kv_heads=cfg.kv_heads, segment=segment,
                                                       dtype=dtype, buffers=(att, att))
         self.o_sharded = sharding.ShardedVQLinear(self.o, segment=segment, max_batch=batch, dtype=dtype, buffers=(o, o))
         e0, e1 = sharding.split_range(cfg.experts, world, rank)
         self.moe = VQMoE(w.moe, (e0, e1))
-        self.moe_ep = sharding.ExpertParallelMoE(self.moe, segment=segment, max_tokens=batch, top_k=cfg.top_k, buffers=(eo, eo))
+        self.moe_ep = sharding.ExpertParallelMoE(self.moe, segment=segment, max_tokens=batch, top_k=cfg.top_k, buffers=(eo, eo),
+                                                 logits_buffers=(lg, lg))
         self.moe.reserve(batch, cfg.top_k)
 
 
@@ -154,7 +155,8 @@ class VQDecoderStack:
         shared = [None, None]
         if segment is not None:      # two sets of exchange buffers, for even and odd layers
             shared = [(segment.alloc((batch, cfg.q_heads, cfg.head_dim), dtype), segment.alloc((batch, cfg.hidden), dtype),
-                       segment.alloc((batch * cfg.top_k, cfg.hidden), torch.float32)) for _ in range(2)]
+                       segment.alloc((batch * cfg.top_k, cfg.hidden), torch.float32),
+                       segment.alloc((batch, cfg.experts), torch.float32)) for _ in range(2)]
         self.layers = [_Layer(weights.layers[i % n], cfg, batch, self.device, segment, dtype, shared[i & 1]) for i in range(cfg.layers)]
         if segment is not None:
             from . import sharding

@@ -183,9 +183,17 @@ class ShardedVQLinear:
 class ExpertParallelMoE:
     """Expert-parallel MoE: ``moe`` is an ``ops.VQMoE`` built with ``expert_range=split_range(E, world, rank)``."""
 
-    def __init__(self, moe, group=None, segment: "PeerSegment" = None, max_tokens: int = 1, top_k: int = 10, buffers=None):
+    def __init__(self, moe, group=None, segment: "PeerSegment" = None, max_tokens: int = 1, top_k: int = 10, buffers=None,
+                 logits_buffers=None, shard_router: bool = True):
+        """``shard_router``: every rank scores only its own experts and the logits are exchanged too (``logits_buffers``:
+        two ``[max_tokens, experts]`` tensors from the segment to use instead of allocating a pair)."""
         self.moe, self.group, self.segment = moe, group, segment
         self._turn = 0
+        self._lg = None
+        self.shard_router_min_tokens = 64
+        if segment is not None and shard_router and moe.has_router:
+            self._lg = list(logits_buffers) if logits_buffers is not None else \
+                [segment.alloc((max_tokens, moe.num_experts_total), torch.float32) for _ in range(2)]
         if segment is not None:     # per-pair expert outputs of every rank, two buffers used in turn
             self._eo = list(buffers) if buffers is not None else \
                 [segment.alloc((max_tokens * top_k, moe.hidden), torch.float32) for _ in range(2)]
@@ -224,8 +232,11 @@ class ExpertParallelMoE:
             from ._lib import lib
             n = x.reshape(-1, self.moe.hidden).shape[0]
             assert n * top_k <= self._eo[0].shape[0]
+            # the logits exchange costs about ten microseconds of signalling: it pays once scoring all experts on every
+            # rank takes longer than that (measured: from a few dozen tokens)
+            lg = self._lg[self._turn].data_ptr() if (self._lg is not None and n >= self.shard_router_min_tokens) else None
             return self._gathered(x, lambda x2, y, eo, dt, st: lib().ojasx_b200_moe_forward_routed_gather(
-                self.moe.handle, x2.data_ptr(), y.data_ptr(), n, top_k, dt, self.segment.link, eo.data_ptr(), st))
+                self.moe.handle, x2.data_ptr(), y.data_ptr(), n, top_k, dt, self.segment.link, eo.data_ptr(), lg, st))
         idx, wts = self.moe.route(x, top_k)   # router weights are replicated: same routing on every rank
         return self.forward(x, idx, wts)
 

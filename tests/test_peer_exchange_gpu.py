@@ -46,6 +46,9 @@ def _worker(rank, world, port, ret):
         idx, wts = whole.route(xm, 4)
         want_m = whole.forward(xm, idx, wts)
         out["moe"] = bool(torch.equal(ep.forward(xm, idx, wts), want_m)) and bool(torch.equal(ep.forward_routed(xm, 4), want_m))
+        ep.shard_router_min_tokens = 1       # every rank scores its own experts only; the logits are exchanged as well
+        out["moe"] = out["moe"] and bool(torch.equal(ep.forward_routed(xm, 4), want_m))
+        ep.shard_router_min_tokens = 64
         out["moe_b1"] = bool(torch.equal(ep.forward_routed(xm[:1], 4), whole.forward_routed(xm[:1], 4)))
         os.environ["OJASX_B200_MOE_FUSED_MIN_PAIRS"] = "1"      # the whole-expert kernel takes the same route
         out["moe_fused"] = bool(torch.equal(ep.forward(xm, idx, wts), whole.forward(xm, idx, wts)))
