@@ -49,8 +49,9 @@ METRIC = "vq_lut_gemv_2560x6912_hbm_gbs"
 # DRAM bytes (read + write) of one 2560->6912 layer inside lut_linear_kernel<8>, from an ncu capture of a
 # 148-layer launch of this kernel (dram__bytes_read.sum + dram__bytes_write.sum over the launch / 148); every
 # layer of a launch does the same work, so a launch's traffic is this figure times its layer count.
-TRAFFIC_PER_LAYER = 4142938
-TRAFFIC_SOURCE = "ncu capture of lut_linear_kernel<8>, 148 layers per launch; kernel unchanged since"
+TRAFFIC_PER_LAYER = 4099592
+TRAFFIC_SOURCE = ("ncu capture of lut_linear_kernel<8> as benched (the kernel with the peer-link argument), 148 layers per launch: "
+                  "606,141,696 B read + 598,016 B written; profiles/lut_linear_kernel_gemv_2560x6912.md")
 
 
 def env_int(name, default):
@@ -763,6 +764,8 @@ def bench_stack(args, E):
                                   dtype=torch.bfloat16 if args.stack_dtype == "bf16" else torch.float32)
         stack.gather_logits = False
         ids = torch.randint(0, cfg.vocab, (B, args.stack_prompt), device=E.dev, generator=torch.Generator(device=E.dev).manual_seed(3))
+        stack.prefill(ids)          # untimed: first use of every kernel at these shapes, scratch growth, graph capture
+        stack.reset()
         E.barrier()
         t0 = time.perf_counter()
         logits = stack.prefill(ids)
