@@ -118,7 +118,8 @@ OJASX_API int ojasx_b200_linear_forward_tensor(OjasxLinearHandle handle, const v
 /* Device-side error flags raised since the last call (the outputs of the launch that raised one are
  * invalid), 0 if none; synchronises the device.  Bit 0: a tensor-core launch gave up on a bounded
  * barrier wait.  Bit 1: the batched MoE expert kernel found its shared memory at an unexpected address
- * and did nothing.  Bit 2: a bounded wait for a bulk copy of a lookup table ran out.  Negative = CUDA error. */
+ * and did nothing.  Bit 2: a bounded wait for a bulk copy of a lookup table ran out, or a whole-expert
+ * MoE kernel of the chain walk found the same placement and did nothing.  Negative = CUDA error. */
 OJASX_API int ojasx_b200_take_device_error(void);
 
 /* Same computation on borrowed device arrays, no handle: the device twin of

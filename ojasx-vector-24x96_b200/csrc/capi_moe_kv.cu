@@ -29,8 +29,8 @@ int MoeHandle::reserve(int n_tokens, int k) {
     const size_t need = sizeof(float) * pairs * ((size_t)I + H) + sizeof(int) * (5 * pairs + 8);   // + work lists
     int rc = ensure_capacity(&scratch, &scratch_cap, need);
     if (rc != OJX_OK) return rc;
-    // Token tables [n_tokens, G, 256] fp32, shared by the k experts of a token (up to 1 GiB).
-    const size_t lut_need = sizeof(float) * (size_t)n_tokens * (H / D) * 256;
+    // Token tables, shared by the k experts of a token (up to 1 GiB), in whichever layout the forward picks.
+    const size_t lut_need = moe_table_bytes(n_tokens, H / D, D);
     if (lut_need <= ((size_t)1 << 30)) {
         if ((rc = ensure_capacity(&lut_scratch, &lut_cap, lut_need)) != OJX_OK) return rc;
     }
@@ -48,7 +48,7 @@ MoeProblem MoeHandle::problem(const void* x, void* y, const int* idx, const floa
     P.dn_codes = dn_codes; P.dn_scales = dn_scales;
     P.gu_csr = CsrView{csr_rp[0], csr_cols[0], csr_vals[0], csr_nnz[0]};
     P.dn_csr = CsrView{csr_rp[1], csr_cols[1], csr_vals[1], csr_nnz[1]};
-    const size_t lut_need = sizeof(float) * (size_t)n_tokens * (H / D) * 256;
+    const size_t lut_need = moe_table_bytes(n_tokens, H / D, D);
     P.lut_in = (lut_scratch && lut_cap >= lut_need) ? static_cast<const float*>(lut_scratch) : nullptr;
     P.inter = static_cast<float*>(scratch);
     P.expert_out = P.inter + (size_t)n_tokens * k * I;
@@ -226,7 +226,7 @@ int ojasx_b200_moe_forward_routed_gather(OjasxMoEHandle handle, const void* d_x,
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     MoeProblem P = h->problem(d_x, d_y, idx, w, n_tokens, top_k, io_dtype);
     P.expert_out = d_expert_out_shared;
-    P.lut_blocks = moe_fused_wanted(P) ? 1 : 0;
+    P.lut_blocks = moe_table_layout(P);
     // with a shared logits buffer every rank scores only the experts it holds (an exchange of its own on the link)
     rc = launch_moe_router(h->router, d_x, io_dtype, n_tokens, h->H, h->E_total, top_k, d_logits_shared ? d_logits_shared : logits,
                            probs, idx, w, s, P.cb_in, P.Kcb, P.D, const_cast<float*>(P.lut_in), P.lut_blocks,
@@ -264,7 +264,7 @@ int ojasx_b200_moe_forward_routed(OjasxMoEHandle handle, const void* d_x, void* 
     float* w = reinterpret_cast<float*>(idx + (size_t)n_tokens * top_k);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     MoeProblem P = h->problem(d_x, d_y, idx, w, n_tokens, top_k, io_dtype);
-    P.lut_blocks = moe_fused_wanted(P) ? 1 : 0;
+    P.lut_blocks = moe_table_layout(P);
     rc = launch_moe_router(h->router, d_x, io_dtype, n_tokens, h->H, h->E_total, top_k, logits, probs, idx, w, s,
                            P.cb_in, P.Kcb, P.D, const_cast<float*>(P.lut_in), P.lut_blocks);
     if (rc != OJX_OK) return rc;

@@ -47,6 +47,10 @@ int launch_moe_router(const float* Wr, const void* x, int io_dtype, int n_tokens
                       int lut_blocks = 0, const PeerLink* link = nullptr, int e_begin = 0, int e_end = 0);
 
 // --- moe_fused.cu: whole-expert work items (gate/up, SiLU gate and down fused) for batches of tokens
+bool moe_chain_wanted(const MoeProblem& P);   // gate/up by the chain walk: whole experts per work item and a fitting shape
+int moe_table_layout(const MoeProblem& P);    // MoeProblem::lut_blocks this forward wants
+size_t moe_table_bytes(int n_tokens, int G, int D);   // table scratch that fits every layout
+int launch_moe_chain_images(const void* x, int io_dtype, int n_tokens, int H, int D, const float* cb, int Kcb, float* out, cudaStream_t s);
 bool moe_fused_wanted(const MoeProblem& P);   // shape fits and enough routed pairs are expected here
 int launch_moe_fused(MoeProblem P, cudaStream_t stream, const PeerLink* link = nullptr);   // work list, token tables (unless lut_ready), experts
 int launch_moe_prebuild_blocks(const void* x, int io_dtype, int n_tokens, int H, int D, const float* codebook, int Kcb,

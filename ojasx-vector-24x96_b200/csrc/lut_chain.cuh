@@ -386,22 +386,26 @@ struct ChainWalker {
     static constexpr int kEpiProducts = 1536;   // products per pass of a warp: (128 KB - 32 KB of x) / 16 warps
     static constexpr int kEpiUnroll = 16;
     __device__ __forceinline__ float* epilogue_x() const { return table(); }
+    // `rp_all`: the work item's row pointers (local row r at rp_all[r], n + 1 of them) already in shared memory, or null.
     template <class Store>
     __device__ __forceinline__ void warp_epilogue(const CsrView& csr, int row0, const float* __restrict__ scales,
                                                   const float* __restrict__ bias, const float* xsm, const XLoad& xl,
-                                                  Store store) const {
+                                                  Store store, const int* rp_all = nullptr) const {
         const int per = ((n + kWarps - 1) / kWarps + 3) & ~3;
         const int rb = min(n, warp * per);
         const int nu = min(n, rb + per) - rb;
         if (nu <= 0) return;
         const bool has = csr.nnz > 0;
         const uint32_t ring = warp < kChLoWarps ? kChRingLo + warp * kChRingBytes : kChRingHi + (warp - kChLoWarps) * kChRingBytes;
-        int* rpw = at<int>(ring);                                   // nu + 1 <= 433 row pointers
+        const int* rpw = rp_all ? rp_all + rb : at<int>(ring);       // nu + 1 <= 433 row pointers
         float* prod = table() + kCsrXFloats + warp * kEpiProducts;
         const float* accw = acc() + rb;
         if (has) {
-            for (int i = lane; i <= nu; i += 32) rpw[i] = csr.row_ptrs[row0 + rb + i];
-            __syncwarp();
+            if (!rp_all) {
+                int* w = at<int>(ring);
+                for (int i = lane; i <= nu; i += 32) w[i] = csr.row_ptrs[row0 + rb + i];
+                __syncwarp();
+            }
             // ask for all of the warp's entries at once (a 128-byte line per lane and step), so that the loads
             // below find them on their way or in L2 instead of paying a DRAM round trip per batch
             for (int j = (rpw[0] & ~31) + lane * 32; j < rpw[nu]; j += 32 * 32) {
@@ -411,9 +415,14 @@ struct ChainWalker {
         }
         for (int q0 = 0; q0 < nu; q0 += kEpiRows) {
             const int R = min(kEpiRows, nu - q0);
-            float osum[kEpiRows / 32];
+            float osum[kEpiRows / 32], sc[kEpiRows / 32], bs[kEpiRows / 32];
 #pragma unroll
-            for (int i = 0; i < kEpiRows / 32; ++i) osum[i] = 0.0f;
+            for (int i = 0; i < kEpiRows / 32; ++i) {   // scale and bias of the rows: asked for now, used after the outlier sums
+                const int row = q0 + lane + 32 * i;
+                osum[i] = 0.0f;
+                sc[i] = (scales && row < q0 + R) ? scales[row0 + rb + row] : 1.0f;
+                bs[i] = (bias && row < q0 + R) ? bias[row0 + rb + row] : 0.0f;
+            }
             if (has) {
                 const int jb = rpw[q0], je = rpw[q0 + R];
                 for (int jc = jb; jc < je; jc += kEpiProducts) {
@@ -454,13 +463,36 @@ struct ChainWalker {
                 if (row < q0 + R) {
                     const int m = row0 + rb + row;
                     float res = accw[row];
-                    if (scales) res = __fmul_rn(res, scales[m]);
-                    if (bias) res = __fadd_rn(res, bias[m]);
+                    if (scales) res = __fmul_rn(res, sc[i]);
+                    if (bias) res = __fadd_rn(res, bs[i]);
                     if (has) res = __fadd_rn(res, osum[i]);
                     store(m, res);
                 }
             }
         }
+    }
+
+    // The same with table slices that were built beforehand (unlike run(), this form ends with a __syncthreads()): `images` holds, for every slice, the 128 KB image of the
+    // table area (the layout above, a slice of at most 64 groups stored twice), so a slice is brought in by ONE bulk copy
+    // of the copy engine instead of being computed.  `before_last` runs once the last slice's table is in.  The mbarrier sits in the activation area, which this form does
+    // not use.
+    static constexpr int kImageFloats = kSliceGroups * 256;
+    template <class F>
+    __device__ void run_prebuilt(const float* __restrict__ images, F before_last) const {
+        void* bar = at<void>(kChXs);
+        if (threadIdx.x == 0) bulk_bar_init(bar);
+        for (int s = 0; s < nslices; ++s) {
+            const int g0 = s * SG, ng = min(SG, G - g0);
+            __syncthreads();  // every warp has left the previous slice's table; the barrier is initialised
+            prefetch(s, ng);
+            if (threadIdx.x == 0) bulk_copy_issue(bar, table(), images + (size_t)s * kImageFloats, (unsigned)(kImageFloats * sizeof(float)));
+            bulk_copy_wait(bar, (unsigned)(s & 1));
+            if (s == nslices - 1) before_last();
+            if (s == 0) walk<true>(s, ng);
+            else walk<false>(s, ng);
+        }
+        __syncthreads();   // walks over (the caller needs this barrier too); the barrier is set up afresh by the next call
+        if (threadIdx.x == 0) bulk_bar_inval(bar);
     }
 
     // Leaves acc()[lr] = sum_{g<G} LUT_x[g, code[lr, g]] for lr < n.  All threads of the CTA must call it; on

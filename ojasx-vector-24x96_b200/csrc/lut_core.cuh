@@ -85,6 +85,11 @@ __device__ __forceinline__ void bulk_bar_init(void* bar) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(a) : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
+// One thread, after a barrier that follows the last wait: the location may be initialised again afterwards.
+__device__ __forceinline__ void bulk_bar_inval(void* bar) {
+    const unsigned a = static_cast<unsigned>(__cvta_generic_to_shared(bar));
+    asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(a) : "memory");
+}
 // One thread: global [src, src + bytes) -> shared dst; src, dst and bytes are multiples of 16, bytes < 1 MiB.
 __device__ __forceinline__ void bulk_copy_issue(void* bar, void* dst, const void* src, unsigned bytes) {
     const unsigned b = static_cast<unsigned>(__cvta_generic_to_shared(bar));
@@ -306,6 +311,10 @@ struct RowWalker {
             }
         }
         cp_async_wait<0>();
+        if (prebuilt) {   // the barrier is set up afresh by the next call
+            __syncthreads();
+            if (threadIdx.x == 0) bulk_bar_inval(sm.xs);
+        }
     }
 };
 

@@ -11,7 +11,9 @@
 //   combine  : y[t] = sum over the token's pairs in caller order of expert_out * weight
 // The combine is a separate ordered pass so that the sum over experts has the reference's
 // order whatever SM finished first.
+#include <cstdlib>
 #include "lut_core.cuh"
+#include "lut_chain.cuh"
 #include "launch.h"
 #include "handles.h"
 #include "peer.cuh"
@@ -132,6 +134,198 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) moe_down_kernel(const __
         __syncthreads();
     }
     peer_signal_when_last(link, gridDim.x);
+}
+
+// ---- gate/up with the lanes of a warp sharing a row (ChainWalker), for batches where a work item is a whole expert
+// (2I rows, gate rows then up rows, contiguous in the code matrix) of one token.  The token's table slices come as
+// ready-made images of the table area (moe_chain_prebuild_kernel) through one bulk copy per slice; every warp finishes
+// the rows it walked (scale, outlier rows) in place, then inter = silu(gate) * up.  Same bits as moe_gate_up_kernel.
+template <int D>
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) moe_gate_up_chain_kernel(const __grid_constant__ MoeProblem P) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int total = P.pair_list ? P.pair_list[0] : P.n_tokens * P.k_active;
+    const size_t esz = P.io_dtype == OJX_BF16 ? 2 : 4;
+    const int nslices = (P.G + ChainWalker<D>::SG - 1) / ChainWalker<D>::SG;
+    if (!ChainWalker<D>::usable(smem_raw, P.gu_codes, P.cb_in, P.G)) {   // checked on the host as far as it can be; the
+        if (threadIdx.x == 0) atomicExch(&g_bulk_copy_timeout, 2);      // shared-memory base only shows here
+        return;
+    }
+    for (int slot = blockIdx.x; slot < total; slot += gridDim.x) {
+        const int pair = P.pair_list ? P.pair_list[1 + slot] : slot;
+        const MoePair pr = decode_pair(P, pair);
+        if (pr.expert < 0) continue;  // uniform across the CTA
+        const int n = 2 * P.I;
+        const size_t row0 = (size_t)pr.expert * n;
+        const ChainWalker<D> cw(smem_raw, P.gu_codes + row0 * P.G, n, P.G);
+        const XLoad xl{static_cast<const char*>(P.x) + (size_t)pr.token * P.H * esz, P.H, P.io_dtype};
+        // Everything the epilogue reads from global memory is asked for while the row walk still hides the latency:
+        // the token's activations wait in registers, the expert's row pointers in the (idle) activation area behind
+        // the copy barrier, the outlier entries and the scales are asked into L2 under the last walk.
+        constexpr int kXr = kCsrXFloats / kThreads, kRpMax = kXsFloats - 4;
+        const bool has = P.gu_csr.nnz > 0;
+        const bool x_regs = has && P.H <= kCsrXFloats, rp_early = has && n + 1 <= kRpMax;
+        float xr[kXr];
+#pragma unroll
+        for (int q = 0; q < kXr; ++q) {
+            const int k = threadIdx.x + q * kThreads;
+            xr[q] = (x_regs && k < P.H) ? xl(k) : 0.0f;
+        }
+        int* rp_s = cw.template at<int>(kChXs) + 4;
+        int jb = 0, je = 0;
+        if (has) { jb = P.gu_csr.row_ptrs[row0]; je = P.gu_csr.row_ptrs[row0 + n]; }
+        if (rp_early) {
+            for (int b0 = threadIdx.x; b0 <= n; b0 += kThreads * 4) {
+                int v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) v[u] = b0 + u * kThreads <= n ? P.gu_csr.row_ptrs[row0 + b0 + u * kThreads] : 0;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) if (b0 + u * kThreads <= n) rp_s[b0 + u * kThreads] = v[u];
+            }
+        }
+        cw.run_prebuilt(P.lut_in + (size_t)pr.token * nslices * ChainWalker<D>::kImageFloats, [&]() {
+            for (int j = (jb & ~31) + threadIdx.x * 32; j < je; j += kThreads * 32) {
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(P.gu_csr.cols + j));
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(P.gu_csr.vals + j));
+            }
+            if (has && !rp_early)
+                for (int r = threadIdx.x * 32; r <= n; r += kThreads * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(P.gu_csr.row_ptrs + row0 + r));
+            if (P.gu_scales)
+                for (int r = threadIdx.x * 32; r < n; r += kThreads * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(P.gu_scales + row0 + r));
+        });   // ends with a barrier: the table area is scratch now
+        const float* xsm = nullptr;
+        if (x_regs) {
+            float* xw = cw.epilogue_x();
+#pragma unroll
+            for (int q = 0; q < kXr; ++q) {
+                const int k = threadIdx.x + q * kThreads;
+                if (k < P.H) xw[k] = xr[q];
+            }
+            __syncthreads();
+            xsm = xw;
+        }
+        float* acc = cw.acc();
+        cw.warp_epilogue(P.gu_csr, (int)row0, P.gu_scales, nullptr, xsm, xl, [&](int m, float res) { acc[m - (int)row0] = res; }, rp_early ? rp_s : nullptr);
+        __syncthreads();
+        for (int i = threadIdx.x; i < P.I; i += kThreads) {
+            float gate = acc[i], up = acc[P.I + i];
+            if (P.gate_limit > 0.0f) {
+                gate = fminf(gate, P.gate_limit);
+                up = fminf(fmaxf(up, -P.gate_limit), P.gate_limit);
+            }
+            P.inter[(size_t)pair * P.I + i] = __fmul_rn(silu_ref(gate), up);
+        }
+        __syncthreads();   // the sums are parked again by the next work item
+    }
+}
+
+// ---- down projection of a routed pair by the chain walk: the pair's table is built in the kernel from its
+// intermediate vector (it is the pair's own, so nothing can be shared), all H rows of the expert are one work item.
+// Same bits as moe_down_kernel.
+template <int D>
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) moe_down_chain_kernel(const __grid_constant__ MoeProblem P,
+                                                                              const __grid_constant__ PeerLink link) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int total = P.pair_list ? P.pair_list[0] : P.n_tokens * P.k_active;
+    const bool usable = ChainWalker<D>::usable(smem_raw, P.dn_codes, P.cb_down, P.Gi);
+    if (!usable && threadIdx.x == 0) atomicExch(&g_bulk_copy_timeout, 2);
+    for (int slot = blockIdx.x; usable && slot < total; slot += gridDim.x) {
+        const int pair = P.pair_list ? P.pair_list[1 + slot] : slot;
+        const MoePair pr = decode_pair(P, pair);
+        if (pr.expert < 0) continue;
+        const int n = P.H;
+        const size_t row0 = (size_t)pr.expert * n;
+        const ChainWalker<D> cw(smem_raw, P.dn_codes + row0 * P.Gi, n, P.Gi);
+        const XLoad xl{P.inter + (size_t)pair * P.I, P.I, OJX_F32};
+        // what the epilogue reads from global memory is asked for before the walk (see moe_gate_up_chain_kernel); the
+        // row pointers wait behind the parked sums
+        constexpr int kXr = 4;
+        const bool has = P.dn_csr.nnz > 0;
+        const int rp_off = (n + 3) & ~3;
+        const bool x_regs = has && P.I <= kXr * kThreads, rp_early = has && rp_off + n + 1 <= kAccRows;
+        float xr[kXr];
+#pragma unroll
+        for (int q = 0; q < kXr; ++q) {
+            const int k = threadIdx.x + q * kThreads;
+            xr[q] = (x_regs && k < P.I) ? xl(k) : 0.0f;
+        }
+        int* rp_s = reinterpret_cast<int*>(cw.acc() + rp_off);
+        int jb = 0, je = 0;
+        if (has) { jb = P.dn_csr.row_ptrs[row0]; je = P.dn_csr.row_ptrs[row0 + n]; }
+        if (rp_early) {
+            for (int b0 = threadIdx.x; b0 <= n; b0 += kThreads * 4) {
+                int v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) v[u] = b0 + u * kThreads <= n ? P.dn_csr.row_ptrs[row0 + b0 + u * kThreads] : 0;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) if (b0 + u * kThreads <= n) rp_s[b0 + u * kThreads] = v[u];
+            }
+        }
+        cw.run(xl, P.cb_down, P.Kcb, [&]() {
+            for (int j = (jb & ~31) + threadIdx.x * 32; j < je; j += kThreads * 32) {
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(P.dn_csr.cols + j));
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(P.dn_csr.vals + j));
+            }
+            if (has && !rp_early)
+                for (int r = threadIdx.x * 32; r <= n; r += kThreads * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(P.dn_csr.row_ptrs + row0 + r));
+            if (P.dn_scales)
+                for (int r = threadIdx.x * 32; r < n; r += kThreads * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(P.dn_scales + row0 + r));
+        });
+        __syncthreads();   // walks over: the table area is scratch now
+        const float* xsm = nullptr;
+        if (has && P.I <= kCsrXFloats) {
+            float* xw = cw.epilogue_x();
+            if (x_regs) {
+#pragma unroll
+                for (int q = 0; q < kXr; ++q) {
+                    const int k = threadIdx.x + q * kThreads;
+                    if (k < P.I) xw[k] = xr[q];
+                }
+            } else {
+                for (int k = threadIdx.x; k < P.I; k += kThreads) xw[k] = xl(k);
+            }
+            __syncthreads();
+            xsm = xw;
+        }
+        float* out = P.expert_out + (size_t)pair * P.H;
+        cw.warp_epilogue(P.dn_csr, (int)row0, P.dn_scales, nullptr, xsm, xl,
+                         [&](int m, float res) { peer_store(link, out + (m - (int)row0), res); },   // expert-parallel: every rank gets the pair's output
+                         rp_early ? rp_s : nullptr);
+        __syncthreads();   // the next work item parks row pointers and sums again
+    }
+    peer_signal_when_last(link, gridDim.x);
+}
+
+// Table slices of one activation vector as images of the chain walk's table area: image[s][h][k][jl][l] =
+// <x[group s*SG + 4*l' + 2*h + jl], cb[k]> with l' = l, or l & 15 when the slice has at most 64 groups (stored twice).
+// Arithmetic of RowWalker::build_slice (d ascending, separate multiply and add).  grid = (slices, vectors), 256
+// threads: thread = (k half, h, jl, l); 32 lanes write 128 contiguous bytes per centroid.
+template <int D>
+__global__ void __launch_bounds__(256) moe_chain_prebuild_kernel(const void* __restrict__ x, int io_dtype, int K, int G,
+                                                                 const float* __restrict__ codebook, int Kcb,
+                                                                 float* __restrict__ out) {
+    constexpr int SG = ChainWalker<D>::SG;
+    __shared__ float cb_s[256 * D];
+    const int s = blockIdx.x, t = blockIdx.y, nsl = gridDim.x;
+    const int g0 = s * SG, ng = min(SG, G - g0);
+    const size_t esz = io_dtype == OJX_BF16 ? 2 : 4;
+    const XLoad xl{static_cast<const char*>(x) + (size_t)t * K * esz, K, io_dtype};
+    for (int i = threadIdx.x; i < 256 * D; i += 256) cb_s[i] = (i / D) < Kcb ? codebook[i] : 0.0f;
+    const int l = threadIdx.x & 31, jl = (threadIdx.x >> 5) & 1, h = (threadIdx.x >> 6) & 1, khalf = threadIdx.x >> 7;
+    const int lpos = ng <= 64 ? (l & 15) : l;
+    const int gl = 4 * lpos + 2 * h + jl;
+    const bool mine = gl < ng;
+    float xg[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) xg[d] = mine ? xl((g0 + gl) * D + d) : 0.0f;
+    __syncthreads();
+    float* img = out + ((size_t)t * nsl + s) * ChainWalker<D>::kImageFloats + (size_t)h * 16384 + jl * 32 + l;
+    for (int k = khalf * 128; k < khalf * 128 + 128; ++k) {
+        const float* c = cb_s + k * D;
+        float dot = __fmul_rn(xg[0], c[0]);
+#pragma unroll
+        for (int d = 1; d < D; ++d) dot = __fadd_rn(dot, __fmul_rn(xg[d], c[d]));
+        img[(size_t)k * 64] = (mine && k < Kcb) ? dot : 0.0f;
+    }
 }
 
 // Work list of one forward: the (token, expert) pairs this handle evaluates -- expert held here,
@@ -472,6 +666,54 @@ static int set_smem(K kern) {
 
 constexpr int kMoePlanMinPairs = 64;
 
+// Pairs this handle expects to evaluate: an expert-parallel shard sees its share of the routed pairs.
+static int expected_pairs(const MoeProblem& P) {
+    const int pairs = P.n_tokens * P.k_active;
+    return P.E_total > P.E ? (int)(((long long)pairs * P.E + P.E_total - 1) / P.E_total) : pairs;
+}
+
+// Gate/up by the chain walk (moe_gate_up_chain_kernel): a work item is a whole expert, which is the case once there
+// is at least one expected pair per resident CTA; the shape must fit the walker (16-byte pieces of code rows, all 2I
+// sums parked at once).  OJASX_B200_MOE_CHAIN=0 keeps the row-per-lane kernel (for comparisons).
+bool moe_chain_wanted(const MoeProblem& P) {
+    if (!P.lut_in || P.D > 16 || (P.G & 15) != 0 || 2 * P.I > kAccRows || 2 * P.I < 512) return false;
+    if (expected_pairs(P) < kCtasPerSm * num_sms()) return false;
+    const char* e = std::getenv("OJASX_B200_MOE_CHAIN");
+    return !(e && e[0] == '0');
+}
+
+static bool moe_chain_down_wanted(const MoeProblem& P) {
+    if (P.D > 16 || (P.Gi & 15) != 0 || P.H > kAccRows || P.H < 512) return false;
+    if (expected_pairs(P) < kCtasPerSm * num_sms()) return false;
+    const char* e = std::getenv("OJASX_B200_MOE_CHAIN");
+    return !(e && e[0] == '0');
+}
+
+size_t moe_table_bytes(int n_tokens, int G, int D) {
+    const size_t plain = (size_t)G * 1024;
+    const int sg = kXsFloats / D < kSliceGroups ? kXsFloats / D : kSliceGroups;
+    const size_t images = (size_t)((G + sg - 1) / sg) * kSliceGroups * 1024;
+    return (size_t)n_tokens * (plain > images ? plain : images);
+}
+
+template <int D>
+static int launch_chain_images(const void* x, int io_dtype, int n_tokens, int H, int G, const float* cb, int Kcb, float* out, cudaStream_t s) {
+    const int nsl = (G + ChainWalker<D>::SG - 1) / ChainWalker<D>::SG;
+    moe_chain_prebuild_kernel<D><<<dim3(nsl, n_tokens), 256, 0, s>>>(x, io_dtype, H, G, cb, Kcb, out);
+    OJX_CUDA_TRY(cudaGetLastError());
+    count_launch(1);
+    return OJX_OK;
+}
+int launch_moe_chain_images(const void* x, int io_dtype, int n_tokens, int H, int D, const float* cb, int Kcb, float* out, cudaStream_t s) {
+    if (!x || !cb || !out || H % D != 0) return OJX_ERR_ARG;
+    switch (D) {
+        case 4: return launch_chain_images<4>(x, io_dtype, n_tokens, H, H / D, cb, Kcb, out, s);
+        case 8: return launch_chain_images<8>(x, io_dtype, n_tokens, H, H / D, cb, Kcb, out, s);
+        case 16: return launch_chain_images<16>(x, io_dtype, n_tokens, H, H / D, cb, Kcb, out, s);
+        default: return OJX_ERR_UNSUPPORTED;
+    }
+}
+
 template <int D>
 static int launch_moe_experts_t(const MoeProblem& P, cudaStream_t s, const PeerLink& link) {
     int rc;
@@ -487,15 +729,35 @@ static int launch_moe_experts_t(const MoeProblem& P, cudaStream_t s, const PeerL
         OJX_CUDA_TRY(cudaGetLastError());
         ++extra;
     }
-    if (P.lut_in && !P.lut_ready) {
-        lut_prebuild_kernel<D><<<dim3((P.G + 15) / 16, P.n_tokens), 256, 0, s>>>(P.x, P.io_dtype, P.H, P.G, P.cb_in, P.Kcb,
-                                                                                const_cast<float*>(P.lut_in));
-        OJX_CUDA_TRY(cudaGetLastError());
-        ++extra;
+    if constexpr (D <= 16) {
+        if (P.lut_blocks == 2) {
+            if ((rc = set_smem(moe_gate_up_chain_kernel<D>)) != OJX_OK) return rc;
+            if (!P.lut_ready) {
+                if ((rc = launch_chain_images<D>(P.x, P.io_dtype, P.n_tokens, P.H, P.G, P.cb_in, P.Kcb, const_cast<float*>(P.lut_in), s)) != OJX_OK) return rc;
+            }
+            moe_gate_up_chain_kernel<D><<<pairs < sms ? pairs : sms, kThreads, sizeof(CoreSmem), s>>>(P);
+            OJX_CUDA_TRY(cudaGetLastError());
+        }
     }
-    moe_gate_up_kernel<D><<<gu_items < sms ? gu_items : sms, kThreads, sizeof(CoreSmem), s>>>(P);
-    OJX_CUDA_TRY(cudaGetLastError());
-    moe_down_kernel<D><<<dn_items < sms ? dn_items : sms, kThreads, sizeof(CoreSmem), s>>>(P, link);
+    if (P.lut_blocks != 2) {
+        if (P.lut_in && !P.lut_ready) {
+            lut_prebuild_kernel<D><<<dim3((P.G + 15) / 16, P.n_tokens), 256, 0, s>>>(P.x, P.io_dtype, P.H, P.G, P.cb_in, P.Kcb,
+                                                                                    const_cast<float*>(P.lut_in));
+            OJX_CUDA_TRY(cudaGetLastError());
+            ++extra;
+        }
+        moe_gate_up_kernel<D><<<gu_items < sms ? gu_items : sms, kThreads, sizeof(CoreSmem), s>>>(P);
+        OJX_CUDA_TRY(cudaGetLastError());
+    }
+    bool chain_down = false;
+    if constexpr (D <= 16) {
+        if (P.dn_tiles == 1 && moe_chain_down_wanted(P)) {
+            if ((rc = set_smem(moe_down_chain_kernel<D>)) != OJX_OK) return rc;
+            moe_down_chain_kernel<D><<<pairs < sms ? pairs : sms, kThreads, sizeof(CoreSmem), s>>>(P, link);
+            chain_down = true;
+        }
+    }
+    if (!chain_down) moe_down_kernel<D><<<dn_items < sms ? dn_items : sms, kThreads, sizeof(CoreSmem), s>>>(P, link);
     OJX_CUDA_TRY(cudaGetLastError());
     const int n = P.n_tokens * P.H;
     moe_combine_kernel<<<(n + 255) / 256, 256, 0, s>>>(P, link);
@@ -504,15 +766,20 @@ static int launch_moe_experts_t(const MoeProblem& P, cudaStream_t s, const PeerL
     return OJX_OK;
 }
 
+// Layout of the token tables this forward wants (MoeProblem::lut_blocks).
+int moe_table_layout(const MoeProblem& P) { return moe_fused_wanted(P) ? 1 : moe_chain_wanted(P) ? 2 : 0; }
+
 int launch_moe_experts(MoeProblem P, cudaStream_t s, const PeerLink* lk) {
     if (!P.x || !P.y || !P.topk_idx || !P.topk_w || !P.inter || !P.expert_out) return OJX_ERR_ARG;
     if (P.n_tokens <= 0 || P.k_active <= 0) return OJX_ERR_ARG;
     const PeerLink none{};
     const PeerLink& link = lk ? *lk : none;
     P.combine_all = link.n > 0 ? 1 : 0;
-    // Batches: whole-expert work items, gate/up and down fused (moe_fused.cu); then the ordered combine.
-    if (moe_fused_wanted(P)) {
-        if (P.lut_ready && !P.lut_blocks) P.lut_ready = 0;   // tables were built in the other layout: rebuild
+    const int layout = moe_table_layout(P);
+    if (P.lut_ready && P.lut_blocks != layout) P.lut_ready = 0;   // tables were built in another layout: rebuild
+    P.lut_blocks = layout;
+    // Whole-expert work items with gate/up and down fused (moe_fused.cu, opt-in); then the ordered combine.
+    if (layout == 1) {
         const int rc = launch_moe_fused(P, s, lk);
         if (rc != OJX_ERR_UNSUPPORTED) {
             if (rc != OJX_OK) return rc;
@@ -522,12 +789,12 @@ int launch_moe_experts(MoeProblem P, cudaStream_t s, const PeerLink* lk) {
             count_launch(1);
             return OJX_OK;
         }
+        P.lut_ready = 0;
+        P.lut_blocks = moe_chain_wanted(P) ? 2 : 0;
     }
-    if (P.lut_ready && P.lut_blocks) P.lut_ready = 0;
     const int pairs = P.n_tokens * P.k_active, sms = kCtasPerSm * num_sms();
-    // Tiles: spread few pairs over the SMs, keep tiles whole when there are many pairs.  An
-    // expert-parallel shard expects only its share of the routed pairs.
-    const int expect = P.E_total > P.E ? (int)(((long long)pairs * P.E + P.E_total - 1) / P.E_total) : pairs;
+    // Tiles: spread few pairs over the SMs, keep tiles whole when there are many pairs.
+    const int expect = expected_pairs(P);
     // A handful of pairs: the work list (grouping by expert, dropping the pairs of other shards) buys nothing, so its
     // kernel is left out and the pairs are visited in order (pairs of other shards are skipped on sight).
     if (pairs <= kMoePlanMinPairs) P.pair_list = nullptr;
@@ -585,8 +852,9 @@ int launch_moe_router(const float* Wr, const void* x, int io_dtype, int n_tokens
     const PeerLink& link = lk ? *lk : none;
     if (link.n <= 0) { e_begin = 0; e_end = E; }
     if (e_begin < 0 || e_end > E || e_begin > e_end) return OJX_ERR_ARG;
-    if (lut_out && lut_blocks) {   // tables in 16-group blocks for the fused expert kernel: a launch of their own
-        const int rc = launch_moe_prebuild_blocks(x, io_dtype, n_tokens, H, D, codebook, Kcb, lut_out, s);
+    if (lut_out && lut_blocks) {   // tables in a layout of one of the whole-expert kernels: a launch of their own
+        const int rc = lut_blocks == 2 ? launch_moe_chain_images(x, io_dtype, n_tokens, H, D, codebook, Kcb, lut_out, s)
+                                       : launch_moe_prebuild_blocks(x, io_dtype, n_tokens, H, D, codebook, Kcb, lut_out, s);
         if (rc != OJX_OK) return rc;
         lut_out = nullptr;
     }

@@ -167,3 +167,52 @@ def test_moe_config2_full_size_batch_256(cuda, oracle):
     # the same tokens one at a time take the small-batch kernels: both paths agree within the tolerance
     one = moe.forward_routed(xt[:4], 10).cpu().numpy()
     assert _close(one, want[:4])
+
+
+@pytest.mark.parametrize("H,I,D,E,k,B", [
+    (2560, 640, 8, 32, 10, 32),   # benchmark geometry: two full table slices and a 64-group one (two chains per warp)
+    (1536, 256, 8, 12, 6, 40),    # a 64-group tail after a full slice; 512 rows per expert (the smallest the walk takes)
+    (1024, 512, 16, 8, 4, 50),    # block_dim 16, one 64-group slice only
+    (768, 3456, 4, 3, 3, 64),     # block_dim 4; 6912 rows per expert (the most the walk parks); a 64-group tail
+])
+@pytest.mark.parametrize("frac", [0.0, 0.01])
+def test_moe_gate_up_chain_walk_equals_row_walk(cuda, oracle, monkeypatch, H, I, D, E, k, B, frac):
+    """From one expected pair per SM the gate/up pass walks a whole expert with 32 lanes per row over table images
+    brought in by bulk copies; OJASX_B200_MOE_CHAIN=0 keeps the lane-per-row kernel.  Same sums in the same order:
+    the outputs are equal bit for bit (and match the oracle), with outlier rows, skipped pairs, a gate clamp, the
+    router in front, and expert shards."""
+    w = synth.make_vq_moe(H + I, E, H, I, block_dim=D, outlier_frac=frac, unit_scales=(frac == 0.0))
+    rng = np.random.default_rng(E + B)
+    x = rng.standard_normal((B, H)).astype(np.float32)
+    idx = np.stack([rng.choice(E, size=k, replace=False) for _ in range(B)]).astype(np.int32)
+    wts = rng.uniform(0.02, 0.3, size=(B, k)).astype(np.float32)
+    idx[1, 0] = -1
+    idx[2, k - 1] = E
+    wts[0, 1] = 5e-9
+    args = (torch.from_numpy(x).to(cuda), torch.from_numpy(idx).to(cuda), torch.from_numpy(wts).to(cuda))
+    moe = ops.VQMoE(w)
+    n0 = ojasx_b200.launch_count()
+    chain = moe.forward(*args)
+    launches = ojasx_b200.launch_count() - n0
+    routed_chain = moe.forward_routed(args[0], k)
+    moe.set_gate_limit(0.05)
+    clamp_chain = moe.forward(*args)
+    moe.set_gate_limit(0.0)
+    assert ojasx_b200.lib().ojasx_b200_take_device_error() == 0
+    monkeypatch.setenv("OJASX_B200_MOE_CHAIN", "0")
+    row = moe.forward(*args)
+    routed_row = moe.forward_routed(args[0], k)
+    moe.set_gate_limit(0.05)
+    clamp_row = moe.forward(*args)
+    moe.set_gate_limit(0.0)
+    monkeypatch.delenv("OJASX_B200_MOE_CHAIN")
+    assert launches == 5                      # work list, table images, gate/up, down, combine
+    assert torch.equal(chain, row) and torch.equal(routed_chain, routed_row) and torch.equal(clamp_chain, clamp_row)
+    assert not torch.equal(clamp_chain, chain)
+    sample = [0, 1, 2, B - 1]
+    want = _oracle_moe(oracle, w, x[sample], idx[sample], wts[sample])
+    assert _close(chain.cpu().numpy()[sample], want)
+    if E % 2 == 0 and B * k // 2 >= 148 * 2:   # both shards still expect a pair per SM
+        lo, hi = ops.VQMoE(w, (0, E // 2)), ops.VQMoE(w, (E // 2, E))
+        ys = lo.forward(*args) + hi.forward(*args)
+        assert np.allclose(ys.cpu().numpy(), chain.cpu().numpy(), rtol=1e-5, atol=1e-6)
