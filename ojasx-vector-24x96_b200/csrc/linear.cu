@@ -74,8 +74,23 @@ lut_linear_kernel(const LinearProblem* __restrict__ probs, int nprobs, int total
         // (Asking L2 for the outlier arrays ahead of the epilogue was measured and costs 5 %: with the code stream
         // running close to the DRAM limit the lines are gone again before they are used.)
         auto ask_l2 = [&]() {};
+        // With the shared-row walk every warp streams the outlier entries of its own rows in the epilogue; where they
+        // begin and end is read under the last walk.
+        int jbw = 0, jew = 0;
+        bool stream = false;
         if constexpr (D <= 16) {
-            if (chain) ChainWalker<D>(smem_raw, rs.base0, n, P.G).run(xl, P.codebook, P.Kcb, ask_l2);
+            if (chain) {
+                const ChainWalker<D> cw(smem_raw, rs.base0, n, P.G);
+                stream = P.csr.nnz > 0 && P.K <= kCsrXFloats && ChainWalker<D>::stream_ok(P.csr);
+                auto entry_range = [&]() {
+                    if (stream && cw.warp_row_count() > 0) {
+                        jbw = P.csr.row_ptrs[r0 + cw.warp_first_row()];
+                        jew = P.csr.row_ptrs[r0 + cw.warp_first_row() + cw.warp_row_count()];
+                    }
+                };
+                cw.run(xl, P.codebook, P.Kcb, entry_range);
+                if (cw.nslices == 0) entry_range();
+            }
             else RowWalker<D>(sm, rs).run(xl, P.codebook, P.Kcb, ask_l2);
         } else {
             RowWalker<D>(sm, rs).run(xl, P.codebook, P.Kcb, ask_l2);
@@ -101,7 +116,8 @@ lut_linear_kernel(const LinearProblem* __restrict__ probs, int nprobs, int total
                     __syncthreads();
                     xsm = xw;
                 }
-                cw.warp_epilogue(P.csr, r0, P.scales, P.bias, xsm, xl, store_y);
+                if (stream) cw.warp_epilogue_stream(P.csr, r0, P.scales, P.bias, xsm, jbw, jew, store_y);
+                else cw.warp_epilogue(P.csr, r0, P.scales, P.bias, xsm, xl, store_y);
                 continue;
             }
         }

@@ -472,6 +472,139 @@ struct ChainWalker {
         }
     }
 
+    // The same epilogue with the outlier entries streamed in by the copy engine.  Per-thread loads keep too few bytes
+    // in flight for the (col, val) arrays (about 18 bytes per clock and SM); here every warp brings its own entries
+    // into its part of the table area in chunks of kStreamChunk entries, two chunks in flight per warp (96 KB per SM),
+    // and walks its rows in order as the chunks land: products in place, then one lane per row adds a row's products
+    // in entry order.  A row whose entries end inside the chunk is finished and stored; the one row that straddles
+    // the end of a chunk carries its partial sum into the next chunk (same additions in the same order).  Scale and
+    // bias are applied to the parked sums beforehand, so finishing a row is one addition.
+    // `jbw`, `jew`: row_ptrs of the warp's first row and of the row after its last one (read before the walk, so no
+    // round trip is left in front of the first copy).  Needs x in shared memory and 16-byte aligned (col, val) arrays.
+    static constexpr int kStreamChunk = kEpiProducts / 4;   // entries; a buffer is cols[kStreamChunk] | vals[kStreamChunk]
+    __device__ __forceinline__ int warp_first_row() const { return min(n, warp * (((n + kWarps - 1) / kWarps + 3) & ~3)); }
+    __device__ __forceinline__ int warp_row_count() const {
+        const int per = ((n + kWarps - 1) / kWarps + 3) & ~3;
+        return min(n, warp_first_row() + per) - warp_first_row();
+    }
+    __device__ static __forceinline__ bool stream_ok(const CsrView& csr) {
+        return ((reinterpret_cast<uintptr_t>(csr.cols) | reinterpret_cast<uintptr_t>(csr.vals)) & 15) == 0;
+    }
+    template <class Store>
+    __device__ __forceinline__ void warp_epilogue_stream(const CsrView& csr, int row0, const float* __restrict__ scales,
+                                                         const float* __restrict__ bias, const float* xsm, int jbw, int jew,
+                                                         Store store) const {
+        const int rb = warp_first_row(), nu = warp_row_count();
+        if (nu <= 0) return;
+        constexpr int CH = kStreamChunk;
+        const uint32_t ring = warp < kChLoWarps ? kChRingLo + warp * kChRingBytes : kChRingHi + (warp - kChLoWarps) * kChRingBytes;
+        int* rpw = at<int>(ring);
+        float* accw = acc() + rb;
+        float* region = table() + kCsrXFloats + warp * kEpiProducts;
+        unsigned char* bars = at<unsigned char>(kChXs) + warp * 16;   // the activation area is idle until the next table build
+        const int jc0 = jbw & ~3;
+        const int nch = max(1, (jew - jc0 + CH - 1) / CH);
+        auto issue = [&](int c) {   // lane 0
+            const int jc = jc0 + c * CH;
+            int cnt = min(CH, (jew - jc + 3) & ~3);
+            cnt = max(0, min(cnt, (csr.nnz - jc) & ~3));   // never past the end of the arrays: the last entries come by plain loads
+            float* buf = region + (c & 1) * 2 * CH;
+            void* bar = bars + (c & 1) * 8;
+            bulk_expect(bar, (unsigned)cnt * 8u);
+            if (cnt > 0) {
+                bulk_copy_add(bar, buf, csr.cols + jc, (unsigned)cnt * 4u);
+                bulk_copy_add(bar, buf + CH, csr.vals + jc, (unsigned)cnt * 4u);
+            }
+        };
+        if (lane == 0) {
+            bulk_bar_init(bars);
+            bulk_bar_init(bars + 8);
+            issue(0);
+            if (nch > 1) issue(1);
+        }
+        // row pointers of the warp's rows into its idle code ring; scale and bias onto the parked sums
+        for (int i0 = lane; i0 <= nu; i0 += 32 * 8) {
+            int v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = i0 + 32 * u <= nu ? csr.row_ptrs[row0 + rb + i0 + 32 * u] : 0;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) if (i0 + 32 * u <= nu) rpw[i0 + 32 * u] = v[u];
+        }
+        if (scales || bias) {
+            for (int i0 = lane; i0 < nu; i0 += 32 * 8) {
+                float sc[8], bs[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int r = i0 + 32 * u;
+                    sc[u] = (scales && r < nu) ? scales[row0 + rb + r] : 1.0f;
+                    bs[u] = (bias && r < nu) ? bias[row0 + rb + r] : 0.0f;
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int r = i0 + 32 * u;
+                    if (r < nu) {
+                        float res = accw[r];
+                        if (scales) res = __fmul_rn(res, sc[u]);
+                        if (bias) res = __fadd_rn(res, bs[u]);
+                        accw[r] = res;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        int cur = 0;             // first row not finished yet
+        float carry = 0.0f;      // partial outlier sum of row `cur` when it began in an earlier chunk
+        bool has_carry = false;
+        for (int c = 0; c < nch; ++c) {
+            const int jc = jc0 + c * CH, ce = min(jc + CH, jew);
+            int* cols = reinterpret_cast<int*>(region + (c & 1) * 2 * CH);
+            float* vals = region + (c & 1) * 2 * CH + CH;
+            {   // entries the copy left out because the arrays end inside their 16-byte piece
+                const int got = max(0, min(min(CH, (jew - jc + 3) & ~3), (csr.nnz - jc) & ~3));
+                const int j = jc + got + lane;
+                if (lane < 4 && j < ce) {
+                    cols[got + lane] = csr.cols[j];
+                    vals[got + lane] = csr.vals[j];
+                }
+            }
+            bulk_copy_wait(bars + (c & 1) * 8, (unsigned)((c >> 1) & 1));
+            __syncwarp();
+            const int m = ce - jc;
+#pragma unroll 4
+            for (int i = lane; i < m; i += 32) vals[i] = __fmul_rn(vals[i], xsm[cols[i]]);
+            __syncwarp();
+            for (;;) {
+                const int r = cur + lane;
+                const bool complete = r < nu && rpw[r + 1] <= ce;
+                const int cnt = __popc(__ballot_sync(0xffffffffu, complete));
+                if (complete) {
+                    float a = (lane == 0 && has_carry) ? carry : 0.0f;
+                    for (int j = max(rpw[r], jc); j < rpw[r + 1]; ++j) a = __fadd_rn(a, vals[j - jc]);
+                    store(row0 + rb + r, __fadd_rn(accw[r], a));
+                }
+                if (cnt == 32) {
+                    cur += 32;
+                    has_carry = false;
+                    continue;
+                }
+                float a = (cnt == 0 && has_carry) ? carry : 0.0f;
+                if (lane == cnt && r < nu)
+                    for (int j = max(rpw[r], jc); j < ce; ++j) a = __fadd_rn(a, vals[j - jc]);
+                carry = __shfl_sync(0xffffffffu, a, cnt);
+                has_carry = true;
+                cur += cnt;
+                break;
+            }
+            __syncwarp();
+            if (lane == 0 && c + 2 < nch) issue(c + 2);
+        }
+        __syncwarp();
+        if (lane == 0) {
+            bulk_bar_inval(bars);
+            bulk_bar_inval(bars + 8);
+        }
+    }
+
     // The same with table slices that were built beforehand (unlike run(), this form ends with a __syncthreads()): `images` holds, for every slice, the 128 KB image of the
     // table area (the layout above, a slice of at most 64 groups stored twice), so a slice is brought in by ONE bulk copy
     // of the copy engine instead of being computed.  `before_last` runs once the last slice's table is in.  The mbarrier sits in the activation area, which this form does

@@ -100,6 +100,20 @@ __device__ __forceinline__ void bulk_copy_issue(void* bar, void* dst, const void
                  "r"(bytes), "r"(b)
                  : "memory");
 }
+// The two halves of bulk_copy_issue, for several copies that complete one phase of a barrier: one bulk_expect with
+// the sum of their sizes (zero completes the phase at once), then a bulk_copy_add per copy.
+__device__ __forceinline__ void bulk_expect(void* bar, unsigned bytes) {
+    const unsigned b = static_cast<unsigned>(__cvta_generic_to_shared(bar));
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // earlier generic accesses to the destinations come first
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_copy_add(void* bar, void* dst, const void* src, unsigned bytes) {
+    const unsigned b = static_cast<unsigned>(__cvta_generic_to_shared(bar));
+    const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(dst));
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(d), "l"(src),
+                 "r"(bytes), "r"(b)
+                 : "memory");
+}
 __device__ __forceinline__ bool bulk_copy_wait(void* bar, unsigned parity) {
     const unsigned b = static_cast<unsigned>(__cvta_generic_to_shared(bar));
     for (int i = 0; i < kBulkSpin; ++i) {

@@ -137,6 +137,49 @@ def test_grouped_layers_walk_variants(cuda, oracle, monkeypatch, K, M, D, kcb, d
         assert np.array_equal(got, want), (walk, np.abs(got - want).max())
 
 
+def test_grouped_layers_streamed_outlier_layouts(cuda, oracle):
+    """Outlier layouts against the streamed epilogue of the shared-row walk (every warp brings the entries of its
+    own rows in 384-entry chunks): rows longer than several chunks, warps without entries, empty rows at chunk
+    ends, entry counts that are not multiples of four (the last piece of the arrays comes by plain loads), repeated
+    columns; with and without scale and bias.  Bit-exact (entry order of ojasx_lut_cpu.cpp:117-126)."""
+    K, M, D, P = 2560, 1000, 8, 150
+    rng = np.random.default_rng(9)
+
+    def csr_of(rows):
+        rp = np.zeros(M + 1, np.int32)
+        cols, vals = [], []
+        for i in range(M):
+            c, v = rows.get(i, ([], []))
+            cols += list(c)
+            vals += list(v)
+            rp[i + 1] = len(cols)
+        return rp, np.asarray(cols, np.int32), np.asarray(vals, np.float32)
+
+    def run(n):
+        return rng.integers(0, K, n), rng.standard_normal(n).astype(np.float32)
+
+    layouts = [
+        {0: run(1)},                                                            # one entry in the first row
+        {M - 1: run(2)},                                                        # two entries in the last row
+        {5: run(2001), 6: run(1), 70: run(383), 71: run(385), 500: run(1535), 999: run(7)},   # long rows, odd totals
+        {i: run(int(rng.integers(0, 4))) for i in range(0, M, 3)},              # many empty rows
+        {i: run(384) for i in range(64, 128)},                                  # every row of one warp is exactly a chunk
+        {i: (np.full(5, 11), np.arange(5, dtype=np.float32)) for i in range(M)},  # repeated column everywhere
+    ]
+    for li, rows in enumerate(layouts):
+        for full in (False, True):
+            w = synth.make_vq_linear(700 + li, K, M, block_dim=D, outlier_frac=0, with_scales=full, with_bias=full)
+            csr = csr_of(rows)
+            layer = ops.VQLinear(w.codebook, w.codes, w.scales, w.bias, csr, block_dim=D)
+            group = ops.VQLinearGroup([layer] * P)
+            x = rng.standard_normal((P, K)).astype(np.float32)
+            y = torch.zeros((P, M), device=cuda)
+            group.forward(torch.from_numpy(x).to(cuda), y)
+            want = oracle.linear_forward(w.codebook, w.codes, w.scales, w.bias, csr, x, block_dim=D)
+            assert np.array_equal(y.cpu().numpy(), want), (li, full)
+    assert ojasx_b200.lib().ojasx_b200_take_device_error() == 0
+
+
 def test_linear_errors(cuda):
     w = synth.make_vq_linear(1, 64, 32, block_dim=16, outlier_frac=0)
     layer = ops.VQLinear.from_weights(w)
