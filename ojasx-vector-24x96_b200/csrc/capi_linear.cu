@@ -89,7 +89,7 @@ DeviceGuard::~DeviceGuard() { if (prev_ >= 0) cudaSetDevice(prev_); }
 LinearHandle::~LinearHandle() {
     DeviceGuard g(dev);
     cudaFree(codes); cudaFree(codebook); cudaFree(scales); cudaFree(bias);
-    cudaFree(row_ptrs); cudaFree(cols); cudaFree(vals); cudaFree(d_x); cudaFree(d_y); cudaFree(dq_scratch);
+    cudaFree(row_ptrs); cudaFree(cols); cudaFree(vals); cudaFree(d_x); cudaFree(d_y);
     if (host_graph) cudaGraphExecDestroy(host_graph);
     if (pin_x) cudaFreeHost(pin_x);
     if (pin_y) cudaFreeHost(pin_y);
@@ -183,7 +183,7 @@ int ojasx_b200_linear_forward(OjasxLinearHandle handle, const void* d_x, void* d
     if (io_dtype == OJX_BF16 && dequant_gemm_supported(P, h->csr_sorted)) {
         const char* e = getenv("OJASX_B200_TENSOR_MIN_BATCH");   // read per call: a process can time both paths
         const int min_batch = e ? atoi(e) : kTensorMinBatch;
-        if (min_batch > 0 && batch_size >= min_batch) return launch_dequant_gemm(P, static_cast<cudaStream_t>(stream), &h->dq_scratch, &h->dq_scratch_cap);
+        if (min_batch > 0 && batch_size >= min_batch) return launch_dequant_gemm(P, static_cast<cudaStream_t>(stream), &h->dq_lists, h->generation);
     }
     return launch_linear(P, static_cast<cudaStream_t>(stream));
 }
@@ -250,7 +250,7 @@ int ojasx_b200_linear_forward_tensor(OjasxLinearHandle handle, const void* d_x, 
     if (batch_size <= 0 || row_start < 0 || row_stop > h->out || row_start >= row_stop) return OJX_ERR_ARG;
     LinearProblem P = h->problem(d_x, d_y, batch_size, OJX_BF16, row_start, row_stop);
     if (!dequant_gemm_supported(P, h->csr_sorted)) return OJX_ERR_UNSUPPORTED;
-    return launch_dequant_gemm(P, static_cast<cudaStream_t>(stream), &h->dq_scratch, &h->dq_scratch_cap);
+    return launch_dequant_gemm(P, static_cast<cudaStream_t>(stream), &h->dq_lists, h->generation);
 }
 
 int ojasx_b200_take_device_error(void) {

@@ -4,23 +4,29 @@
 // The weights are never materialised in global memory: per 128-row x 64-column tile a group of
 // two producer warps turns code bytes into bf16 (one 16-byte shared-memory gather from a bf16 copy
 // of the codebook per code byte), adds the rows' CSR outliers that fall in the tile, and stores the
-// tile in the 128-byte-swizzled K-major layout that tcgen05.mma reads; the same threads stage the
-// matching X tile.  Four such groups work on four consecutive K tiles at the same time, so the
+// tile in the 128-byte-swizzled K-major layout that tcgen05.mma reads; the matching X tile (batch rows x 64
+// columns, up to 32 KB) is one tiled bulk-tensor copy of the copy engine (cp.async.bulk.tensor.2d with the same
+// swizzle; rows past the batch are zero-filled), issued by one thread of the group -- per-thread 16-byte copies
+// kept too few bytes in flight and made the X tile the slowest part of a stage.  Four such groups work on four consecutive K tiles at the same time, so the
 // latencies of one tile's hand-over overlap with the others.  One thread of a ninth warp issues the MMAs (M = 128, N = padded batch, K = 16
 // per instruction, fp32 accumulation in tensor memory) and signals stage reuse with
 // tcgen05.commit.  After the last K tile the producer warps become the epilogue: tcgen05.ld the
 // accumulator rows, scale, bias, store bf16.
 //
 // A layer has few 128-row tiles (54 for 6912 rows), so the K axis is split over up to four CTAs per
-// tile until the GPU is full: each writes its raw fp32 partial sums to scratch, and the CTA that
-// finishes last (an atomic count after a device-wide fence) adds the partials in split order and
-// applies scale and bias -- no CTA waits for another.
+// tile until the GPU is full.  The CTAs of a tile form a thread-block cluster: each leaves its raw fp32
+// partial sums in its own shared memory (the stage buffers are idle by then), and after a cluster barrier
+// every CTA adds the partials of its share of the batch columns in split order, reading the other CTAs'
+// copies through distributed shared memory, and applies scale and bias.  (Partial sums through global
+// memory with the last CTA to arrive adding them cost 20 of the kernel's 40 microseconds at batch 256.)
 //
 // This path trades the bit-exactness of the table kernels for throughput (weights are rounded to
 // bf16), so it is used only for bf16 I/O, inside the rel 2e-2 tolerance of the bf16 activation path.
 // Every wait on an mbarrier is bounded; on a timeout the kernel raises a flag that the host reads.
 #include <algorithm>
 #include <cstdlib>
+
+#include <cuda.h>   // CUtensorMap and the types of cuTensorMapEncodeTiled (the entry point is looked up at run time)
 
 #include "common.cuh"
 #include "launch.h"
@@ -69,6 +75,17 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
     return false;
 }
 
+__device__ __forceinline__ void dq_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float dq_ld_cluster(unsigned local_addr, unsigned rank) {
+    unsigned remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
 // Shared-memory matrix descriptor of a K-major tile stored with the 128-byte swizzle: rows of 128
 // bytes, groups of 8 rows 1024 bytes apart.
 __device__ __forceinline__ unsigned long long make_desc_sw128(unsigned smem_addr) {
@@ -95,13 +112,17 @@ struct DequantGemmProblem {
     int tmem_cols;              // power of two >= n_pad, >= 32
     int stages;                 // stage buffers (3..8)
     int csr_cap;                // outlier entries of the CTA's rows that fit in shared memory
-    int ksplit;                 // CTAs per tile along K (gridDim.z)
+    int ksplit;                 // CTAs per tile along K (gridDim.z = the cluster's size)
     int tiles_per_split;        // K tiles per split (even, so that a split's code bytes start 16-byte aligned)
-    float* partial;             // ksplit > 1: [tile][split][n_pad][128] raw fp32 partial sums
-    int* tile_done;             // ksplit > 1: [tile] splits that have written their partial (returns to 0)
+    // Outliers listed per (128-row tile, 64-column tile) once per layer (dq_list_* kernels), or null: the lists are
+    // then made in shared memory by every CTA.  tile_off[rt * (KT_all + 1) + kt] .. [+ 1] = the tile's entries.
+    const int* tile_off;
+    const int2* tile_ent;       // (row in tile << 8 | column in tile, value / row scale)
+    int use_tma;                // X tiles by the copy engine (xmap); 0 = 16-byte cp.async pieces
 };
 
-__global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __grid_constant__ DequantGemmProblem P) {
+__global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __grid_constant__ DequantGemmProblem P,
+                                                                        const __grid_constant__ CUtensorMap xmap) {
     extern __shared__ unsigned char dq_smem_raw[];
     // swizzled tiles need 1024-byte alignment; the dynamic segment only promises 16
     unsigned char* dq_smem = dq_smem_raw + ((1024u - (smem_u32(dq_smem_raw) & 1023u)) & 1023u);
@@ -126,7 +147,6 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
     const int KT_all = P.K / kDqBlockK;
     const int kt0 = blockIdx.z * P.tiles_per_split;                  // this CTA's K tiles: [kt0, kt0 + KT)
     const int KT = min(P.tiles_per_split, KT_all - kt0);
-    const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
     const bool split = P.ksplit > 1;
 
     // codebook -> bf16, one 16-byte entry per centroid
@@ -142,7 +162,11 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
     // lists would not fit, the row-ordered entries are staged instead and every thread walks its rows.
     int csr_base = 0, csr_staged = 0;
     bool listed = false;
-    if (P.csr.nnz > 0 && m0 < P.row_stop) {
+    const bool glists = P.tile_off != nullptr && P.csr.nnz > 0 && KT <= kDqMaxTiles;
+    if (glists) {
+        const int* off = P.tile_off + (size_t)blockIdx.x * (KT_all + 1) + kt0;
+        for (int i = tid; i <= KT; i += kDqThreads) tstart[i] = off[i];
+    } else if (P.csr.nnz > 0 && m0 < P.row_stop) {
         const int n_rows = min(kDqBlockM, P.row_stop - m0);
         for (int i = tid; i <= n_rows; i += kDqThreads) rp_s[i] = P.csr.row_ptrs[m0 + i];
         for (int i = tid; i <= kDqMaxTiles + 1; i += kDqThreads) tstart[i] = 0;
@@ -216,7 +240,7 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
             rok[u] = rm[u] < P.row_stop;
             crow[u] = P.codes + (size_t)(rok[u] ? rm[u] : P.row_start) * P.G;
             cur[u] = cend[u] = 0;
-            if (rok[u] && P.csr.nnz > 0) { cur[u] = P.csr.row_ptrs[rm[u]]; cend[u] = P.csr.row_ptrs[rm[u] + 1]; }
+            if (rok[u] && P.csr.nnz > 0 && !glists) { cur[u] = P.csr.row_ptrs[rm[u]]; cend[u] = P.csr.row_ptrs[rm[u] + 1]; }
             // The reference adds the outlier row sum AFTER the row scale (ojasx_lut_cpu.cpp:178-182, 127), so an
             // outlier folded into the weight tile is pre-divided by the scale that the epilogue applies.
             const float sc = (rok[u] && P.scales) ? P.scales[rm[u]] : 1.0f;
@@ -230,7 +254,7 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
             if (i < csr_staged) { const int2 e = csr_s[i]; col_next[u] = e.x; val_next[u] = __int_as_float(e.y) * inv_scale[u]; }
             else { col_next[u] = P.csr.cols[cur[u]]; val_next[u] = P.csr.vals[cur[u]] * inv_scale[u]; }
         };
-        if (!listed) {
+        if (!listed && !glists) {
             fetch_outlier(0);
             fetch_outlier(1);
             while (col_next[0] < kt0 * kDqBlockK) { ++cur[0]; fetch_outlier(0); }   // outliers of the splits before this one
@@ -241,23 +265,47 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
             for (int u = 0; u < 2; ++u)
                 c[u] = kt < KT ? *reinterpret_cast<const uint2*>(crow[u] + (size_t)(kt0 + kt) * 8) : make_uint2(0u, 0u);
         };
+        // listed outliers of a tile in global memory: thread gt takes entry gt of the tile (read one tile ahead)
+        auto load_entry = [&](int kt) {
+            int2 e = make_int2(-1, 0);
+            if (glists && kt < KT && tstart[kt] + gt < tstart[kt + 1]) e = P.tile_ent[tstart[kt] + gt];
+            return e;
+        };
+        auto apply_entry = [&](unsigned char* A, const int2 e) {
+            const int row = e.x >> 8, kk = e.x & (kDqBlockK - 1), r7 = row & 7;
+            __nv_bfloat16* w = reinterpret_cast<__nv_bfloat16*>(A + (row >> 3) * 1024 + r7 * 128 + (((kk >> 3) ^ r7) << 4)) + (kk & 7);
+            *w = __float2bfloat16_rn(__bfloat162float(*w) + __int_as_float(e.y));
+        };
         uint2 codes_now[2], codes_next[2];
         load_codes(gq, codes_now);
+        int2 ent_now = load_entry(gq), ent_next;
         for (int kt = gq; kt < KT && ok; kt += kDqGroups) {
             const int s = kt % S;
             load_codes(kt + kDqGroups, codes_next);   // in flight while this tile is built
+            ent_next = load_entry(kt + kDqGroups);
             // the MMAs that read this stage's previous contents must be done
             if (kt >= S) ok = mbar_wait(empty0 + 8 * s, ((kt / S) - 1) & 1);
             if (!ok) break;
             unsigned char* A = tiles + s * stage_bytes;
             unsigned char* B = A + a_bytes;
-            for (int i = gt; i < total_x; i += kDqGroupThreads) {   // X tile: 16-byte chunks straight into their swizzled place
-                const int r = i >> 3, c = i & 7;
-                const bool in = r < nb;
-                cp_async16_zfill(B + (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4),
-                                 P.x + (size_t)(b0 + (in ? r : 0)) * P.K + (kt0 + kt) * kDqBlockK + c * 8, in ? 16 : 0);
+            if (P.use_tma) {
+                if (gt == 0) {   // X tile: one tiled copy; its bytes complete the stage's full barrier together with the arrivals
+                    const unsigned bar = full0 + 8 * s;
+                    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"((unsigned)b_bytes) : "memory");
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                        ::"r"(smem_u32(B)), "l"(reinterpret_cast<unsigned long long>(&xmap)), "r"((kt0 + kt) * kDqBlockK), "r"(b0), "r"(bar)
+                        : "memory");
+                }
+            } else {
+                for (int i = gt; i < total_x; i += kDqGroupThreads) {   // X tile: 16-byte chunks straight into their swizzled place
+                    const int r = i >> 3, c = i & 7;
+                    const bool in = r < nb;
+                    cp_async16_zfill(B + (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4),
+                                     P.x + (size_t)(b0 + (in ? r : 0)) * P.K + (kt0 + kt) * kDqBlockK + c * 8, in ? 16 : 0);
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");
             }
-            asm volatile("cp.async.commit_group;" ::: "memory");
             const int kbeg = (kt0 + kt) * kDqBlockK, kend = kbeg + kDqBlockK;
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
@@ -275,7 +323,7 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
                 for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(arow + ((q ^ r7) << 4)) = wv[q];
                 // row-walk fallback: CSR outliers of the row inside this tile (columns ascending): w += value / scale;
                 // entries of the tiles that other groups build are passed over
-                while (!listed && col_next[u] < kend) {
+                while (!listed && !glists && col_next[u] < kend) {
                     const int kk = col_next[u] - kbeg;
                     if (kk >= 0) {
                         __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(arow + (((kk >> 3) ^ r7) << 4)) + (kk & 7);
@@ -285,20 +333,21 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
                     fetch_outlier(u);
                 }
             }
-            if (listed && tstart[kt + 1] > tstart[kt]) {   // uniform over the group
+            if ((listed || glists) && tstart[kt + 1] > tstart[kt]) {   // uniform over the group
                 asm volatile("bar.sync %0, %1;" ::"r"(1 + gq), "n"(kDqGroupThreads) : "memory");   // the group's rows are stored
-                for (int i = tstart[kt] + gt; i < tstart[kt + 1]; i += kDqGroupThreads) {
-                    const int2 e = csr_s[i];
-                    const int row = e.x >> 8, kk = e.x & (kDqBlockK - 1), r7 = row & 7;
-                    __nv_bfloat16* w = reinterpret_cast<__nv_bfloat16*>(A + (row >> 3) * 1024 + r7 * 128 + (((kk >> 3) ^ r7) << 4)) + (kk & 7);
-                    *w = __float2bfloat16_rn(__bfloat162float(*w) + __int_as_float(e.y));
+                if (glists) {
+                    if (ent_now.x >= 0) apply_entry(A, ent_now);
+                    for (int i = tstart[kt] + gt + kDqGroupThreads; i < tstart[kt + 1]; i += kDqGroupThreads) apply_entry(A, P.tile_ent[i]);
+                } else {
+                    for (int i = tstart[kt] + gt; i < tstart[kt + 1]; i += kDqGroupThreads) apply_entry(A, csr_s[i]);
                 }
             }
-            asm volatile("cp.async.wait_group 0;" ::: "memory");   // this thread's share of the X tile has landed
+            if (!P.use_tma) asm volatile("cp.async.wait_group 0;" ::: "memory");   // this thread's share of the X tile has landed
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic and cp.async stores -> visible to the tensor core
             mbar_arrive(full0 + 8 * s);
             codes_now[0] = codes_next[0];
             codes_now[1] = codes_next[1];
+            ent_now = ent_next;
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         // the epilogue and the split reduction address rows as (tid & 127, tid >> 7)
@@ -315,24 +364,25 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
             const float sc = row_scale;
             const float bi = (row_ok && P.bias) ? P.bias[m] : 0.0f;
             const int cbeg = half * (N >> 1), cstop = cbeg + (N >> 1);
-            for (int c0 = cbeg; c0 < cstop; c0 += 8) {
-                unsigned v[8];
+            float* part = reinterpret_cast<float*>(tiles);   // split: [column][row] fp32, read by the whole cluster
+            for (int c0 = cbeg; c0 < cstop; c0 += 16) {
+                unsigned v[16];
                 const unsigned taddr = tmem_base + ((unsigned)((warp & 3) * 32) << 16) + (unsigned)c0;
                 asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                      "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
                     : "r"(taddr));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (split) {   // raw partial sums, rows contiguous
 #pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        if (c0 + j < nb)
-                            P.partial[(((size_t)tile_id * P.ksplit + blockIdx.z) * N + c0 + j) * kDqBlockM + trow] = __uint_as_float(v[j]);
+                    for (int j = 0; j < 16; ++j)
+                        if (c0 + j < cstop) part[(c0 + j) * kDqBlockM + trow] = __uint_as_float(v[j]);
                 } else if (row_ok) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
+                    for (int j = 0; j < 16; ++j) {
                         const int b = c0 + j;
-                        if (b < nb) {
+                        if (b < nb && b < cstop) {
                             float r = fmaf(__uint_as_float(v[j]), sc, bi);
                             if (sc == 0.0f)  // a zero row scale cannot carry the folded outliers: add them here
                                 for (int q = csr_begin; q < cend_row; ++q)
@@ -375,38 +425,35 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)P.tmem_cols) : "memory");
     }
     if (split) {
-        __shared__ int s_last;
-        __threadfence();   // this thread's partial sums are visible device-wide before the CTA is counted
-        __syncthreads();
-        if (tid == 0) {
-            const int last = atomicAdd(P.tile_done + tile_id, 1) == P.ksplit - 1;
-            if (last) P.tile_done[tile_id] = 0;
-            s_last = last;
-        }
-        __syncthreads();
-        if (s_last && warp < kDqProducers / 32) {
-            __threadfence();
+        // Every CTA of the cluster adds the partial sums of its share of the batch columns, in split order (the result
+        // does not depend on timing), and finishes those outputs.  All threads take part in the two cluster barriers;
+        // a CTA whose waits ran out still arrives, so the others are not left waiting.
+        dq_cluster_sync();   // the partial sums of every split are in place
+        if (warp < kDqProducers / 32) {
+            unsigned rank;
+            asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+            const int per = (N + P.ksplit - 1) / P.ksplit;
+            const int cfirst = (int)rank * per, clast = min(min(N, nb), cfirst + per);
             const int trow = tid & 127, half = tid >> 7, m = m0 + trow;
             if (m < P.row_stop) {
                 const float sc = P.scales ? P.scales[m] : 1.0f, bi = P.bias ? P.bias[m] : 0.0f;
-                const int cbeg = half * (N >> 1), cstop = min(cbeg + (N >> 1), nb);
-                for (int bb = cbeg; bb < cstop; bb += 8) {   // eight columns at a time: all loads first
-                    float acc[8];
+                const unsigned part0 = smem_u32(tiles);
+                for (int bb = cfirst + half; bb < clast; bb += 8) {   // four columns at a time: all loads first
+                    float pv[4][4];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
-                    for (int z = 0; z < P.ksplit; ++z) {   // split order: the result does not depend on which CTA came last
-                        float pv[8];
+                    for (int j = 0; j < 4; ++j)
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            pv[j] = bb + j < cstop ? __ldcg(P.partial + (((size_t)tile_id * P.ksplit + z) * N + bb + j) * kDqBlockM + trow) : 0.0f;
+                        for (int z = 0; z < 4; ++z)
+                            pv[j][z] = (bb + 2 * j < clast && z < P.ksplit)
+                                           ? dq_ld_cluster(part0 + (unsigned)((bb + 2 * j) * kDqBlockM + trow) * 4u, (unsigned)z) : 0.0f;
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) acc[j] += pv[j];
-                    }
+                    for (int j = 0; j < 4; ++j) {
+                        const int b = bb + 2 * j;
+                        if (b >= clast) break;
+                        float acc = 0.0f;
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int b = bb + j;
-                        if (b >= cstop) break;
-                        float r = fmaf(acc[j], sc, bi);
+                        for (int z = 0; z < 4; ++z) if (z < P.ksplit) acc += pv[j][z];
+                        float r = fmaf(acc, sc, bi);
                         if (sc == 0.0f && P.csr.nnz > 0)  // a zero row scale cannot carry the folded outliers: add them here
                             for (int q = P.csr.row_ptrs[m]; q < P.csr.row_ptrs[m + 1]; ++q)
                                 r += P.csr.vals[q] * __bfloat162float(P.x[(size_t)(b0 + b) * P.K + P.csr.cols[q]]);
@@ -415,6 +462,7 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
                 }
             }
         }
+        dq_cluster_sync();   // nobody leaves while its partial sums may still be read
     }
 }
 
@@ -445,7 +493,7 @@ bool dequant_gemm_supported(const LinearProblem& P, bool csr_sorted) {
 }
 
 // Splits along K for `ctas` (row tile, batch tile) pairs and KT tiles of 64 columns: fill the SMs, at most
-// four splits, at least eight tiles per split, an even number of tiles per split.
+// four splits (one thread-block cluster), at least eight tiles per split, an even number of tiles per split.
 static void plan_ksplit(int ctas, int KT, int sms, int* ksplit, int* per) {
     int z = sms / (ctas > 0 ? ctas : 1);
     z = z < 1 ? 1 : z > 4 ? 4 : z;
@@ -456,7 +504,138 @@ static void plan_ksplit(int ctas, int KT, int sms, int* ksplit, int* per) {
     *ksplit = z > 1 ? (KT + p - 1) / p : 1;
 }
 
-int launch_dequant_gemm(const LinearProblem& L, cudaStream_t stream, void** scratch, size_t* scratch_cap) {
+// ---- outliers listed per (128-row tile, 64-column tile), once per layer and row range
+// counts[rt * (KT + 1) + kt + 1] = entries of tile (rt, kt); after the scan the same array holds the offsets.
+__global__ void dq_list_count_kernel(CsrView csr, int row_start, int row_stop, int KT, int* counts) {
+    const int m = row_start + blockIdx.x * blockDim.x + threadIdx.x;
+    if (m >= row_stop) return;
+    const int rt = (m - row_start) / kDqBlockM;
+    for (int j = csr.row_ptrs[m]; j < csr.row_ptrs[m + 1]; ++j) {
+        const int kt = csr.cols[j] / kDqBlockK;
+        if (kt < KT) atomicAdd(&counts[(size_t)rt * (KT + 1) + kt + 1], 1);
+    }
+}
+// One block: inclusive scan of counts[0, n) in place (counts[0] and every tile row's first slot are zero, so
+// slot rt * (KT + 1) + kt ends up as the first entry of tile (rt, kt)); `fill` gets a copy for the scatter.
+__global__ void dq_list_scan_kernel(int* counts, int* fill, int n, int base) {
+    __shared__ int warp_sum[32];
+    __shared__ int carry;
+    if (threadIdx.x == 0) carry = base;
+    __syncthreads();
+    for (int i0 = 0; i0 < n; i0 += blockDim.x) {
+        const int i = i0 + threadIdx.x;
+        int v = i < n ? counts[i] : 0;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, v, o);
+            if ((threadIdx.x & 31) >= o) v += t;
+        }
+        if ((threadIdx.x & 31) == 31) warp_sum[threadIdx.x >> 5] = v;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            int w = threadIdx.x < (blockDim.x >> 5) ? warp_sum[threadIdx.x] : 0;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, w, o);
+                if (threadIdx.x >= o) w += t;
+            }
+            warp_sum[threadIdx.x] = w;
+        }
+        __syncthreads();
+        const int before = carry + ((threadIdx.x >> 5) ? warp_sum[(threadIdx.x >> 5) - 1] : 0);
+        if (i < n) { counts[i] = before + v; fill[i] = before + v; }
+        __syncthreads();
+        if (threadIdx.x == blockDim.x - 1) carry = before + v;
+        __syncthreads();
+    }
+}
+__global__ void dq_list_fill_kernel(CsrView csr, const float* scales, int row_start, int row_stop, int KT, int* fill, int2* ent) {
+    const int m = row_start + blockIdx.x * blockDim.x + threadIdx.x;
+    if (m >= row_stop) return;
+    const int rt = (m - row_start) / kDqBlockM, row = (m - row_start) % kDqBlockM;
+    // The reference adds the outlier row sum AFTER the row scale (ojasx_lut_cpu.cpp:178-182, 127), so an outlier
+    // folded into the weight tile is pre-divided by the scale that the epilogue applies.
+    const float sc = scales ? scales[m] : 1.0f;
+    for (int j = csr.row_ptrs[m]; j < csr.row_ptrs[m + 1]; ++j) {
+        const int col = csr.cols[j], kt = col / kDqBlockK;
+        if (kt >= KT) continue;
+        const float v = sc != 0.0f ? csr.vals[j] / sc : 0.0f;
+        // slot kt of the row tile holds the END of tile kt - 1 = start of tile kt after the scan
+        const int pos = atomicAdd(&fill[(size_t)rt * (KT + 1) + kt], 1);
+        ent[pos] = make_int2((row << 8) | (col & (kDqBlockK - 1)), __float_as_int(v));
+    }
+}
+
+DqLists::~DqLists() { cudaFree(off); cudaFree(ent); }
+
+// Builds (or reuses) the lists for rows [row_start, row_stop) of the layer behind L.  Returns false when they cannot be
+// used for this launch (no outliers, a stream capture in progress before they exist, an allocation that failed).
+static bool ensure_dq_lists(DqLists* d, const LinearProblem& L, unsigned generation, cudaStream_t stream) {
+    if (!d || L.csr.nnz <= 0) return false;
+    const int KT = L.K / kDqBlockK, rows = L.row_stop - L.row_start, row_tiles = (rows + kDqBlockM - 1) / kDqBlockM;
+    if (d->valid && d->generation == generation && d->row_start == L.row_start && d->row_stop == L.row_stop && d->csr_vals == L.csr.vals)
+        return true;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return false;
+    d->valid = false;
+    const size_t n_off = (size_t)row_tiles * (KT + 1) + 1;
+    if (n_off > d->off_cap) {
+        cudaFree(d->off);
+        d->off = nullptr; d->off_cap = 0;
+        if (cudaMalloc((void**)&d->off, sizeof(int) * 2 * n_off) != cudaSuccess) { cudaGetLastError(); return false; }
+        d->off_cap = n_off;
+    }
+    if ((size_t)L.csr.nnz > d->ent_cap) {
+        cudaFree(d->ent);
+        d->ent = nullptr; d->ent_cap = 0;
+        if (cudaMalloc((void**)&d->ent, sizeof(int2) * (size_t)L.csr.nnz) != cudaSuccess) { cudaGetLastError(); return false; }
+        d->ent_cap = (size_t)L.csr.nnz;
+    }
+    int* fill = d->off + d->off_cap;
+    if (cudaMemsetAsync(d->off, 0, sizeof(int) * n_off, stream) != cudaSuccess) return false;
+    const int blocks = (rows + 255) / 256;
+    dq_list_count_kernel<<<blocks, 256, 0, stream>>>(L.csr, L.row_start, L.row_stop, KT, d->off);
+    dq_list_scan_kernel<<<1, 1024, 0, stream>>>(d->off, fill, (int)n_off, 0);
+    // after the inclusive scan slot (rt, kt + 1) holds the end of tile (rt, kt): shift by one slot when reading, i.e.
+    // tile (rt, kt) = [slot(rt, kt), slot(rt, kt + 1)) -- slot (rt, 0) is the end of the previous row tile
+    dq_list_fill_kernel<<<blocks, 256, 0, stream>>>(L.csr, L.scales, L.row_start, L.row_stop, KT, fill, d->ent);
+    if (cudaGetLastError() != cudaSuccess) return false;
+    count_launch(3);
+    d->row_start = L.row_start; d->row_stop = L.row_stop; d->generation = generation; d->csr_vals = L.csr.vals;
+    d->valid = true;
+    return true;
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link against the driver library).
+using TensorMapEncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                       const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                       CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static TensorMapEncodeFn tensor_map_encoder() {
+    static TensorMapEncodeFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) {
+            cudaGetLastError();
+            p = nullptr;
+        }
+        return reinterpret_cast<TensorMapEncodeFn>(p);
+    }();
+    return fn;
+}
+// X [batch, K] bf16 row-major as a 2-D tensor (columns innermost), box = 64 columns x n_pad rows, 128-byte swizzle;
+// rows past the batch read as zero.
+static bool encode_x_map(CUtensorMap* map, const void* x, int K, int batch, int n_pad) {
+    TensorMapEncodeFn enc = tensor_map_encoder();
+    if (!enc) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)batch};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kDqBlockK, (cuuint32_t)n_pad};
+    const cuuint32_t estr[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int launch_dequant_gemm(const LinearProblem& L, cudaStream_t stream, DqLists* lists, unsigned generation) {
     DequantGemmProblem P{};
     int* error_flag = nullptr;
     OJX_CUDA_TRY(cudaGetSymbolAddress((void**)&error_flag, g_dq_error));
@@ -473,13 +652,16 @@ int launch_dequant_gemm(const LinearProblem& L, cudaStream_t stream, void** scra
     // parity; with fewer stages than groups a group could be two phases ahead of a stage it shares with
     // another group, and a parity wait cannot tell "two ahead" from "done".)  More stages when the batch
     // tile is narrow; room for at least 1024 staged outlier entries is kept.
+    // Outlier lists of the layer (built once) spare every CTA the sort in its prologue and the shared memory for it.
+    const bool glists = L.K / kDqBlockK <= kDqMaxTiles && !getenv("OJASX_B200_TENSOR_NO_LISTS") && ensure_dq_lists(lists, L, generation, stream);
+    if (glists) { P.tile_off = lists->off; P.tile_ent = lists->ent; }
     P.stages = kDqGroups;
-    if (dequant_gemm_smem(P.n_pad, P.stages, 1024) > kDqSmemBudget) return OJX_ERR_UNSUPPORTED;
-    while (P.stages < kDqStages && dequant_gemm_smem(P.n_pad, P.stages + 1, 4096) <= kDqSmemBudget) ++P.stages;
+    if (dequant_gemm_smem(P.n_pad, P.stages, glists ? 0 : 1024) > kDqSmemBudget) return OJX_ERR_UNSUPPORTED;
+    while (P.stages < kDqStages && dequant_gemm_smem(P.n_pad, P.stages + 1, glists ? 0 : 4096) <= kDqSmemBudget) ++P.stages;
     // shared-memory room for the outliers of 128 rows: whatever is left, up to 8192 entries; the
     // kernel reads entries beyond that from global memory
     P.csr_cap = 0;
-    if (L.csr.nnz > 0) {
+    if (L.csr.nnz > 0 && !glists) {
         const size_t left = kDqSmemBudget - dequant_gemm_smem(P.n_pad, P.stages, 0);
         P.csr_cap = (int)(left / 8 < 8192 ? left / 8 : 8192);
     }
@@ -496,27 +678,33 @@ int launch_dequant_gemm(const LinearProblem& L, cudaStream_t stream, void** scra
     dim3 grid((rows + kDqBlockM - 1) / kDqBlockM, (L.batch + 255) / 256, 1);
     P.ksplit = 1;
     P.tiles_per_split = L.K / kDqBlockK;
-    if (scratch && scratch_cap && !getenv("OJASX_B200_TENSOR_NO_KSPLIT")) {
+    if (!getenv("OJASX_B200_TENSOR_NO_KSPLIT")) {
         int z = 1, per = P.tiles_per_split;
         plan_ksplit((int)(grid.x * grid.y), L.K / kDqBlockK, num_sms(), &z, &per);
         if (z > 1) {
-            // [tiles] counters (zeroed once; they return to zero) followed by the partial sums
-            const size_t tiles = (size_t)grid.x * grid.y, cnt_bytes = round_up((int)(tiles * sizeof(int)), 256);
-            const size_t need = cnt_bytes + sizeof(float) * tiles * z * P.n_pad * kDqBlockM;
-            if (*scratch_cap < need || !*scratch) {
-                int rc = ensure_capacity(scratch, scratch_cap, need);
-                if (rc != OJX_OK) return rc;
-                OJX_CUDA_TRY(cudaMemsetAsync(*scratch, 0, *scratch_cap, stream));
-            }
-            P.tile_done = static_cast<int*>(*scratch);
-            P.partial = reinterpret_cast<float*>(static_cast<char*>(*scratch) + cnt_bytes);
             P.ksplit = z;
             P.tiles_per_split = per;
             grid.z = z;
         }
     }
-    vq_dequant_gemm_kernel<<<grid, kDqThreads, smem, stream>>>(P);
-    OJX_CUDA_TRY(cudaGetLastError());
+    // X tiles by the copy engine when the tensor map can be made (OJASX_B200_TENSOR_TMA=0 keeps the 16-byte copies)
+    CUtensorMap xmap{};
+    const char* tma_env = getenv("OJASX_B200_TENSOR_TMA");
+    P.use_tma = !(tma_env && tma_env[0] == '0') && encode_x_map(&xmap, L.x, L.K, L.batch, P.n_pad) ? 1 : 0;
+    // the K splits of a tile are one cluster (they exchange partial sums through distributed shared memory)
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kDqThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = grid.z;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    OJX_CUDA_TRY(cudaLaunchKernelEx(&cfg, vq_dequant_gemm_kernel, P, xmap));
     count_launch(1);
     return OJX_OK;
 }

@@ -1,6 +1,7 @@
 // Host-side objects behind the opaque C handles.
 #pragma once
 #include "common.cuh"
+#include "launch.h"
 #include <mutex>
 #include <vector>
 
@@ -45,8 +46,7 @@ struct LinearHandle {
     void* pin_y_dev_of = nullptr;  // the pin_y it was taken from
     cudaStream_t stream = nullptr;
     std::mutex host_mu;            // the host-pointer entry points use this handle's staging buffers one call at a time
-    void* dq_scratch = nullptr;    // tensor-core path: tile counters and split-K partial sums
-    size_t dq_scratch_cap = 0;
+    DqLists dq_lists;              // tensor-core path: outliers listed per weight tile (freed by its own destructor)
     // host-pointer forward: the copy of x and the kernel as one instantiated graph (one launch call per forward)
     cudaGraphExec_t host_graph = nullptr;
     int host_graph_batch = 0;

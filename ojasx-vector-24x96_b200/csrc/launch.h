@@ -30,7 +30,19 @@ int launch_rvq_generic(const uint8_t* packed, const float* codebooks, const floa
 bool dequant_gemm_supported(const LinearProblem& P, bool csr_sorted);
 // scratch / scratch_cap: a grow-only device buffer of the caller (per layer handle) for the split-K partial
 // sums and tile counters; null = never split.  Calls that share the buffer must not overlap in time.
-int launch_dequant_gemm(const LinearProblem& P, cudaStream_t stream, void** scratch = nullptr, size_t* scratch_cap = nullptr);
+// Outliers of a layer listed per (128-row, 64-column) weight tile for the tensor-core path; built on the device the
+// first time a layer and row range take that path, kept by the layer's handle.
+struct DqLists {
+    int* off = nullptr;        // [row_tiles * (K / 64 + 1) + 1] tile offsets, followed by the scatter cursors
+    int2* ent = nullptr;       // [nnz] (row in tile << 8 | column in tile, value / row scale)
+    size_t off_cap = 0, ent_cap = 0;
+    int row_start = -1, row_stop = -1;
+    unsigned generation = 0;
+    const float* csr_vals = nullptr;
+    bool valid = false;
+    ~DqLists();
+};
+int launch_dequant_gemm(const LinearProblem& P, cudaStream_t stream, DqLists* lists = nullptr, unsigned generation = 0);
 int take_dequant_gemm_error(int* out);
 
 // --- moe.cu

@@ -250,3 +250,38 @@ def test_tensor_core_outlier_paths(cuda, oracle, frac):
     err = np.abs(got - want)
     assert np.all(err <= 2e-2 * np.abs(want) + 3e-2 * (1 + 20 * frac)), (err.max(), np.abs(want).max())
 
+
+
+@pytest.mark.parametrize("K,M,batch,frac", [(2560, 6912, 256, 0.0038), (6912, 2560, 64, 0.0038), (640, 1000, 300, 0.05), (2560, 700, 40, 0.0),
+                                            (2560, 5120, 48, 0.0038)])   # the last one: three K splits, 16 batch columns each
+def test_tensor_core_feeds_agree(cuda, oracle, monkeypatch, K, M, batch, frac):
+    """The X tile by the copy engine against 16-byte copies, and the outlier lists built once per layer against the
+    lists every CTA sorts for itself: the same weights meet the same activations in the same order, so the outputs
+    are equal bit for bit -- for whole layers, row slices that start off a 128-row boundary, a second slice of the
+    same layer (the lists are rebuilt)."""
+    w = synth.make_vq_linear(K + M, K, M, block_dim=8, outlier_frac=frac, with_scales=True, with_bias=True)
+    layer = ops.VQLinear.from_weights(w)
+    xb = synth.to_bf16_f32(np.random.default_rng(batch).standard_normal((batch, K)).astype(np.float32))
+    xt = torch.from_numpy(xb).to(cuda).bfloat16()
+    slices = [(0, M), (100, M - 37), (3, 131)]
+
+    def run_all():
+        return [layer.forward_tensor(xt, a, b) for a, b in slices]
+
+    new = run_all()
+    monkeypatch.setenv("OJASX_B200_TENSOR_TMA", "0")
+    no_tma = run_all()
+    monkeypatch.setenv("OJASX_B200_TENSOR_NO_LISTS", "1")
+    old = run_all()
+    monkeypatch.delenv("OJASX_B200_TENSOR_TMA")
+    no_lists = run_all()
+    monkeypatch.delenv("OJASX_B200_TENSOR_NO_LISTS")
+    assert ojasx_b200.lib().ojasx_b200_take_device_error() == 0
+    for i in range(len(slices)):
+        assert torch.equal(new[i], no_tma[i]) and torch.equal(new[i], old[i]) and torch.equal(new[i], no_lists[i]), slices[i]
+    want = oracle.linear_forward(w.codebook, w.codes, w.scales, w.bias, w.csr, xb, block_dim=8)
+    got = new[0].float().cpu().numpy()
+    assert np.all(np.abs(got - want) <= 2e-2 * np.abs(want) + 3e-2), np.abs(got - want).max()
+    # row slices may split K differently from the whole layer (other partial sums, same tolerance)
+    for (a, b), y in zip(slices[1:], new[1:]):
+        assert torch.allclose(y.float(), new[0][:, a:b].float(), rtol=2e-2, atol=3e-2)
