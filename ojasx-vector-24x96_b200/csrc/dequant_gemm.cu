@@ -466,6 +466,277 @@ __global__ void __launch_bounds__(kDqThreads, 1) vq_dequant_gemm_kernel(const __
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// 256-row variant, for batches of several 256-column tiles.  Every row tile streams all of X from L2 (an X tile is
+// twice the size of a 128-row weight tile at batch 256), and L2 delivers about 25 bytes per clock and SM, which is
+// what bounds the 128-row kernel at wide batches.  Here a CTA owns two adjacent 128-row tiles: a stage holds both
+// weight tiles and ONE X tile, every K step issues two MMAs that share the B operand, and the two accumulators sit
+// side by side in tensor memory (2 x N <= 512 columns).  Three producer groups of 128 threads each own one of three
+// stages (thread t builds row t of both weight tiles), so a group can never be two phases ahead of a stage.
+// It is used when (row pairs x batch tiles) fill the GPU without a split along K: with a split, the fp32 partial sums
+// of a 256 x 256 tile (256 KB per CTA, whatever the split) cost as much traffic between the SMs as the X tiles they
+// save -- measured at batch 256 with a cluster of five: 56 against 29 microseconds for the 128-row kernel; at batch
+// 1024 (no split) 66 against 73.  Needs the X tiles by the copy engine and the outlier lists of the layer (or no
+// outliers); other cases take the 128-row kernel.
+constexpr int kDq2Groups = 3;
+constexpr int kDq2GroupThreads = 128;
+constexpr int kDq2Producers = kDq2Groups * kDq2GroupThreads;
+constexpr int kDq2Threads = kDq2Producers + 32;
+constexpr int kDq2Stages = kDq2Groups;
+
+__global__ void __launch_bounds__(kDq2Threads, 1) vq_dequant_gemm256_kernel(const __grid_constant__ DequantGemmProblem P,
+                                                                           const __grid_constant__ CUtensorMap xmap) {
+    extern __shared__ unsigned char dq_smem_raw[];
+    unsigned char* dq_smem = dq_smem_raw + ((1024u - (smem_u32(dq_smem_raw) & 1023u)) & 1023u);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int N = P.n_pad;
+    constexpr int S = kDq2Stages;
+    const int a_bytes = 2 * kDqBlockM * 128, b_bytes = N * 128, stage_bytes = a_bytes + b_bytes;
+    unsigned char* tiles = dq_smem;                                    // [3][A0 | A1 | B], 1024-byte aligned
+    uint4* cb16 = reinterpret_cast<uint4*>(tiles + S * stage_bytes);    // [256] centroids as 8 bf16
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(cb16 + 256);
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * S + 1);
+    int* toff = reinterpret_cast<int*>(tmem_slot + 2);                  // [2][kDqMaxTiles + 2] outlier list offsets of both row tiles
+    const unsigned full0 = smem_u32(bars), empty0 = full0 + 8 * S, accum = empty0 + 8 * S;
+
+    const int m0 = P.row_start + blockIdx.x * 2 * kDqBlockM;
+    const int b0 = blockIdx.y * 256;
+    const int nb = min(256, P.batch - b0);
+    const int rows_out = P.row_stop - P.row_start;
+    const int KT_all = P.K / kDqBlockK;
+    const int kt0 = blockIdx.z * P.tiles_per_split;
+    const int KT = min(P.tiles_per_split, KT_all - kt0);
+    const bool split = P.ksplit > 1;
+    const bool glists = P.tile_off != nullptr && P.csr.nnz > 0;
+    const int row_tiles = (rows_out + kDqBlockM - 1) / kDqBlockM;
+
+    for (int c = tid; c < 256; c += kDq2Threads) {
+        __nv_bfloat162 h[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(P.codebook[c * 8 + 2 * q], P.codebook[c * 8 + 2 * q + 1]);
+        cb16[c] = *reinterpret_cast<uint4*>(h);
+    }
+    for (int i = tid; i < 2 * (kDqMaxTiles + 2); i += kDq2Threads) {
+        const int a = i / (kDqMaxTiles + 2), k = i - a * (kDqMaxTiles + 2), rt = 2 * (int)blockIdx.x + a;
+        toff[i] = (glists && rt < row_tiles && k <= KT) ? P.tile_off[(size_t)rt * (KT_all + 1) + kt0 + k] : 0;
+    }
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) { mbar_init(full0 + 8 * s, kDq2GroupThreads); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kDq2Producers / 32) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((unsigned)P.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem_base = *tmem_slot;
+    bool ok = true;
+
+    // accumulator rows of this thread in the epilogue: row (warp & 3) * 32 + lane of both tiles (tensor-memory lanes are
+    // tied to warp % 4); the three warps of a lane quarter share the columns
+    const int erow = (warp & 3) * 32 + lane, esib = warp >> 2;
+    auto ld16 = [&](int a, int c0, unsigned (&v)[16]) {
+        const unsigned taddr = tmem_base + ((unsigned)((warp & 3) * 32) << 16) + (unsigned)(a * N + c0);
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+              "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+            : "r"(taddr));
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    };
+    auto finish = [&](int m, int b, float acc, float sc, float bi) {   // scale, bias, store (zero scales: outliers added here)
+        float r = fmaf(acc, sc, bi);
+        if (sc == 0.0f && P.csr.nnz > 0)
+            for (int q = P.csr.row_ptrs[m]; q < P.csr.row_ptrs[m + 1]; ++q)
+                r += P.csr.vals[q] * __bfloat162float(P.x[(size_t)(b0 + b) * P.K + P.csr.cols[q]]);
+        P.y[(size_t)(b0 + b) * rows_out + (m - P.row_start)] = __float2bfloat16_rn(r);
+    };
+
+    if (warp < kDq2Producers / 32) {
+        const int gq = tid / kDq2GroupThreads, gt = tid - gq * kDq2GroupThreads;
+        bool rok[2];
+        const uint8_t* crow[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int m = m0 + u * kDqBlockM + gt;
+            rok[u] = m < P.row_stop;
+            crow[u] = P.codes + (size_t)(rok[u] ? m : P.row_start) * P.G;
+        }
+        auto load_codes = [&](int kt, uint2 (&c)[2]) {
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+                c[u] = kt < KT ? *reinterpret_cast<const uint2*>(crow[u] + (size_t)(kt0 + kt) * 8) : make_uint2(0u, 0u);
+        };
+        auto load_entries = [&](int kt, int2 (&e)[2]) {   // entry gt of the K tile's list of each row tile (read one tile ahead)
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int* o = toff + u * (kDqMaxTiles + 2);
+                e[u] = make_int2(-1, 0);
+                if (glists && kt < KT && o[kt] + gt < o[kt + 1]) e[u] = P.tile_ent[o[kt] + gt];
+            }
+        };
+        auto apply_entry = [&](unsigned char* A, const int2 e) {
+            const int row = e.x >> 8, kk = e.x & (kDqBlockK - 1), r7 = row & 7;
+            __nv_bfloat16* w = reinterpret_cast<__nv_bfloat16*>(A + (row >> 3) * 1024 + r7 * 128 + (((kk >> 3) ^ r7) << 4)) + (kk & 7);
+            *w = __float2bfloat16_rn(__bfloat162float(*w) + __int_as_float(e.y));
+        };
+        uint2 codes_now[2], codes_next[2];
+        int2 ent_now[2], ent_next[2];
+        load_codes(gq, codes_now);
+        load_entries(gq, ent_now);
+        for (int kt = gq; kt < KT && ok; kt += kDq2Groups) {
+            const int s = gq;   // == kt % 3: every group owns one stage
+            load_codes(kt + kDq2Groups, codes_next);
+            load_entries(kt + kDq2Groups, ent_next);
+            if (kt >= S) ok = mbar_wait(empty0 + 8 * s, ((kt / S) - 1) & 1);
+            if (!ok) break;
+            unsigned char* A = tiles + s * stage_bytes;
+            unsigned char* B = A + a_bytes;
+            if (gt == 0) {   // the X tile of this K step, once for both weight tiles
+                const unsigned bar = full0 + 8 * s;
+                asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"((unsigned)b_bytes) : "memory");
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                    ::"r"(smem_u32(B)), "l"(reinterpret_cast<unsigned long long>(&xmap)), "r"((kt0 + kt) * kDqBlockK), "r"(b0), "r"(bar)
+                    : "memory");
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int r7 = gt & 7;
+                unsigned char* arow = A + u * (kDqBlockM * 128) + (gt >> 3) * 1024 + r7 * 128;
+                const unsigned cw[2] = {codes_now[u].x, codes_now[u].y};
+                uint4 wv[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    const unsigned code = (cw[q >> 2] >> ((q & 3) * 8)) & 0xffu;
+                    wv[q] = rok[u] ? cb16[code] : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(arow + ((q ^ r7) << 4)) = wv[q];
+            }
+            const int* o0 = toff;
+            const int* o1 = toff + (kDqMaxTiles + 2);
+            if (o0[kt + 1] > o0[kt] || o1[kt + 1] > o1[kt]) {   // uniform over the group
+                asm volatile("bar.sync %0, %1;" ::"r"(1 + gq), "n"(kDq2GroupThreads) : "memory");   // the group's rows are stored
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int* o = u ? o1 : o0;
+                    unsigned char* Au = A + u * (kDqBlockM * 128);
+                    if (ent_now[u].x >= 0) apply_entry(Au, ent_now[u]);
+                    for (int i = o[kt] + gt + kDq2GroupThreads; i < o[kt + 1]; i += kDq2GroupThreads) apply_entry(Au, P.tile_ent[i]);
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(full0 + 8 * s);
+            codes_now[0] = codes_next[0];
+            codes_now[1] = codes_next[1];
+            ent_now[0] = ent_next[0];
+            ent_now[1] = ent_next[1];
+        }
+        if (ok) ok = mbar_wait(accum, 0);
+        if (__all_sync(0xffffffffu, ok) && !split) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            for (int ci = esib; ci < 2 * N / 16; ci += kDq2Groups) {
+                const int a = (ci * 16) / N, c0 = ci * 16 - a * N, m = m0 + a * kDqBlockM + erow;
+                unsigned v[16];
+                ld16(a, c0, v);   // every lane of the warp takes part in the load
+                if (m < P.row_stop) {
+                    const float sc = P.scales ? P.scales[m] : 1.0f, bi = P.bias ? P.bias[m] : 0.0f;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (c0 + j < nb) finish(m, c0 + j, __uint_as_float(v[j]), sc, bi);
+                }
+            }
+        }
+    } else if (lane == 0) {
+        const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(N >> 3) << 17) | ((unsigned)(kDqBlockM >> 4) << 24);
+        for (int kt = 0; kt < KT && ok; ++kt) {
+            const int s = kt % S;
+            ok = mbar_wait(full0 + 8 * s, (kt / S) & 1);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const unsigned a_addr = smem_u32(tiles + s * stage_bytes), b_addr = a_addr + a_bytes;
+#pragma unroll
+            for (int j = 0; j < kDqBlockK / 16; ++j) {
+                const unsigned long long db = make_desc_sw128(b_addr + j * 32);
+                const unsigned acc = (kt > 0 || j > 0) ? 1u : 0u;
+#pragma unroll
+                for (int a = 0; a < 2; ++a) {
+                    const unsigned long long da = make_desc_sw128(a_addr + a * (kDqBlockM * 128) + j * 32);
+                    asm volatile(
+                        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                        ::"r"(tmem_base + (unsigned)(a * N)), "l"(da), "l"(db), "r"(idesc), "r"(acc)
+                        : "memory");
+                }
+            }
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(empty0 + 8 * s) : "memory");
+        }
+        if (ok) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(accum) : "memory");
+    }
+    if (!ok && P.error_flag) atomicExch(P.error_flag, 1);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (split) {
+        // One accumulator at a time (both do not fit in shared memory): every CTA of the cluster leaves its partial sums
+        // in its stage buffers, then adds its share of the batch columns over all splits, in split order.
+        unsigned rank;
+        asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+        const int per = (N + P.ksplit - 1) / P.ksplit;
+        const int cfirst = (int)rank * per, clast = min(min(N, nb), cfirst + per);
+        float* part = reinterpret_cast<float*>(tiles);   // [column][row] fp32
+        const unsigned part0 = smem_u32(tiles);
+        for (int a = 0; a < 2; ++a) {
+            if (warp < kDq2Producers / 32 && __all_sync(0xffffffffu, ok)) {   // (a warp whose waits ran out leaves its part undefined; the flag is up)
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (int ci = esib; ci < N / 16; ci += kDq2Groups) {
+                    unsigned v[16];
+                    ld16(a, ci * 16, v);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) part[(ci * 16 + j) * kDqBlockM + erow] = __uint_as_float(v[j]);
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            }
+            dq_cluster_sync();   // the partial sums of every split are in place
+            const int m = m0 + a * kDqBlockM + erow;
+            if (warp < kDq2Producers / 32 && m < P.row_stop) {
+                const float sc = P.scales ? P.scales[m] : 1.0f, bi = P.bias ? P.bias[m] : 0.0f;
+                for (int bb = cfirst + esib; bb < clast; bb += 4 * kDq2Groups) {   // four columns at a time: all loads first
+                    float pv[4][8];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+#pragma unroll
+                        for (int z = 0; z < 8; ++z)
+                            pv[j][z] = (bb + kDq2Groups * j < clast && z < P.ksplit)
+                                           ? dq_ld_cluster(part0 + (unsigned)((bb + kDq2Groups * j) * kDqBlockM + erow) * 4u, (unsigned)z) : 0.0f;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int b = bb + kDq2Groups * j;
+                        if (b >= clast) break;
+                        float acc = 0.0f;
+#pragma unroll
+                        for (int z = 0; z < 8; ++z) if (z < P.ksplit) acc += pv[j][z];
+                        finish(m, b, acc, sc, bi);
+                    }
+                }
+            }
+            dq_cluster_sync();   // nobody overwrites or leaves while its partial sums may still be read
+        }
+    }
+    if (warp == kDq2Producers / 32) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)P.tmem_cols) : "memory");
+    }
+}
+
+size_t dequant_gemm256_smem(int n_pad) {
+    return (size_t)kDq2Stages * (2 * kDqBlockM * 128 + (size_t)n_pad * 128) + 256 * 16 + (2 * kDq2Stages + 1) * 8 + 16 +
+           sizeof(int) * 2 * (kDqMaxTiles + 2) + 1024;
+}
+
 constexpr size_t kDqSmemBudget = 226 * 1024;   // dynamic shared memory; the kernel also has a few static bytes
 
 size_t dequant_gemm_smem(int n_pad, int stages, int csr_cap) {
@@ -494,9 +765,9 @@ bool dequant_gemm_supported(const LinearProblem& P, bool csr_sorted) {
 
 // Splits along K for `ctas` (row tile, batch tile) pairs and KT tiles of 64 columns: fill the SMs, at most
 // four splits (one thread-block cluster), at least eight tiles per split, an even number of tiles per split.
-static void plan_ksplit(int ctas, int KT, int sms, int* ksplit, int* per) {
+static void plan_ksplit(int ctas, int KT, int sms, int zmax, int* ksplit, int* per) {
     int z = sms / (ctas > 0 ? ctas : 1);
-    z = z < 1 ? 1 : z > 4 ? 4 : z;
+    z = z < 1 ? 1 : z > zmax ? zmax : z;
     while (z > 1 && KT / z < 8) --z;
     int p = (KT + z - 1) / z;
     p += p & 1;
@@ -648,13 +919,63 @@ int launch_dequant_gemm(const LinearProblem& L, cudaStream_t stream, DqLists* li
     int cols = 32;
     while (cols < P.n_pad) cols <<= 1;
     P.tmem_cols = cols;
-    // Stage buffers: at least one per producer group.  (A group waits on a stage's "empty" barrier by phase
-    // parity; with fewer stages than groups a group could be two phases ahead of a stage it shares with
-    // another group, and a parity wait cannot tell "two ahead" from "done".)  More stages when the batch
-    // tile is narrow; room for at least 1024 staged outlier entries is kept.
     // Outlier lists of the layer (built once) spare every CTA the sort in its prologue and the shared memory for it.
     const bool glists = L.K / kDqBlockK <= kDqMaxTiles && !getenv("OJASX_B200_TENSOR_NO_LISTS") && ensure_dq_lists(lists, L, generation, stream);
     if (glists) { P.tile_off = lists->off; P.tile_ent = lists->ent; }
+    // Batches of several 256-column tiles: two row tiles per CTA share every X tile (vq_dequant_gemm256_kernel), when
+    // the tile pairs fill the GPU without a split along K.  OJASX_B200_TENSOR_ROWS=128 / 256 forces one kernel or the
+    // other (256: with a split if the grid is small).
+    {
+        const char* rows_env = getenv("OJASX_B200_TENSOR_ROWS");
+        const char* tma_off = getenv("OJASX_B200_TENSOR_TMA");
+        const int rows = L.row_stop - L.row_start, forced = rows_env ? atoi(rows_env) : 0;
+        dim3 grid((rows + 2 * kDqBlockM - 1) / (2 * kDqBlockM), (L.batch + 255) / 256, 1);
+        const bool fills = (int)(grid.x * grid.y) * 3 >= num_sms() * 2;
+        CUtensorMap xmap{};
+        if ((forced == 256 || (forced != 128 && fills)) && !(tma_off && tma_off[0] == '0') && (glists || L.csr.nnz == 0) &&
+            rows > kDqBlockM && P.n_pad >= 64 && dequant_gemm256_smem(P.n_pad) <= kDqSmemBudget &&
+            encode_x_map(&xmap, L.x, L.K, L.batch, P.n_pad)) {
+            int z = 1, per = L.K / kDqBlockK;
+            if (forced == 256 && !getenv("OJASX_B200_TENSOR_NO_KSPLIT")) plan_ksplit((int)(grid.x * grid.y), L.K / kDqBlockK, num_sms(), 8, &z, &per);
+            if ((z > 1 ? per : L.K / kDqBlockK) <= kDqMaxTiles) {
+                P.ksplit = z;
+                P.tiles_per_split = z > 1 ? per : L.K / kDqBlockK;
+                int cols2 = 32;
+                while (cols2 < 2 * P.n_pad) cols2 <<= 1;
+                P.tmem_cols = cols2;
+                P.stages = kDq2Stages;
+                P.use_tma = 1;
+                const size_t smem = dequant_gemm256_smem(P.n_pad);
+                static thread_local size_t configured2[64] = {};
+                int dev = 0;
+                OJX_CUDA_TRY(cudaGetDevice(&dev));
+                if (dev < 0 || dev >= 64 || smem > configured2[dev]) {
+                    OJX_CUDA_TRY(cudaFuncSetAttribute(vq_dequant_gemm256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+                    if (dev >= 0 && dev < 64) configured2[dev] = smem;
+                }
+                grid.z = z;
+                cudaLaunchConfig_t cfg{};
+                cfg.gridDim = grid;
+                cfg.blockDim = dim3(kDq2Threads);
+                cfg.dynamicSmemBytes = smem;
+                cfg.stream = stream;
+                cudaLaunchAttribute attr[1];
+                attr[0].id = cudaLaunchAttributeClusterDimension;
+                attr[0].val.clusterDim.x = 1;
+                attr[0].val.clusterDim.y = 1;
+                attr[0].val.clusterDim.z = grid.z;
+                cfg.attrs = attr;
+                cfg.numAttrs = 1;
+                OJX_CUDA_TRY(cudaLaunchKernelEx(&cfg, vq_dequant_gemm256_kernel, P, xmap));
+                count_launch(1);
+                return OJX_OK;
+            }
+        }
+    }
+    // Stage buffers: at least one per producer group.  (A group waits on a stage's "empty" barrier by phase
+    // parity; with fewer stages than groups a group could be two phases ahead of a stage it shares with
+    // another group, and a parity wait cannot tell "two ahead" from "done".)  More stages when the batch
+    // tile is narrow; room for at least 1024 staged outlier entries is kept when every CTA lists its own.
     P.stages = kDqGroups;
     if (dequant_gemm_smem(P.n_pad, P.stages, glists ? 0 : 1024) > kDqSmemBudget) return OJX_ERR_UNSUPPORTED;
     while (P.stages < kDqStages && dequant_gemm_smem(P.n_pad, P.stages + 1, glists ? 0 : 4096) <= kDqSmemBudget) ++P.stages;
@@ -680,7 +1001,7 @@ int launch_dequant_gemm(const LinearProblem& L, cudaStream_t stream, DqLists* li
     P.tiles_per_split = L.K / kDqBlockK;
     if (!getenv("OJASX_B200_TENSOR_NO_KSPLIT")) {
         int z = 1, per = P.tiles_per_split;
-        plan_ksplit((int)(grid.x * grid.y), L.K / kDqBlockK, num_sms(), &z, &per);
+        plan_ksplit((int)(grid.x * grid.y), L.K / kDqBlockK, num_sms(), 4, &z, &per);
         if (z > 1) {
             P.ksplit = z;
             P.tiles_per_split = per;

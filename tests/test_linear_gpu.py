@@ -253,21 +253,27 @@ def test_tensor_core_outlier_paths(cuda, oracle, frac):
 
 
 @pytest.mark.parametrize("K,M,batch,frac", [(2560, 6912, 256, 0.0038), (6912, 2560, 64, 0.0038), (640, 1000, 300, 0.05), (2560, 700, 40, 0.0),
-                                            (2560, 5120, 48, 0.0038)])   # the last one: three K splits, 16 batch columns each
+                                            (2560, 5120, 48, 0.0038),   # three K splits, 16 batch columns each
+                                            (1280, 6912, 1100, 0.0038)])   # five batch tiles: the 256-row kernel by itself
 def test_tensor_core_feeds_agree(cuda, oracle, monkeypatch, K, M, batch, frac):
     """The X tile by the copy engine against 16-byte copies, and the outlier lists built once per layer against the
-    lists every CTA sorts for itself: the same weights meet the same activations in the same order, so the outputs
-    are equal bit for bit -- for whole layers, row slices that start off a 128-row boundary, a second slice of the
-    same layer (the lists are rebuilt)."""
+    lists every CTA sorts for itself: the same weights meet the same activations in the same order, so with one row
+    tile per CTA the outputs are equal bit for bit -- for whole layers, row slices that start off a 128-row boundary
+    and a second slice of the same layer (the lists are rebuilt).  The kernel with two row tiles per CTA (forced
+    here; by itself it takes batches of several 256-column tiles) splits K differently: same tolerance against the
+    oracle, close to the other kernel."""
     w = synth.make_vq_linear(K + M, K, M, block_dim=8, outlier_frac=frac, with_scales=True, with_bias=True)
     layer = ops.VQLinear.from_weights(w)
     xb = synth.to_bf16_f32(np.random.default_rng(batch).standard_normal((batch, K)).astype(np.float32))
     xt = torch.from_numpy(xb).to(cuda).bfloat16()
-    slices = [(0, M), (100, M - 37), (3, 131)]
+    slices = [(0, M), (100, M - 37), (3, 131), (256, min(M, 700))]
 
     def run_all():
         return [layer.forward_tensor(xt, a, b) for a, b in slices]
 
+    monkeypatch.setenv("OJASX_B200_TENSOR_ROWS", "256")
+    wide = run_all()
+    monkeypatch.setenv("OJASX_B200_TENSOR_ROWS", "128")
     new = run_all()
     monkeypatch.setenv("OJASX_B200_TENSOR_TMA", "0")
     no_tma = run_all()
@@ -276,12 +282,12 @@ def test_tensor_core_feeds_agree(cuda, oracle, monkeypatch, K, M, batch, frac):
     monkeypatch.delenv("OJASX_B200_TENSOR_TMA")
     no_lists = run_all()
     monkeypatch.delenv("OJASX_B200_TENSOR_NO_LISTS")
+    monkeypatch.delenv("OJASX_B200_TENSOR_ROWS")
     assert ojasx_b200.lib().ojasx_b200_take_device_error() == 0
-    for i in range(len(slices)):
-        assert torch.equal(new[i], no_tma[i]) and torch.equal(new[i], old[i]) and torch.equal(new[i], no_lists[i]), slices[i]
     want = oracle.linear_forward(w.codebook, w.codes, w.scales, w.bias, w.csr, xb, block_dim=8)
-    got = new[0].float().cpu().numpy()
-    assert np.all(np.abs(got - want) <= 2e-2 * np.abs(want) + 3e-2), np.abs(got - want).max()
-    # row slices may split K differently from the whole layer (other partial sums, same tolerance)
-    for (a, b), y in zip(slices[1:], new[1:]):
-        assert torch.allclose(y.float(), new[0][:, a:b].float(), rtol=2e-2, atol=3e-2)
+    for i, (a, b) in enumerate(slices):
+        assert torch.equal(new[i], no_tma[i]) and torch.equal(new[i], old[i]) and torch.equal(new[i], no_lists[i]), slices[i]
+        for y in (new[i], wide[i]):
+            got = y.float().cpu().numpy()
+            assert np.all(np.abs(got - want[:, a:b]) <= 2e-2 * np.abs(want[:, a:b]) + 3e-2), (slices[i], np.abs(got - want[:, a:b]).max())
+        assert torch.allclose(wide[i].float(), new[i].float(), rtol=2e-2, atol=3e-2)
