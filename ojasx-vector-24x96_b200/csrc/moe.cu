@@ -458,6 +458,74 @@ __global__ void __launch_bounds__(256) moe_router_logits_kernel(const float* __r
     peer_signal_when_last(link, gridDim.x * gridDim.y);
 }
 
+// Batches: a block scores eight experts (a warp each) for eight tokens at a time from a shared-memory tile of x, so a
+// router row is read once per eight tokens instead of once per token.  Every (token, expert) sum is formed exactly as
+// in router_logits_block: lane l adds columns l, l + 32, ... in order, then the same butterfly.
+constexpr int kLogitTokens = 8, kLogitCols = 512;
+__global__ void __launch_bounds__(256) moe_router_logits_tiled_kernel(const float* __restrict__ Wr, const void* __restrict__ x,
+                                                                      int io_dtype, int n_tokens, int H, int E,
+                                                                      float* __restrict__ logits, int e_begin, int e_end,
+                                                                      const __grid_constant__ PeerLink link) {
+    __shared__ __align__(16) float xs[kLogitTokens][kLogitCols];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = e_begin + blockIdx.x * 8 + warp, t0 = blockIdx.y * kLogitTokens;
+    const bool live = e < e_end;
+    const float* w = Wr + (size_t)(live ? e : e_begin) * H;
+    const size_t esz = io_dtype == OJX_BF16 ? 2 : 4;
+    float acc[kLogitTokens];
+#pragma unroll
+    for (int tt = 0; tt < kLogitTokens; ++tt) acc[tt] = 0.0f;
+    for (int c0 = 0; c0 < H; c0 += kLogitCols) {
+        const int nc = min(kLogitCols, H - c0);
+        __syncthreads();   // the previous tile has been read
+        if (io_dtype == OJX_F32 && (H & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {   // 16-byte pieces
+            const float* xf = static_cast<const float*>(x);
+            for (int i = threadIdx.x; i < kLogitTokens * kLogitCols / 4; i += 256) {
+                const int tt = i / (kLogitCols / 4), j = (i - tt * (kLogitCols / 4)) * 4, t = t0 + tt;
+                float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (t < n_tokens && j < nc) v = *reinterpret_cast<const float4*>(xf + (size_t)t * H + c0 + j);
+                *reinterpret_cast<float4*>(&xs[tt][j]) = v;
+            }
+        } else {
+            for (int i = threadIdx.x; i < kLogitTokens * kLogitCols; i += 256) {
+                const int tt = i / kLogitCols, j = i - tt * kLogitCols, t = t0 + tt;
+                float v = 0.0f;
+                if (t < n_tokens && j < nc) {
+                    const XLoad xl{static_cast<const char*>(x) + (size_t)t * H * esz, H, io_dtype};
+                    v = xl(c0 + j);
+                }
+                xs[tt][j] = v;
+            }
+        }
+        __syncthreads();
+        if (live) {
+            int cc = lane;
+            for (; cc + 3 * 32 < nc; cc += 4 * 32) {   // four router weights in flight, additions still in column order
+                float wv[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) wv[u] = __ldg(w + c0 + cc + 32 * u);
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int tt = 0; tt < kLogitTokens; ++tt) acc[tt] = __fadd_rn(acc[tt], __fmul_rn(wv[u], xs[tt][cc + 32 * u]));
+            }
+            for (; cc < nc; cc += 32) {
+                const float wv = __ldg(w + c0 + cc);
+#pragma unroll
+                for (int tt = 0; tt < kLogitTokens; ++tt) acc[tt] = __fadd_rn(acc[tt], __fmul_rn(wv, xs[tt][cc]));
+            }
+        }
+    }
+#pragma unroll
+    for (int tt = 0; tt < kLogitTokens; ++tt) {
+        float part = acc[tt];
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, off));
+        if (live && lane == 0 && t0 + tt < n_tokens) peer_store(link, logits + (size_t)(t0 + tt) * E + e, part);
+    }
+    peer_signal_when_last(link, gridDim.x * gridDim.y);
+}
+
 // Router logits and the per-token gate/up tables in one launch: neither depends on the other, both
 // depend only on x.  Blocks [0, lx*ly) are logits blocks (bx = b % lx, by = b / lx), the rest build
 // tables (16 groups of one token each).
@@ -871,6 +939,9 @@ int launch_moe_router(const float* Wr, const void* x, int io_dtype, int n_tokens
             case 32: moe_logits_prebuild_kernel<32><<<grid, 256, 0, s>>>(Wr, x, io_dtype, n_tokens, H, E, logits, lx, ly, G, codebook, Kcb, lut_out, e_begin, e_end, link); break;
             default: return OJX_ERR_UNSUPPORTED;
         }
+    } else if (n_tokens >= kLogitTokens) {
+        moe_router_logits_tiled_kernel<<<dim3(lx, (n_tokens + kLogitTokens - 1) / kLogitTokens), 256, 0, s>>>(Wr, x, io_dtype, n_tokens, H, E, logits,
+                                                                                                          e_begin, e_end, link);
     } else {
         moe_router_logits_kernel<<<dim3(lx, ly), 256, 0, s>>>(Wr, x, io_dtype, n_tokens, H, E, logits, e_begin, e_end, link);
     }
