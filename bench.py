@@ -49,9 +49,9 @@ METRIC = "vq_lut_gemv_2560x6912_hbm_gbs"
 # DRAM bytes (read + write) of one 2560->6912 layer inside lut_linear_kernel<8>, from an ncu capture of a
 # 148-layer launch of this kernel (dram__bytes_read.sum + dram__bytes_write.sum over the launch / 148); every
 # layer of a launch does the same work, so a launch's traffic is this figure times its layer count.
-TRAFFIC_PER_LAYER = 4099592
-TRAFFIC_SOURCE = ("ncu capture of lut_linear_kernel<8> as benched (the kernel with the peer-link argument), 148 layers per launch: "
-                  "606,141,696 B read + 598,016 B written; profiles/lut_linear_kernel_gemv_2560x6912.md")
+TRAFFIC_PER_LAYER = 4074776
+TRAFFIC_SOURCE = ("ncu capture of lut_linear_kernel<8> as benched (outlier entries streamed by the copy engine in the epilogue), "
+                  "148 layers per launch: 602,837,760 B read + 229,120 B written; profiles/lut_linear_kernel_gemv_2560x6912.md")
 
 
 def env_int(name, default):
@@ -722,7 +722,7 @@ def bench_kv(args, E):
             from oracle import oracle as O
             n = cache.sync_len()
             gk, gv = cache.read(0, n)
-            got = (cache.decode(q) if world == 1 else None)
+            got = cache.decode(q)      # this rank's heads, decoded locally (no exchange): every rank's shard is the same kernel
             if got is not None:
                 b = B - 1
                 qf = q[b, 0:4].float().cpu().numpy()

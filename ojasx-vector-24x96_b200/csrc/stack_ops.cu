@@ -40,10 +40,12 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(void* __restrict__ x, cons
         }
         return v;
     };
+    float wk[kNormKeep];   // the weights do not depend on the row sum: asked for now, used after it
 #pragma unroll
     for (int u = 0; u < kNormKeep; ++u) {
         const int i = tid + u * 256;
         keep[u] = i < H ? element(i) : 0.0f;
+        wk[u] = i < H ? w[i] : 0.0f;
         ss += keep[u] * keep[u];
     }
     for (int i = tid + kNormKeep * 256; i < H; i += 256) {
@@ -61,25 +63,25 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(void* __restrict__ x, cons
 #pragma unroll
     for (int u = 0; u < kNormKeep; ++u) {
         const int i = tid + u * 256;
-        if (i < H) st_io(out, base + i, io_dtype, keep[u] * inv * w[i]);
+        if (i < H) st_io(out, base + i, io_dtype, keep[u] * inv * wk[u]);
     }
     for (int i = tid + kNormKeep * 256; i < H; i += 256) st_io(out, base + i, io_dtype, ld_io(x, base + i, io_dtype) * inv * w[i]);
 }
 
 // Rotate-half rotary embedding in place on q [B, Hq, hd] and k [B, Hkv, hd] at positions pos[b].
+// grid = (heads of q and k, batch): a block turns one head, a thread one pair, so that a single sequence still
+// spreads over forty SMs instead of one block looping ten times over slow-path powf / sincosf.
 __global__ void rope_qk_kernel(void* __restrict__ q, void* __restrict__ k, const int* __restrict__ pos, int Hq, int Hkv,
                                int hd, float theta, int io_dtype) {
-    const int b = blockIdx.x, half = hd >> 1;
+    const int b = blockIdx.y, head = blockIdx.x, half = hd >> 1;
     const float p = (float)pos[b];
-    const int total = (Hq + Hkv) * half;
-    for (int i = threadIdx.x; i < total; i += blockDim.x) {
-        const int head = i / half, j = i - head * half;
-        void* buf = head < Hq ? q : k;
-        const size_t base = head < Hq ? ((size_t)b * Hq + head) * hd : ((size_t)b * Hkv + (head - Hq)) * hd;
+    void* buf = head < Hq ? q : k;
+    const size_t base = head < Hq ? ((size_t)b * Hq + head) * hd : ((size_t)b * Hkv + (head - Hq)) * hd;
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        const float x1 = ld_io(buf, base + j, io_dtype), x2 = ld_io(buf, base + half + j, io_dtype);
         const float inv = 1.0f / powf(theta, (float)(2 * j) / (float)hd);
         float s, c;
         sincosf(p * inv, &s, &c);
-        const float x1 = ld_io(buf, base + j, io_dtype), x2 = ld_io(buf, base + half + j, io_dtype);
         st_io(buf, base + j, io_dtype, x1 * c - x2 * s);
         st_io(buf, base + half + j, io_dtype, x2 * c + x1 * s);
     }
@@ -110,7 +112,8 @@ int ojasx_b200_rope_qk(void* d_q, void* d_k, const int* d_positions, int batch, 
                        float theta, int io_dtype, void* stream) {
     if (!d_q || !d_k || !d_positions || batch <= 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 || (head_dim & 1)) return OJX_ERR_ARG;
     if (io_dtype != OJX_F32 && io_dtype != OJX_BF16) return OJX_ERR_ARG;
-    rope_qk_kernel<<<batch, 256, 0, static_cast<cudaStream_t>(stream)>>>(d_q, d_k, d_positions, q_heads, kv_heads, head_dim, theta, io_dtype);
+    if (batch > 65535) return OJX_ERR_TOO_LARGE;   // a grid row per sequence
+    rope_qk_kernel<<<dim3(q_heads + kv_heads, batch), (head_dim / 2 + 31) / 32 * 32 < 256 ? (head_dim / 2 + 31) / 32 * 32 : 256, 0, static_cast<cudaStream_t>(stream)>>>(d_q, d_k, d_positions, q_heads, kv_heads, head_dim, theta, io_dtype);
     OJX_CUDA_TRY(cudaGetLastError());
     count_launch(1);
     return OJX_OK;
