@@ -54,6 +54,7 @@ MoeProblem MoeHandle::problem(const void* x, void* y, const int* idx, const floa
     P.expert_out = P.inter + (size_t)n_tokens * k * I;
     P.pair_list = reinterpret_cast<const int*>(P.expert_out + (size_t)n_tokens * k * H);
     P.plan = P.pair_list;   // the two expert paths keep their work lists in the same scratch
+    P.chain_ctl = P.pair_list + (size_t)n_tokens * k + 4;   // behind the pair list (1 + pairs ints of the 5 * pairs + 8 reserved)
     P.E_total = E_total;
     P.n_tokens = n_tokens; P.k_active = k; P.E = E; P.expert_offset = expert_offset;
     P.H = H; P.I = I; P.G = H / D; P.Gi = I / D; P.D = D; P.Kcb = 256; P.io_dtype = io;

@@ -89,6 +89,7 @@ struct MoeProblem {
                               // gathered into expert_out); 0: only the pairs this handle evaluated
     float gate_limit;         // > 0: gate is clamped from above and up to [-limit, limit] before silu(gate) * up
                               // (ResidualVQFusedExperts._apply_gate, ojasx_24x96/module.py:646-651); <= 0: no clamp
+    const int* chain_ctl;     // [1 + pairs] claim counter and per-slot flags of moe_experts_chain_kernel (zeroed by the plan kernel), or null
     int lut_blocks;           // layout of lut_in: 0 = [token][group][256]; 1 = 16-group blocks (moe_prebuild_kernel);
                               // 2 = per-slice images of the chain walk's table area (moe_chain_prebuild_kernel)
 };

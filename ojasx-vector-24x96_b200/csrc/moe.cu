@@ -140,87 +140,158 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) moe_down_kernel(const __
 // (2I rows, gate rows then up rows, contiguous in the code matrix) of one token.  The token's table slices come as
 // ready-made images of the table area (moe_chain_prebuild_kernel) through one bulk copy per slice; every warp finishes
 // the rows it walked (scale, outlier rows) in place, then inter = silu(gate) * up.  Same bits as moe_gate_up_kernel.
+// One work item of the gate/up pass: the routed pair in slot `slot` of the work list (all threads of the CTA; ends
+// with a barrier).
+template <int D>
+__device__ __forceinline__ void moe_gate_up_chain_item(const MoeProblem& P, unsigned char* smem_raw, int slot) {
+    const size_t esz = P.io_dtype == OJX_BF16 ? 2 : 4;
+    const int nslices = (P.G + ChainWalker<D>::SG - 1) / ChainWalker<D>::SG;
+    const int pair = P.pair_list ? P.pair_list[1 + slot] : slot;
+    const MoePair pr = decode_pair(P, pair);
+    if (pr.expert < 0) return;  // uniform across the CTA
+    const int n = 2 * P.I;
+    const size_t row0 = (size_t)pr.expert * n;
+    const ChainWalker<D> cw(smem_raw, P.gu_codes + row0 * P.G, n, P.G);
+    const XLoad xl{static_cast<const char*>(P.x) + (size_t)pr.token * P.H * esz, P.H, P.io_dtype};
+    // Everything the epilogue reads from global memory is asked for while the row walk still hides the latency:
+    // the token's activations wait in registers, the expert's row pointers in the (idle) activation area behind
+    // the copy barrier, the outlier entries and the scales are asked into L2 under the last walk.
+    constexpr int kXr = kCsrXFloats / kThreads, kRpMax = kXsFloats - 4;
+    const bool has = P.gu_csr.nnz > 0;
+    const bool x_regs = has && P.H <= kCsrXFloats, rp_early = has && n + 1 <= kRpMax;
+    float xr[kXr];
+#pragma unroll
+    for (int q = 0; q < kXr; ++q) {
+        const int k = threadIdx.x + q * kThreads;
+        xr[q] = (x_regs && k < P.H) ? xl(k) : 0.0f;
+    }
+    int* rp_s = cw.template at<int>(kChXs) + 4;
+    int jb = 0, je = 0;
+    if (has) { jb = P.gu_csr.row_ptrs[row0]; je = P.gu_csr.row_ptrs[row0 + n]; }
+    if (rp_early) {
+        for (int b0 = threadIdx.x; b0 <= n; b0 += kThreads * 4) {
+            int v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = b0 + u * kThreads <= n ? P.gu_csr.row_ptrs[row0 + b0 + u * kThreads] : 0;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) if (b0 + u * kThreads <= n) rp_s[b0 + u * kThreads] = v[u];
+        }
+    }
+    cw.run_prebuilt(P.lut_in + (size_t)pr.token * nslices * ChainWalker<D>::kImageFloats, [&]() {
+        for (int j = (jb & ~31) + threadIdx.x * 32; j < je; j += kThreads * 32) {
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(P.gu_csr.cols + j));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(P.gu_csr.vals + j));
+        }
+        if (has && !rp_early)
+            for (int r = threadIdx.x * 32; r <= n; r += kThreads * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(P.gu_csr.row_ptrs + row0 + r));
+        if (P.gu_scales)
+            for (int r = threadIdx.x * 32; r < n; r += kThreads * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(P.gu_scales + row0 + r));
+    });   // ends with a barrier: the table area is scratch now
+    const float* xsm = nullptr;
+    if (x_regs) {
+        float* xw = cw.epilogue_x();
+#pragma unroll
+        for (int q = 0; q < kXr; ++q) {
+            const int k = threadIdx.x + q * kThreads;
+            if (k < P.H) xw[k] = xr[q];
+        }
+        __syncthreads();
+        xsm = xw;
+    }
+    float* acc = cw.acc();
+    cw.warp_epilogue(P.gu_csr, (int)row0, P.gu_scales, nullptr, xsm, xl, [&](int m, float res) { acc[m - (int)row0] = res; }, rp_early ? rp_s : nullptr);
+    __syncthreads();
+    for (int i = threadIdx.x; i < P.I; i += kThreads) {
+        float gate = acc[i], up = acc[P.I + i];
+        if (P.gate_limit > 0.0f) {
+            gate = fminf(gate, P.gate_limit);
+            up = fminf(fmaxf(up, -P.gate_limit), P.gate_limit);
+        }
+        P.inter[(size_t)pair * P.I + i] = __fmul_rn(silu_ref(gate), up);
+    }
+    __syncthreads();   // the sums are parked again by the next work item
+}
+
 template <int D>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm) moe_gate_up_chain_kernel(const __grid_constant__ MoeProblem P) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int total = P.pair_list ? P.pair_list[0] : P.n_tokens * P.k_active;
-    const size_t esz = P.io_dtype == OJX_BF16 ? 2 : 4;
-    const int nslices = (P.G + ChainWalker<D>::SG - 1) / ChainWalker<D>::SG;
     if (!ChainWalker<D>::usable(smem_raw, P.gu_codes, P.cb_in, P.G)) {   // checked on the host as far as it can be; the
         if (threadIdx.x == 0) atomicExch(&g_bulk_copy_timeout, 2);      // shared-memory base only shows here
         return;
     }
-    for (int slot = blockIdx.x; slot < total; slot += gridDim.x) {
-        const int pair = P.pair_list ? P.pair_list[1 + slot] : slot;
-        const MoePair pr = decode_pair(P, pair);
-        if (pr.expert < 0) continue;  // uniform across the CTA
-        const int n = 2 * P.I;
-        const size_t row0 = (size_t)pr.expert * n;
-        const ChainWalker<D> cw(smem_raw, P.gu_codes + row0 * P.G, n, P.G);
-        const XLoad xl{static_cast<const char*>(P.x) + (size_t)pr.token * P.H * esz, P.H, P.io_dtype};
-        // Everything the epilogue reads from global memory is asked for while the row walk still hides the latency:
-        // the token's activations wait in registers, the expert's row pointers in the (idle) activation area behind
-        // the copy barrier, the outlier entries and the scales are asked into L2 under the last walk.
-        constexpr int kXr = kCsrXFloats / kThreads, kRpMax = kXsFloats - 4;
-        const bool has = P.gu_csr.nnz > 0;
-        const bool x_regs = has && P.H <= kCsrXFloats, rp_early = has && n + 1 <= kRpMax;
-        float xr[kXr];
-#pragma unroll
-        for (int q = 0; q < kXr; ++q) {
-            const int k = threadIdx.x + q * kThreads;
-            xr[q] = (x_regs && k < P.H) ? xl(k) : 0.0f;
-        }
-        int* rp_s = cw.template at<int>(kChXs) + 4;
-        int jb = 0, je = 0;
-        if (has) { jb = P.gu_csr.row_ptrs[row0]; je = P.gu_csr.row_ptrs[row0 + n]; }
-        if (rp_early) {
-            for (int b0 = threadIdx.x; b0 <= n; b0 += kThreads * 4) {
-                int v[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) v[u] = b0 + u * kThreads <= n ? P.gu_csr.row_ptrs[row0 + b0 + u * kThreads] : 0;
-#pragma unroll
-                for (int u = 0; u < 4; ++u) if (b0 + u * kThreads <= n) rp_s[b0 + u * kThreads] = v[u];
-            }
-        }
-        cw.run_prebuilt(P.lut_in + (size_t)pr.token * nslices * ChainWalker<D>::kImageFloats, [&]() {
-            for (int j = (jb & ~31) + threadIdx.x * 32; j < je; j += kThreads * 32) {
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(P.gu_csr.cols + j));
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(P.gu_csr.vals + j));
-            }
-            if (has && !rp_early)
-                for (int r = threadIdx.x * 32; r <= n; r += kThreads * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(P.gu_csr.row_ptrs + row0 + r));
-            if (P.gu_scales)
-                for (int r = threadIdx.x * 32; r < n; r += kThreads * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(P.gu_scales + row0 + r));
-        });   // ends with a barrier: the table area is scratch now
-        const float* xsm = nullptr;
-        if (x_regs) {
-            float* xw = cw.epilogue_x();
-#pragma unroll
-            for (int q = 0; q < kXr; ++q) {
-                const int k = threadIdx.x + q * kThreads;
-                if (k < P.H) xw[k] = xr[q];
-            }
-            __syncthreads();
-            xsm = xw;
-        }
-        float* acc = cw.acc();
-        cw.warp_epilogue(P.gu_csr, (int)row0, P.gu_scales, nullptr, xsm, xl, [&](int m, float res) { acc[m - (int)row0] = res; }, rp_early ? rp_s : nullptr);
-        __syncthreads();
-        for (int i = threadIdx.x; i < P.I; i += kThreads) {
-            float gate = acc[i], up = acc[P.I + i];
-            if (P.gate_limit > 0.0f) {
-                gate = fminf(gate, P.gate_limit);
-                up = fminf(fmaxf(up, -P.gate_limit), P.gate_limit);
-            }
-            P.inter[(size_t)pair * P.I + i] = __fmul_rn(silu_ref(gate), up);
-        }
-        __syncthreads();   // the sums are parked again by the next work item
-    }
+    for (int slot = blockIdx.x; slot < total; slot += gridDim.x) moe_gate_up_chain_item<D>(P, smem_raw, slot);
 }
 
 // ---- down projection of a routed pair by the chain walk: the pair's table is built in the kernel from its
 // intermediate vector (it is the pair's own, so nothing can be shared), all H rows of the expert are one work item.
 // Same bits as moe_down_kernel.
+template <int D>
+__device__ __forceinline__ void moe_down_chain_item(const MoeProblem& P, const PeerLink& link, unsigned char* smem_raw, int slot) {
+    const int pair = P.pair_list ? P.pair_list[1 + slot] : slot;
+    const MoePair pr = decode_pair(P, pair);
+    if (pr.expert < 0) return;
+    const int n = P.H;
+    const size_t row0 = (size_t)pr.expert * n;
+    const ChainWalker<D> cw(smem_raw, P.dn_codes + row0 * P.Gi, n, P.Gi);
+    const XLoad xl{P.inter + (size_t)pair * P.I, P.I, OJX_F32};
+    // what the epilogue reads from global memory is asked for before the walk (see moe_gate_up_chain_kernel); the
+    // row pointers wait behind the parked sums
+    constexpr int kXr = 4;
+    const bool has = P.dn_csr.nnz > 0;
+    const int rp_off = (n + 3) & ~3;
+    const bool x_regs = has && P.I <= kXr * kThreads, rp_early = has && rp_off + n + 1 <= kAccRows;
+    float xr[kXr];
+#pragma unroll
+    for (int q = 0; q < kXr; ++q) {
+        const int k = threadIdx.x + q * kThreads;
+        xr[q] = (x_regs && k < P.I) ? xl(k) : 0.0f;
+    }
+    int* rp_s = reinterpret_cast<int*>(cw.acc() + rp_off);
+    int jb = 0, je = 0;
+    if (has) { jb = P.dn_csr.row_ptrs[row0]; je = P.dn_csr.row_ptrs[row0 + n]; }
+    if (rp_early) {
+        for (int b0 = threadIdx.x; b0 <= n; b0 += kThreads * 4) {
+            int v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = b0 + u * kThreads <= n ? P.dn_csr.row_ptrs[row0 + b0 + u * kThreads] : 0;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) if (b0 + u * kThreads <= n) rp_s[b0 + u * kThreads] = v[u];
+        }
+    }
+    cw.run(xl, P.cb_down, P.Kcb, [&]() {
+        for (int j = (jb & ~31) + threadIdx.x * 32; j < je; j += kThreads * 32) {
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(P.dn_csr.cols + j));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(P.dn_csr.vals + j));
+        }
+        if (has && !rp_early)
+            for (int r = threadIdx.x * 32; r <= n; r += kThreads * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(P.dn_csr.row_ptrs + row0 + r));
+        if (P.dn_scales)
+            for (int r = threadIdx.x * 32; r < n; r += kThreads * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(P.dn_scales + row0 + r));
+    });
+    __syncthreads();   // walks over: the table area is scratch now
+    const float* xsm = nullptr;
+    if (has && P.I <= kCsrXFloats) {
+        float* xw = cw.epilogue_x();
+        if (x_regs) {
+#pragma unroll
+            for (int q = 0; q < kXr; ++q) {
+                const int k = threadIdx.x + q * kThreads;
+                if (k < P.I) xw[k] = xr[q];
+            }
+        } else {
+            for (int k = threadIdx.x; k < P.I; k += kThreads) xw[k] = xl(k);
+        }
+        __syncthreads();
+        xsm = xw;
+    }
+    float* out = P.expert_out + (size_t)pair * P.H;
+    cw.warp_epilogue(P.dn_csr, (int)row0, P.dn_scales, nullptr, xsm, xl,
+                     [&](int m, float res) { peer_store(link, out + (m - (int)row0), res); },   // expert-parallel: every rank gets the pair's output
+                     rp_early ? rp_s : nullptr);
+    __syncthreads();   // the next work item parks row pointers and sums again
+}
+
 template <int D>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm) moe_down_chain_kernel(const __grid_constant__ MoeProblem P,
                                                                               const __grid_constant__ PeerLink link) {
@@ -228,69 +299,53 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) moe_down_chain_kernel(co
     const int total = P.pair_list ? P.pair_list[0] : P.n_tokens * P.k_active;
     const bool usable = ChainWalker<D>::usable(smem_raw, P.dn_codes, P.cb_down, P.Gi);
     if (!usable && threadIdx.x == 0) atomicExch(&g_bulk_copy_timeout, 2);
-    for (int slot = blockIdx.x; usable && slot < total; slot += gridDim.x) {
-        const int pair = P.pair_list ? P.pair_list[1 + slot] : slot;
-        const MoePair pr = decode_pair(P, pair);
-        if (pr.expert < 0) continue;
-        const int n = P.H;
-        const size_t row0 = (size_t)pr.expert * n;
-        const ChainWalker<D> cw(smem_raw, P.dn_codes + row0 * P.Gi, n, P.Gi);
-        const XLoad xl{P.inter + (size_t)pair * P.I, P.I, OJX_F32};
-        // what the epilogue reads from global memory is asked for before the walk (see moe_gate_up_chain_kernel); the
-        // row pointers wait behind the parked sums
-        constexpr int kXr = 4;
-        const bool has = P.dn_csr.nnz > 0;
-        const int rp_off = (n + 3) & ~3;
-        const bool x_regs = has && P.I <= kXr * kThreads, rp_early = has && rp_off + n + 1 <= kAccRows;
-        float xr[kXr];
-#pragma unroll
-        for (int q = 0; q < kXr; ++q) {
-            const int k = threadIdx.x + q * kThreads;
-            xr[q] = (x_regs && k < P.I) ? xl(k) : 0.0f;
-        }
-        int* rp_s = reinterpret_cast<int*>(cw.acc() + rp_off);
-        int jb = 0, je = 0;
-        if (has) { jb = P.dn_csr.row_ptrs[row0]; je = P.dn_csr.row_ptrs[row0 + n]; }
-        if (rp_early) {
-            for (int b0 = threadIdx.x; b0 <= n; b0 += kThreads * 4) {
-                int v[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) v[u] = b0 + u * kThreads <= n ? P.dn_csr.row_ptrs[row0 + b0 + u * kThreads] : 0;
-#pragma unroll
-                for (int u = 0; u < 4; ++u) if (b0 + u * kThreads <= n) rp_s[b0 + u * kThreads] = v[u];
+    for (int slot = blockIdx.x; usable && slot < total; slot += gridDim.x) moe_down_chain_item<D>(P, link, smem_raw, slot);
+    peer_signal_when_last(link, gridDim.x);
+}
+
+// ---- both passes in one launch.  With a few routed pairs per CTA (32 tokens on one GPU, or a shard of an
+// expert-parallel layer) two launches cost a rounded-up wave each: 320 pairs on 148 CTAs are three waves of gate/up and
+// three of down where 4.3 would do.  Here the CTAs claim work items from one counter: first every pair's gate/up, then
+// every pair's down, which waits (bounded) for the flag its gate/up item raised.  A down item is claimed only after
+// all gate/up items have been claimed by CTAs that are running and never wait themselves, so the wait always ends.
+// ctl[0] = claim counter, ctl[1 + slot] = "intermediate vector of the slot is written"; moe_plan_kernel zeroes both.
+constexpr int kMoeFlagSpin = 1 << 22;
+template <int D>
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) moe_experts_chain_kernel(const __grid_constant__ MoeProblem P,
+                                                                                 const __grid_constant__ PeerLink link) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    // (no static shared memory: the walker needs the dynamic area at its fixed address; between two work items all of
+    // it is free, so the claimed item is handed round through its first word)
+    volatile int* s_item = reinterpret_cast<volatile int*>(smem_raw);
+    const int total = P.pair_list[0];
+    int* ctl = const_cast<int*>(P.chain_ctl);
+    const bool usable = ChainWalker<D>::usable(smem_raw, P.gu_codes, P.cb_in, P.G) && ChainWalker<D>::usable(smem_raw, P.dn_codes, P.cb_down, P.Gi);
+    if (!usable && threadIdx.x == 0) atomicExch(&g_bulk_copy_timeout, 2);
+    while (usable) {
+        if (threadIdx.x == 0) *s_item = atomicAdd(&ctl[0], 1);
+        __syncthreads();
+        const int item = *s_item;
+        __syncthreads();   // everyone has read the claim before it is overwritten
+        if (item >= 2 * total) break;
+        if (item < total) {
+            moe_gate_up_chain_item<D>(P, smem_raw, item);   // ends with a barrier: the intermediate vector is written
+            if (threadIdx.x == 0) {
+                __threadfence();
+                asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(ctl + 1 + item), "r"(1) : "memory");
             }
-        }
-        cw.run(xl, P.cb_down, P.Kcb, [&]() {
-            for (int j = (jb & ~31) + threadIdx.x * 32; j < je; j += kThreads * 32) {
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(P.dn_csr.cols + j));
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(P.dn_csr.vals + j));
-            }
-            if (has && !rp_early)
-                for (int r = threadIdx.x * 32; r <= n; r += kThreads * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(P.dn_csr.row_ptrs + row0 + r));
-            if (P.dn_scales)
-                for (int r = threadIdx.x * 32; r < n; r += kThreads * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(P.dn_scales + row0 + r));
-        });
-        __syncthreads();   // walks over: the table area is scratch now
-        const float* xsm = nullptr;
-        if (has && P.I <= kCsrXFloats) {
-            float* xw = cw.epilogue_x();
-            if (x_regs) {
-#pragma unroll
-                for (int q = 0; q < kXr; ++q) {
-                    const int k = threadIdx.x + q * kThreads;
-                    if (k < P.I) xw[k] = xr[q];
+        } else {
+            const int slot = item - total;
+            if (threadIdx.x == 0) {
+                int seen = 0;
+                for (int i = 0; i < kMoeFlagSpin && !seen; ++i) {
+                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(ctl + 1 + slot) : "memory");
+                    if (!seen) __nanosleep(64);
                 }
-            } else {
-                for (int k = threadIdx.x; k < P.I; k += kThreads) xw[k] = xl(k);
+                if (!seen) atomicExch(&g_bulk_copy_timeout, 4);
             }
             __syncthreads();
-            xsm = xw;
+            moe_down_chain_item<D>(P, link, smem_raw, slot);
         }
-        float* out = P.expert_out + (size_t)pair * P.H;
-        cw.warp_epilogue(P.dn_csr, (int)row0, P.dn_scales, nullptr, xsm, xl,
-                         [&](int m, float res) { peer_store(link, out + (m - (int)row0), res); },   // expert-parallel: every rank gets the pair's output
-                         rp_early ? rp_s : nullptr);
-        __syncthreads();   // the next work item parks row pointers and sums again
     }
     peer_signal_when_last(link, gridDim.x);
 }
@@ -341,6 +396,8 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const __grid_constant__ 
     const int pairs = P.n_tokens * P.k_active;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     for (int e = threadIdx.x; e < P.E; e += blockDim.x) cnt[e] = 0;
+    if (P.chain_ctl)   // claim counter and flags of the one-launch expert pass
+        for (int i = threadIdx.x; i <= pairs; i += blockDim.x) const_cast<int*>(P.chain_ctl)[i] = 0;
     __syncthreads();
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
         const int e = decode_pair(P, p).expert;
@@ -799,10 +856,22 @@ static int launch_moe_experts_t(const MoeProblem& P, cudaStream_t s, const PeerL
     }
     if constexpr (D <= 16) {
         if (P.lut_blocks == 2) {
-            if ((rc = set_smem(moe_gate_up_chain_kernel<D>)) != OJX_OK) return rc;
             if (!P.lut_ready) {
                 if ((rc = launch_chain_images<D>(P.x, P.io_dtype, P.n_tokens, P.H, P.G, P.cb_in, P.Kcb, const_cast<float*>(P.lut_in), s)) != OJX_OK) return rc;
             }
+            const char* one = std::getenv("OJASX_B200_MOE_ONE_LAUNCH");
+            if (P.pair_list && P.chain_ctl && P.dn_tiles == 1 && moe_chain_down_wanted(P) && !(one && one[0] == '0')) {
+                // gate/up and down of every pair from one work queue (no rounded-up wave between the two passes)
+                if ((rc = set_smem(moe_experts_chain_kernel<D>)) != OJX_OK) return rc;
+                moe_experts_chain_kernel<D><<<pairs < sms ? pairs : sms, kThreads, sizeof(CoreSmem), s>>>(P, link);
+                OJX_CUDA_TRY(cudaGetLastError());
+                const int n = P.n_tokens * P.H;
+                moe_combine_kernel<<<(n + 255) / 256, 256, 0, s>>>(P, link);
+                OJX_CUDA_TRY(cudaGetLastError());
+                count_launch(2 + extra);
+                return OJX_OK;
+            }
+            if ((rc = set_smem(moe_gate_up_chain_kernel<D>)) != OJX_OK) return rc;
             moe_gate_up_chain_kernel<D><<<pairs < sms ? pairs : sms, kThreads, sizeof(CoreSmem), s>>>(P);
             OJX_CUDA_TRY(cudaGetLastError());
         }

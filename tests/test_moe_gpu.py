@@ -199,6 +199,9 @@ def test_moe_gate_up_chain_walk_equals_row_walk(cuda, oracle, monkeypatch, H, I,
     clamp_chain = moe.forward(*args)
     moe.set_gate_limit(0.0)
     assert ojasx_b200.lib().ojasx_b200_take_device_error() == 0
+    monkeypatch.setenv("OJASX_B200_MOE_ONE_LAUNCH", "0")   # the same walks as two launches
+    assert torch.equal(moe.forward(*args), chain)
+    monkeypatch.delenv("OJASX_B200_MOE_ONE_LAUNCH")
     monkeypatch.setenv("OJASX_B200_MOE_CHAIN", "0")
     row = moe.forward(*args)
     routed_row = moe.forward_routed(args[0], k)
@@ -206,7 +209,7 @@ def test_moe_gate_up_chain_walk_equals_row_walk(cuda, oracle, monkeypatch, H, I,
     clamp_row = moe.forward(*args)
     moe.set_gate_limit(0.0)
     monkeypatch.delenv("OJASX_B200_MOE_CHAIN")
-    assert launches == 5                      # work list, table images, gate/up, down, combine
+    assert launches == 4                      # work list, table images, experts (gate/up and down from one queue), combine
     assert torch.equal(chain, row) and torch.equal(routed_chain, routed_row) and torch.equal(clamp_chain, clamp_row)
     assert not torch.equal(clamp_chain, chain)
     sample = [0, 1, 2, B - 1]
