@@ -797,19 +797,26 @@ static int expected_pairs(const MoeProblem& P) {
     return P.E_total > P.E ? (int)(((long long)pairs * P.E + P.E_total - 1) / P.E_total) : pairs;
 }
 
-// Gate/up by the chain walk (moe_gate_up_chain_kernel): a work item is a whole expert, which is the case once there
-// is at least one expected pair per resident CTA; the shape must fit the walker (16-byte pieces of code rows, all 2I
+// Routed pairs expected on this handle from which the expert pass takes whole experts by the chain walk: measured
+// faster than the tiled row-per-lane kernels from about half a pair per SM (80 pairs: 118 against 128 us per layer).
+static int moe_chain_min_pairs() {
+    const char* e = std::getenv("OJASX_B200_MOE_CHAIN_MIN_PAIRS");
+    return e ? atoi(e) : (kCtasPerSm * num_sms() + 1) / 2;
+}
+
+// Gate/up by the chain walk (moe_gate_up_chain_kernel): a work item is a whole expert, which pays once there are
+// enough expected pairs (moe_chain_min_pairs); the shape must fit the walker (16-byte pieces of code rows, all 2I
 // sums parked at once).  OJASX_B200_MOE_CHAIN=0 keeps the row-per-lane kernel (for comparisons).
 bool moe_chain_wanted(const MoeProblem& P) {
     if (!P.lut_in || P.D > 16 || (P.G & 15) != 0 || 2 * P.I > kAccRows || 2 * P.I < 512) return false;
-    if (expected_pairs(P) < kCtasPerSm * num_sms()) return false;
+    if (expected_pairs(P) < moe_chain_min_pairs()) return false;
     const char* e = std::getenv("OJASX_B200_MOE_CHAIN");
     return !(e && e[0] == '0');
 }
 
 static bool moe_chain_down_wanted(const MoeProblem& P) {
     if (P.D > 16 || (P.Gi & 15) != 0 || P.H > kAccRows || P.H < 512) return false;
-    if (expected_pairs(P) < kCtasPerSm * num_sms()) return false;
+    if (expected_pairs(P) < moe_chain_min_pairs()) return false;
     const char* e = std::getenv("OJASX_B200_MOE_CHAIN");
     return !(e && e[0] == '0');
 }
@@ -936,6 +943,7 @@ int launch_moe_experts(MoeProblem P, cudaStream_t s, const PeerLink* lk) {
     // kernel is left out and the pairs are visited in order (pairs of other shards are skipped on sight).
     if (pairs <= kMoePlanMinPairs) P.pair_list = nullptr;
     int want = (sms + expect - 1) / (expect > 0 ? expect : 1);
+    if (P.lut_blocks == 2) want = 1;   // the chain walk takes whole experts
     P.gu_tile = round_up((P.I + want - 1) / want, 16);
     if (P.gu_tile > kAccRows / 2) P.gu_tile = kAccRows / 2;
     P.gu_tiles = (P.I + P.gu_tile - 1) / P.gu_tile;
