@@ -1086,6 +1086,7 @@ extern "C" int ojasx_b200_moe_forward_noalloc(OjasxMoEHandle handle, const void*
     P.lut_in = nullptr;  // tables are rebuilt inside the gate/up kernel: no further scratch
     P.pair_list = nullptr;  // every pair is visited in order and skipped if it is not evaluated here
     P.plan = nullptr;
+    P.chain_ctl = nullptr;
     P.inter = scratch;
     P.expert_out = scratch + (size_t)n_tokens * k_active * h->I;
     return launch_moe_experts(P, static_cast<cudaStream_t>(stream));
