@@ -321,11 +321,11 @@ def run_ours(args):
 
     for _ in range(args.warmup):
         step()
-    E.barrier()
     sampler = ClockSampler(E.local)
+    sampler.start()          # before the barrier: a rank that is late into the timed loop holds every other rank up
     n0 = ojasx_b200.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler.start()
+    E.barrier()
     e0.record()
     for _ in range(args.steps):
         step()
@@ -333,7 +333,17 @@ def run_ours(args):
     E.barrier()
     clocks = sampler.stop()
     launches = ojasx_b200.launch_count() - n0
-    ms_step = E.max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    my_ms = e0.elapsed_time(e1)
+    ms_step = E.max_over_ranks(my_ms) / args.steps
+    if world > 1:
+        # every rank sampled its own GPU: the line carries the slowest median clock and every reason seen on any of them
+        # (a run in which ANY GPU of the job was slowed down is to be read as such)
+        clocks["min_sm_mhz_over_ranks"] = int(-E.max_over_ranks(-float(clocks["sm_mhz"] or 0)))
+        for name in ClockSampler.REASONS.values():
+            if E.max_over_ranks(1.0 if name in clocks["reasons"] else 0.0) > 0 and name not in clocks["reasons"]:
+                clocks["reasons"].append(name)
+        clocks["reasons"] = sorted(clocks["reasons"])
+        clocks["ms_per_step_fastest_rank"] = round(-E.max_over_ranks(-my_ms) / args.steps, 5)
     value = P * alg / (ms_step * 1e-3) / 1e9          # whole job: the P layers, whoever computed them
 
     # spot-check the last pass against the oracle (outside the timed region): full rows on every rank
