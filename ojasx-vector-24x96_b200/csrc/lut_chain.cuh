@@ -519,8 +519,6 @@ struct ChainWalker {
         if (lane == 0) {
             bulk_bar_init(bars);
             bulk_bar_init(bars + 8);
-            issue(0);
-            if (nch > 1) issue(1);
         }
         // row pointers of the warp's rows into its idle code ring; scale and bias onto the parked sums
         for (int i0 = lane; i0 <= nu; i0 += 32 * 8) {
@@ -529,6 +527,38 @@ struct ChainWalker {
             for (int u = 0; u < 8; ++u) v[u] = i0 + 32 * u <= nu ? csr.row_ptrs[row0 + rb + i0 + 32 * u] : 0;
 #pragma unroll
             for (int u = 0; u < 8; ++u) if (i0 + 32 * u <= nu) rpw[i0 + 32 * u] = v[u];
+        }
+        __syncwarp();
+        // Normally the entries of 32 consecutive rows fit a buffer (384 entries are 12 per row): then a chunk is exactly
+        // the entries of the next 32 rows, every lane finishes one whole row per chunk and nothing straddles.
+        const int nblk = (nu + 31) >> 5;
+        bool fits = true;
+        for (int k = lane; k < nblk; k += 32) fits = fits && (rpw[min(32 * k + 32, nu)] - (rpw[32 * k] & ~3)) <= CH;
+        fits = __all_sync(0xffffffffu, fits);
+        auto count_of = [&](int k, int& jc) {   // entries the copy engine brings for block k, from entry jc on
+            jc = rpw[32 * k] & ~3;
+            const int want = (rpw[min(32 * k + 32, nu)] - jc + 3) & ~3;
+            return max(0, min(want, (csr.nnz - jc) & ~3));
+        };
+        auto issue_block = [&](int k) {   // lane 0
+            int jc;
+            const int cnt = count_of(k, jc);
+            float* buf = region + (k & 1) * 2 * CH;
+            void* bar = bars + (k & 1) * 8;
+            bulk_expect(bar, (unsigned)cnt * 8u);
+            if (cnt > 0) {
+                bulk_copy_add(bar, buf, csr.cols + jc, (unsigned)cnt * 4u);
+                bulk_copy_add(bar, buf + CH, csr.vals + jc, (unsigned)cnt * 4u);
+            }
+        };
+        if (lane == 0) {   // the first two chunks are on their way while scale and bias are applied
+            if (fits) {
+                issue_block(0);
+                if (nblk > 1) issue_block(1);
+            } else {       // a block of rows with more entries than a buffer: fixed-size chunks, rows finished as their entries land
+                issue(0);
+                if (nch > 1) issue(1);
+            }
         }
         if (scales || bias) {
             for (int i0 = lane; i0 < nu; i0 += 32 * 8) {
@@ -550,6 +580,39 @@ struct ChainWalker {
                     }
                 }
             }
+        }
+        __syncwarp();
+        if (fits) {
+            for (int k = 0; k < nblk; ++k) {
+                const int r = 32 * k + lane, ee = rpw[min(32 * k + 32, nu)];
+                int jc;
+                const int got = count_of(k, jc);
+                int* cols = reinterpret_cast<int*>(region + (k & 1) * 2 * CH);
+                float* vals = region + (k & 1) * 2 * CH + CH;
+                if (lane < 4 && jc + got + lane < ee) {   // entries the copy left out because the arrays end inside their 16-byte piece
+                    cols[got + lane] = csr.cols[jc + got + lane];
+                    vals[got + lane] = csr.vals[jc + got + lane];
+                }
+                bulk_copy_wait(bars + (k & 1) * 8, (unsigned)((k >> 1) & 1));
+                __syncwarp();
+                const int m = ee - jc;
+#pragma unroll 4
+                for (int i = lane; i < m; i += 32) vals[i] = __fmul_rn(vals[i], xsm[cols[i]]);
+                __syncwarp();
+                if (r < nu) {
+                    float a = 0.0f;
+                    for (int j = rpw[r]; j < rpw[r + 1]; ++j) a = __fadd_rn(a, vals[j - jc]);
+                    store(row0 + rb + r, __fadd_rn(accw[r], a));
+                }
+                __syncwarp();
+                if (lane == 0 && k + 2 < nblk) issue_block(k + 2);
+            }
+            __syncwarp();
+            if (lane == 0) {
+                bulk_bar_inval(bars);
+                bulk_bar_inval(bars + 8);
+            }
+            return;
         }
         __syncwarp();
         int cur = 0;             // first row not finished yet
