@@ -803,7 +803,7 @@ def bench_stack(args, E):
                                    else "token by token through the sharded decode step",
                         "bytes_per_step_estimate": int(step_bytes),
                         "roofline": hbm_roofline(step_bytes, dt_dec / args.stack_new, E.world,
-                                                 note="a decode step is a chain of about 340 small launches per rank; latency, not bandwidth, bounds it"),
+                                                 note="a decode step is a chain of about 290 small launches per rank; latency, not bandwidth, bounds it"),
                         "all_finite": bool(torch.isfinite(logits).all().item())}
         del stack
         torch.cuda.empty_cache()
